@@ -1,0 +1,214 @@
+"""Python host-side mirror of the C ABI in ``include/gie_b200.h`` (ctypes; no torch types cross the boundary).
+
+The native library ``libgie_b200.so`` is built in-tree by ``build.py``.  Importing this package never falls back to
+any other implementation: if the library is missing, loading raises.  Device memory and streams come from the caller
+(raw integer device pointers and a ``cudaStream_t`` value), exactly as in the reference's operator API.
+
+Because the directory name contains a hyphen, load the package with ``importlib`` under the module name
+``cuda_inference_b200`` (see ``__graft_entry__.load_package``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libgie_b200.so")
+
+# gie::StatusCode values (include/gpu_inference/error.h:16-26 of the reference)
+OK, INVALID_ARGUMENT, UNSUPPORTED, WORKSPACE_TOO_SMALL, CUDA_ERROR, INTERNAL = 0, 1, 2, 3, 4, 7
+STATUS_NAMES = {0: "ok", 1: "invalid_argument", 2: "unsupported", 3: "workspace_too_small", 4: "cuda_error", 7: "internal"}
+# gie::Precision order
+FP32, FP16, BF16, TF32 = 0, 1, 2, 3
+FLAG_BIAS_FP32, FLAG_WEIGHTS_PREPACKED = 1, 2
+
+
+class GieError(RuntimeError):
+    """Mirror of gie::Error: carries the status code of the failed call."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(code, code)}: {message}")
+        self.code = code
+
+
+class ConvDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "batch", "in_channels", "in_h", "in_w", "out_channels", "kernel_h", "kernel_w", "stride_h", "stride_w",
+        "pad_h", "pad_w", "dilation_h", "dilation_w", "groups", "precision", "has_bias", "relu")] + [("flags", C.c_uint32)]
+
+
+class ConvCfg(C.Structure):
+    _fields_ = [("tile_n", C.c_int32), ("tile_k", C.c_int32), ("stages", C.c_int32), ("split_k", C.c_int32),
+                ("variant", C.c_int32), ("reserved", C.c_int32 * 3)]
+
+
+class ConvInfo(C.Structure):
+    _fields_ = [("supported", C.c_int32), ("variant", C.c_int32), ("cfg", ConvCfg), ("workspace_bytes", C.c_uint64),
+                ("persistent_bytes", C.c_uint64), ("dynamic_smem_bytes", C.c_uint32), ("threads_per_block", C.c_uint32),
+                ("num_blocks", C.c_int64), ("launches", C.c_int32), ("padded_channels", C.c_int32), ("reason", C.c_char * 256)]
+
+
+class RmsNormDesc(C.Structure):
+    _fields_ = [("rows", C.c_int32), ("hidden", C.c_int32), ("eps", C.c_float), ("dtype", C.c_int32), ("flags", C.c_uint32)]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the native library once; raises if it has not been built (there is no fallback path)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python {os.path.join(HERE, 'build.py')}` (needs nvcc, no GPU)")
+        L = C.CDLL(LIB_PATH)
+        vp, i32, i64, sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+        L.gieb_last_error.restype = C.c_char_p
+        L.gieb_version.restype = i32
+        L.gieb_conv_validate.argtypes = [C.POINTER(ConvDesc)]
+        L.gieb_conv_query.argtypes = [C.POINTER(ConvDesc), C.POINTER(ConvCfg), i32, C.POINTER(ConvInfo)]
+        L.gieb_padded_channels.argtypes = [C.POINTER(ConvDesc), C.POINTER(ConvCfg)]
+        L.gieb_conv_plan_create.argtypes = [C.POINTER(ConvDesc), C.POINTER(ConvCfg), i32, C.POINTER(vp)]
+        L.gieb_conv_plan_destroy.argtypes = [vp]
+        L.gieb_conv_plan_destroy.restype = None
+        L.gieb_conv_plan_info.argtypes = [vp, C.POINTER(ConvInfo)]
+        L.gieb_conv_launch.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp]
+        L.gieb_conv_plan_device_status.argtypes = [vp, C.POINTER(C.c_uint32)]
+        L.gieb_repack_nchw_to_nhwc.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+        L.gieb_prepack_weights.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+        L.gieb_rmsnorm_launch.argtypes = [C.POINTER(RmsNormDesc), vp, vp, vp, vp, vp, vp]
+        L.gieb_bias_act_launch.argtypes = [i32, i32, i32, i32, vp, i32, vp, vp]
+        L.gieb_maxpool2d_launch.argtypes = [i32] * 8 + [vp, vp, vp]
+        L.gieb_add_relu_launch.argtypes = [i32, i32, vp, vp, vp, i64, vp]
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().gieb_last_error().decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise GieError(status, last_error())
+
+
+@dataclass
+class ConvProblem:
+    """Mirror of gie::ConvProblem (geometry + precision + fused epilogue), plus the extension flags."""
+
+    batch: int = 1
+    in_channels: int = 1
+    in_h: int = 1
+    in_w: int = 1
+    out_channels: int = 1
+    kernel_h: int = 1
+    kernel_w: int = 1
+    stride_h: int = 1
+    stride_w: int = 1
+    pad_h: int = 0
+    pad_w: int = 0
+    dilation_h: int = 1
+    dilation_w: int = 1
+    groups: int = 1
+    precision: int = FP32
+    has_bias: bool = False
+    relu: bool = False
+    flags: int = 0
+
+    def desc(self) -> ConvDesc:
+        return ConvDesc(self.batch, self.in_channels, self.in_h, self.in_w, self.out_channels, self.kernel_h, self.kernel_w,
+                        self.stride_h, self.stride_w, self.pad_h, self.pad_w, self.dilation_h, self.dilation_w, self.groups,
+                        int(self.precision), int(self.has_bias), int(self.relu), int(self.flags))
+
+    @property
+    def out_h(self) -> int:
+        return (self.in_h + 2 * self.pad_h - self.dilation_h * (self.kernel_h - 1) - 1) // self.stride_h + 1
+
+    @property
+    def out_w(self) -> int:
+        return (self.in_w + 2 * self.pad_w - self.dilation_w * (self.kernel_w - 1) - 1) // self.stride_w + 1
+
+    @property
+    def flops(self) -> int:
+        return 2 * self.out_channels * self.batch * self.out_h * self.out_w * self.in_channels * self.kernel_h * self.kernel_w
+
+
+def make_cfg(tile_n=0, tile_k=0, stages=0, split_k=0, variant=0) -> ConvCfg:
+    return ConvCfg(tile_n, tile_k, stages, split_k, variant, (C.c_int32 * 3)(0, 0, 0))
+
+
+def validate_problem(p: ConvProblem) -> None:
+    """gie::validate_problem: raises GieError(INVALID_ARGUMENT / UNSUPPORTED)."""
+    check(lib().gieb_conv_validate(C.byref(p.desc())))
+
+
+def query(p: ConvProblem, cfg: ConvCfg | None = None, device: int = -1) -> ConvInfo:
+    info = ConvInfo()
+    check(lib().gieb_conv_query(C.byref(p.desc()), C.byref(cfg) if cfg is not None else None, device, C.byref(info)))
+    return info
+
+
+class ConvPlan:
+    """Mirror of gie::ExecutionPlan for the one sm_100a kernel family: create once, launch many times."""
+
+    def __init__(self, problem: ConvProblem, cfg: ConvCfg | None = None, device: int = -1):
+        self.problem = problem
+        self._h = C.c_void_p()
+        check(lib().gieb_conv_plan_create(C.byref(problem.desc()), C.byref(cfg) if cfg is not None else None, device,
+                                          C.byref(self._h)))
+        self.info = ConvInfo()
+        check(lib().gieb_conv_plan_info(self._h, C.byref(self.info)))
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(self.info.workspace_bytes)
+
+    def launch(self, x: int, w: int, bias: int | None, y: int, workspace: int | None, workspace_bytes: int, stream: int = 0) -> None:
+        """execute_unchecked: raw device pointers, asynchronous on `stream`."""
+        check(lib().gieb_conv_launch(self._h, x, w, bias, y, workspace, workspace_bytes, stream))
+
+    def device_status(self) -> int:
+        v = C.c_uint32()
+        check(lib().gieb_conv_plan_device_status(self._h, C.byref(v)))
+        return int(v.value)
+
+    def close(self) -> None:
+        if self._h:
+            lib().gieb_conv_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def repack_nchw_to_nhwc(src: int, dst: int, batch: int, channels: int, hw: int, c_padded: int, stream: int = 0) -> None:
+    check(lib().gieb_repack_nchw_to_nhwc(src, dst, batch, channels, hw, c_padded, stream))
+
+
+def prepack_weights(src: int, dst: int, out_channels: int, channels: int, rs: int, c_padded: int, stream: int = 0) -> None:
+    check(lib().gieb_prepack_weights(src, dst, out_channels, channels, rs, c_padded, stream))
+
+
+def rmsnorm_forward(rows: int, hidden: int, eps: float, dtype: int, x: int, gamma: int, y: int, residual_in: int | None = None,
+                    residual_out: int | None = None, stream: int = 0, gamma_fp32: bool = False) -> None:
+    """gie::rmsnorm_forward on raw device pointers; dtype uses gie::DataType order (0 fp32, 1 fp16, 2 bf16)."""
+    d = RmsNormDesc(rows, hidden, eps, dtype, 1 if gamma_fp32 else 0)
+    check(lib().gieb_rmsnorm_launch(C.byref(d), x, gamma, y, residual_in, residual_out, stream))
+
+
+def bias_act(precision: int, batch: int, channels: int, hw: int, bias: int | None, relu: bool, y: int, stream: int = 0) -> None:
+    check(lib().gieb_bias_act_launch(precision, batch, channels, hw, bias, int(relu), y, stream))
+
+
+def maxpool2d(precision: int, batch: int, channels: int, h: int, w: int, kernel: int, stride: int, pad: int, x: int, y: int,
+              stream: int = 0) -> None:
+    check(lib().gieb_maxpool2d_launch(precision, batch, channels, h, w, kernel, stride, pad, x, y, stream))
+
+
+def add_relu(precision: int, relu: bool, a: int, b: int, y: int, n: int, stream: int = 0) -> None:
+    check(lib().gieb_add_relu_launch(precision, int(relu), a, b, y, n, stream))

@@ -1,0 +1,553 @@
+// C ABI of the library (declared in include/gie_b200.h): problem validation, configuration selection inside the one
+// sm_100a kernel family, plans, tensor-map encoding and launches.  Host code only; the kernels live in the other
+// translation units of this directory.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "gie_b200.h"
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace {
+
+using namespace gieb;
+
+// ---- error reporting -------------------------------------------------------------------------------------------
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+int fail_cuda(cudaError_t e, const char* what) {
+  (void)cudaGetLastError();  // clear the non-sticky error, as the reference's throw_cuda_error does (src/runtime/error.cpp:22-24)
+  return fail(GIEB_CUDA_ERROR, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+#define GIEB_CUDA(expr)                                  \
+  do {                                                   \
+    const cudaError_t gieb_e_ = (expr);                  \
+    if (gieb_e_ != cudaSuccess) return fail_cuda(gieb_e_, #expr); \
+  } while (0)
+
+// ---- hardware constants of the one supported target (B200, sm_100a) -------------------------------------------------
+constexpr int kNumSms = 148;
+constexpr size_t kMaxDynamicSmem = 232448;  // 227 KiB opt-in limit per CTA
+constexpr size_t kSmemBudget = 200 * 1024;  // ring + control; leaves headroom below the opt-in limit
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); }
+int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+struct Geometry {
+  int out_h, out_w, pq;
+  int64_t pixels;      // B * P * Q
+  int64_t y_elems, x_elems, w_elems;
+  int esize;
+};
+
+Geometry geometry(const gieb_conv_desc& d) {
+  Geometry g;
+  g.out_h = (d.in_h + 2 * d.pad_h - d.dilation_h * (d.kernel_h - 1) - 1) / d.stride_h + 1;
+  g.out_w = (d.in_w + 2 * d.pad_w - d.dilation_w * (d.kernel_w - 1) - 1) / d.stride_w + 1;
+  g.pq = g.out_h * g.out_w;
+  g.pixels = int64_t(d.batch) * g.pq;
+  g.y_elems = g.pixels * d.out_channels;
+  g.x_elems = int64_t(d.batch) * d.in_channels * d.in_h * d.in_w;
+  g.w_elems = int64_t(d.out_channels) * d.in_channels * d.kernel_h * d.kernel_w;
+  g.esize = (d.precision == GIEB_FP16 || d.precision == GIEB_BF16) ? 2 : 4;
+  return g;
+}
+
+// validate_problem (src/runtime/conv2d.cpp:83-109)
+int validate(const gieb_conv_desc* d) {
+  if (d == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null problem descriptor");
+  if (d->batch <= 0 || d->in_channels <= 0 || d->in_h <= 0 || d->in_w <= 0 || d->out_channels <= 0 || d->kernel_h <= 0 ||
+      d->kernel_w <= 0)
+    return fail(GIEB_INVALID_ARGUMENT, "all extents must be positive");
+  if (d->stride_h <= 0 || d->stride_w <= 0) return fail(GIEB_INVALID_ARGUMENT, "strides must be positive");
+  if (d->pad_h < 0 || d->pad_w < 0) return fail(GIEB_INVALID_ARGUMENT, "padding must be non-negative");
+  if (d->dilation_h != 1 || d->dilation_w != 1) return fail(GIEB_UNSUPPORTED, "dilation != 1 is not supported");
+  if (d->groups != 1) return fail(GIEB_UNSUPPORTED, "grouped convolution is not supported");
+  if (d->precision < GIEB_FP32 || d->precision > GIEB_TF32) return fail(GIEB_INVALID_ARGUMENT, "unknown precision id %d", d->precision);
+  if (int64_t(d->in_h) + 2 * d->pad_h < d->kernel_h || int64_t(d->in_w) + 2 * d->pad_w < d->kernel_w)
+    return fail(GIEB_INVALID_ARGUMENT, "kernel larger than padded input");
+  const Geometry g = geometry(*d);
+  if (g.out_h <= 0 || g.out_w <= 0) return fail(GIEB_INVALID_ARGUMENT, "empty output");
+  const int64_t lim = 2147483647LL;
+  const int64_t gk = int64_t(d->in_channels) * d->kernel_h * d->kernel_w;
+  if (int64_t(d->batch) * g.out_h * g.out_w > lim || gk > lim) return fail(GIEB_INVALID_ARGUMENT, "GEMM extents exceed 32-bit indexing");
+  if (int64_t(d->in_channels) * d->in_h * d->in_w > lim) return fail(GIEB_INVALID_ARGUMENT, "per-image input size exceeds 32-bit indexing");
+  if (int64_t(d->out_channels) * g.out_h * g.out_w > lim) return fail(GIEB_INVALID_ARGUMENT, "per-image output size exceeds 32-bit indexing");
+  return GIEB_OK;
+}
+
+// ---- configuration selection --------------------------------------------------------------------------------------
+// The reference ranks ~115 kernels of six backends with a roofline model (src/runtime/perf_model.cpp:130-174).  Here
+// the search space is one kernel family: (tile_n, tile_k, stages, split_k).  The estimate below counts SM cycles of
+// the slowest CTA: per reduction slab max(tensor-pipe time, shared-memory read time), plus fixed prologue/epilogue
+// cost, plus (for split-K) writing and re-reading FP32 partials and the extra launch.
+struct Resolved {
+  int variant;  // 1 tensor path (repack + im2col TMA), 3 FP32 SIMT
+  int tile_n, tile_k, stages, split_k;
+  int c_padded, kb_per_tap, total_kb, kb_per_split;
+  int tiles_m, tiles_n;
+  size_t smem;
+  size_t ws_x, ws_w, ws_part, ws_total;  // workspace layout (bytes; offsets are cumulative in this order)
+};
+
+int pick_tile_k(int c) {
+  const int base = round_up(c, 16);
+  if (double(round_up(c, 64)) <= 1.15 * base) return 64;
+  if (double(round_up(c, 32)) <= 1.15 * base) return 32;
+  return 16;
+}
+
+double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_n, int tile_k, int split) {
+  const int c_padded = round_up(d.in_channels, tile_k);
+  const int total_kb = d.kernel_h * d.kernel_w * (c_padded / tile_k);
+  const int kb_per_split = ceil_div(total_kb, split);
+  const int real_split = ceil_div(total_kb, kb_per_split);
+  const int64_t ctas = int64_t(ceil_div(g.pixels, kTileM)) * ceil_div(d.out_channels, tile_n) * real_split;
+  const double waves = double((ctas + kNumSms - 1) / kNumSms);
+  const double mma = double(tile_n) * tile_k / 32.0;                   // 128 x N x K MACs at 4096 MAC/clk/SM
+  const double smem = double(kTileM + tile_n) * tile_k * 2.0 / 128.0;  // operand bytes at 128 B/clk/SM
+  const double slab = mma > smem ? mma : smem;
+  const double epilogue = 600.0 + 6.0 * tile_n;
+  double per_cta = 1800.0 + kb_per_split * slab + epilogue;
+  double total = waves * per_cta;
+  if (real_split > 1) {
+    const double bytes = 2.0 * real_split * double(g.y_elems) * 4.0;
+    total += 6000.0 + bytes / 2048.0;  // extra launch + partial traffic at ~4 TB/s (L2-resident partials)
+  }
+  return total;
+}
+
+int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, char* why, size_t why_len) {
+  auto no = [&](const char* m) { snprintf(why, why_len, "%s", m); return GIEB_UNSUPPORTED; };
+  memset(r, 0, sizeof(*r));
+  const Geometry g = geometry(d);
+  gieb_conv_cfg c;
+  memset(&c, 0, sizeof(c));
+  if (user) c = *user;
+
+  if (d.precision == GIEB_TF32) return no("TF32 is not offered: the only TF32 route of the reference is its cuBLAS im2col backend");
+  if (d.precision == GIEB_FP32) {
+    if (c.variant != 0 && c.variant != 3) return no("FP32 runs on the SIMT kernel only (variant 3)");
+    if (d.flags & (GIEB_FLAG_WEIGHTS_PREPACKED)) return no("prepacked weights apply to the 16-bit tensor path only");
+    r->variant = 3;
+    r->tile_n = conv_fp32_tile(g.pixels, d.out_channels);
+    r->tile_k = 16;
+    r->stages = 2;
+    r->split_k = 1;
+    if (ceil_div(d.out_channels, 32) > 65535) return no("grid.y limit exceeded");
+    return GIEB_OK;
+  }
+  if (c.variant != 0 && c.variant != 1) return no("unknown kernel variant for 16-bit precision (1 = im2col-TMA tensor path)");
+  r->variant = 1;
+
+  // hardware limits of the im2col-mode tensor map (rank 4): traversal strides 1..8, corners and offsets 8-bit
+  if (d.stride_h > 8 || d.stride_w > 8) return no("stride > 8 cannot be expressed by the TMA im2col traversal stride");
+  if (d.pad_h > 127 || d.pad_w > 127 || d.kernel_h > 128 || d.kernel_w > 128) return no("padding/kernel extent exceeds the TMA im2col corner range");
+
+  r->tile_k = c.tile_k ? c.tile_k : pick_tile_k(d.in_channels);
+  if (r->tile_k != 16 && r->tile_k != 32 && r->tile_k != 64) return no("tile_k must be 16, 32 or 64");
+  r->c_padded = round_up(d.in_channels, r->tile_k);
+  r->kb_per_tap = r->c_padded / r->tile_k;
+  r->total_kb = d.kernel_h * d.kernel_w * r->kb_per_tap;
+
+  if (c.tile_n) {
+    if (c.tile_n != 32 && c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256) return no("tile_n must be 32, 64, 128 or 256");
+    r->tile_n = c.tile_n;
+  }
+  if (c.split_k < 0) return no("split_k must be >= 0");
+  // search (tile_n, split_k) unless fixed
+  double best = 1e300;
+  int best_n = 0, best_s = 0;
+  const int n_opts[4] = {32, 64, 128, 256};
+  for (int ni = 0; ni < 4; ++ni) {
+    const int tn = n_opts[ni];
+    if (r->tile_n && tn != r->tile_n) continue;
+    if (!r->tile_n && tn > 32 && tn / 2 >= d.out_channels) continue;  // never pad channels by 2x or more
+    for (int s = 1; s <= 16; ++s) {
+      if (c.split_k && s != c.split_k) continue;
+      if (s > 1 && r->total_kb < 2 * s) break;  // reduction too short (src/kernels/tensor_core_mma.cu:292 rule)
+      if (s > 1 && size_t(s) * size_t(g.y_elems) * 4 > (size_t(1) << 31)) break;
+      const double t = estimate_cycles(d, g, tn, r->tile_k, s);
+      if (t < best) { best = t; best_n = tn; best_s = s; }
+    }
+  }
+  if (best_n == 0) {
+    if (c.split_k > 1) return no("reduction too short for this split-K factor");
+    return no("no feasible tile configuration");
+  }
+  r->tile_n = best_n;
+  r->kb_per_split = ceil_div(r->total_kb, best_s);
+  r->split_k = ceil_div(r->total_kb, r->kb_per_split);  // every slice non-empty
+  r->tiles_m = ceil_div(g.pixels, kTileM);
+  r->tiles_n = ceil_div(d.out_channels, r->tile_n);
+  if (r->tiles_n > 65535 || r->split_k > 65535) return no("grid limit exceeded");
+
+  const size_t stage_bytes = size_t(kTileM + r->tile_n) * r->tile_k * 2;
+  int stages = c.stages ? c.stages : int((kSmemBudget - 3072) / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (!c.stages && stages > r->kb_per_split) stages = r->kb_per_split < 2 ? 2 : r->kb_per_split;
+  if (stages < 2 || stages > kMaxStages) return no("stages must be in [2, 8]");
+  r->stages = stages;
+  r->smem = conv_tc_smem_bytes(r->tile_n, r->tile_k, stages);
+  if (r->smem > kMaxDynamicSmem) return no("configuration needs more shared memory than one CTA may have (227 KiB)");
+
+  // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
+  // src/kernels/tensor_core_mma.cu:265-278)
+  r->ws_x = align256(size_t(d.batch) * d.in_h * d.in_w * r->c_padded * 2);
+  r->ws_w = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : align256(size_t(d.out_channels) * d.kernel_h * d.kernel_w * r->c_padded * 2);
+  r->ws_part = r->split_k > 1 ? align256(size_t(r->split_k) * size_t((g.y_elems + 3) & ~int64_t(3)) * 4) : 0;
+  r->ws_total = r->ws_x + r->ws_w + r->ws_part;
+  if (r->ws_total > (size_t(180) << 30) / 4) return no("workspace exceeds a quarter of device memory");
+  return GIEB_OK;
+}
+
+void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) {
+  const Geometry g = geometry(d);
+  out->supported = 1;
+  out->variant = r.variant;
+  out->cfg.tile_n = r.tile_n;
+  out->cfg.tile_k = r.tile_k;
+  out->cfg.stages = r.stages;
+  out->cfg.split_k = r.split_k;
+  out->cfg.variant = r.variant;
+  out->workspace_bytes = r.ws_total;
+  out->persistent_bytes = sizeof(uint32_t);
+  out->padded_channels = r.c_padded;
+  if (r.variant == 3) {
+    out->dynamic_smem_bytes = 0;
+    out->threads_per_block = r.tile_n == 64 ? 256 : 64;
+    out->num_blocks = conv_fp32_num_blocks(g.pixels, d.out_channels);
+    out->launches = 1;
+  } else {
+    out->dynamic_smem_bytes = uint32_t(r.smem);
+    out->threads_per_block = kTcThreads;
+    out->num_blocks = int64_t(r.tiles_m) * r.tiles_n * r.split_k;
+    out->launches = 2 + ((d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : 1) + (r.split_k > 1 ? 1 : 0);
+  }
+}
+
+// ---- tensor-map encoding ------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+using EncodeIm2colFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const int*, const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+int g_driver_version = 0;
+std::once_flag g_driver_once;
+cudaError_t g_driver_err = cudaSuccess;
+
+void load_driver_entry_points() {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  g_driver_err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (g_driver_err != cudaSuccess || q != cudaDriverEntryPointSuccess) { if (g_driver_err == cudaSuccess) g_driver_err = cudaErrorSymbolNotFound; return; }
+  g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+  g_driver_err = cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q);
+  if (g_driver_err != cudaSuccess || q != cudaDriverEntryPointSuccess) { if (g_driver_err == cudaSuccess) g_driver_err = cudaErrorSymbolNotFound; return; }
+  g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+  (void)cudaDriverGetVersion(&g_driver_version);
+}
+
+CUtensorMapSwizzle swizzle_for(int tile_k) {
+  return tile_k == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (tile_k == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+// Drivers up to 13.1 mis-handle descriptors of tensors smaller than 128 KiB unless one descriptor bit is cleared; this
+// is the work-around CUTLASS applies after both encode calls (cute/atom/copy_traits_sm90_tma.hpp and
+// copy_traits_sm90_im2col.hpp in the CUTLASS 4.x header tree).
+void small_tensor_fixup(CUtensorMap* m, size_t tensor_bytes) {
+  if (g_driver_version <= 13010 && tensor_bytes < 131072) reinterpret_cast<uint64_t*>(m)[1] &= ~(1ull << 21);
+}
+
+}  // namespace
+
+struct gieb_conv_plan {
+  gieb_conv_desc desc;
+  Resolved r;
+  Geometry g;
+  int device;
+  uint32_t* d_status;
+};
+
+namespace {
+
+int encode_maps(const gieb_conv_plan* pl, const void* xn, const void* wk, CUtensorMap* tm_act, CUtensorMap* tm_wgt) {
+  const gieb_conv_desc& d = pl->desc;
+  const Resolved& r = pl->r;
+  const CUtensorMapDataType dt = d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapSwizzle sw = swizzle_for(r.tile_k);
+  {
+    const cuuint64_t dims[4] = {cuuint64_t(r.c_padded), cuuint64_t(d.in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
+    const cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(d.in_w) * r.c_padded * 2,
+                                   cuuint64_t(d.in_h) * d.in_w * r.c_padded * 2};
+    const int lower[2] = {-d.pad_w, -d.pad_h};
+    const int upper[2] = {d.pad_w - (d.kernel_w - 1), d.pad_h - (d.kernel_h - 1)};
+    const cuuint32_t trav[4] = {1, cuuint32_t(d.stride_w), cuuint32_t(d.stride_h), 1};
+    const CUresult res = g_encode_im2col(tm_act, dt, 4, const_cast<void*>(xn), dims, strides, lower, upper, cuuint32_t(r.tile_k),
+                                         cuuint32_t(kTileM), trav, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeIm2col failed with CUresult %d", int(res));
+    small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * d.in_w * r.c_padded * 2);
+  }
+  {
+    const cuuint64_t kp = cuuint64_t(d.kernel_h) * d.kernel_w * r.c_padded;
+    const cuuint64_t dims[2] = {kp, cuuint64_t(d.out_channels)};
+    const cuuint64_t strides[1] = {kp * 2};
+    const cuuint32_t box[2] = {cuuint32_t(r.tile_k), cuuint32_t(r.tile_n)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult res = g_encode_tiled(tm_wgt, dt, 2, const_cast<void*>(wk), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled failed with CUresult %d", int(res));
+    small_tensor_fixup(tm_wgt, size_t(kp) * d.out_channels * 2);
+  }
+  return GIEB_OK;
+}
+
+int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
+                cudaStream_t st) {
+  if (pl == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null plan");
+  const gieb_conv_desc& d = pl->desc;
+  const Resolved& r = pl->r;
+  if (x == nullptr || w == nullptr || y == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
+  if (d.has_bias && bias == nullptr) return fail(GIEB_INVALID_ARGUMENT, "problem has a bias but no bias pointer was given");
+  if (!d.has_bias) bias = nullptr;
+  if (r.ws_total > 0) {
+    if (reinterpret_cast<uintptr_t>(ws) % 256 != 0) return fail(GIEB_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+    if (ws == nullptr || ws_bytes < r.ws_total)
+      return fail(GIEB_WORKSPACE_TOO_SMALL, "needs %zu bytes of workspace, got %zu", r.ws_total, ws_bytes);
+  }
+  int cur = 0;
+  GIEB_CUDA(cudaGetDevice(&cur));
+  if (cur != pl->device) return fail(GIEB_INVALID_ARGUMENT, "plan was created for device %d but device %d is current", pl->device, cur);
+
+  if (r.variant == 3) {
+    GIEB_CUDA(conv_fp32_launch(x, w, bias, y, d.batch, d.in_channels, d.in_h, d.in_w, d.out_channels, d.kernel_h, d.kernel_w,
+                               d.stride_h, d.stride_w, d.pad_h, d.pad_w, pl->g.out_h, pl->g.out_w, d.relu, st));
+    return GIEB_OK;
+  }
+
+  std::call_once(g_driver_once, load_driver_entry_points);
+  if (g_driver_err != cudaSuccess) return fail_cuda(g_driver_err, "resolving cuTensorMapEncode* driver entry points");
+
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  void* xn = wsb;
+  const void* wk = w;
+  if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)) wk = wsb + r.ws_x;
+  else if (reinterpret_cast<uintptr_t>(w) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "prepacked weights must be 16-byte aligned");
+  float* part = r.split_k > 1 ? reinterpret_cast<float*>(wsb + r.ws_x + r.ws_w) : nullptr;
+
+  CUtensorMap tm_act, tm_wgt;
+  const int st_maps = encode_maps(pl, xn, wk, &tm_act, &tm_wgt);
+  if (st_maps != GIEB_OK) return st_maps;
+
+  GIEB_CUDA(repack_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, st));
+  if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED))
+    GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
+
+  ConvTcParams p;
+  memset(&p, 0, sizeof(p));
+  p.m_total = int(pl->g.pixels);
+  p.out_channels = d.out_channels;
+  p.out_h = pl->g.out_h;
+  p.out_w = pl->g.out_w;
+  p.pq = pl->g.pq;
+  p.kernel_w = d.kernel_w;
+  p.c_padded = r.c_padded;
+  p.kb_per_tap = r.kb_per_tap;
+  p.total_kb = r.total_kb;
+  p.kb_per_split = r.kb_per_split;
+  p.stride_h = d.stride_h; p.stride_w = d.stride_w; p.pad_h = d.pad_h; p.pad_w = d.pad_w;
+  p.stages = r.stages;
+  p.relu = d.relu; p.has_bias = d.has_bias;
+  p.is_bf16 = d.precision == GIEB_BF16;
+  p.bias_fp32 = (d.flags & GIEB_FLAG_BIAS_FP32) ? 1 : 0;
+  p.idesc = ptx::make_idesc_f16(kTileM, r.tile_n, p.is_bf16, false, false);
+  p.bias = bias;
+  p.y = y;
+  p.partial = part;
+  p.status = pl->d_status;
+  dim3 grid(unsigned(r.tiles_m), unsigned(r.tiles_n), unsigned(r.split_k));
+  GIEB_CUDA(conv_tc_launch(r.tile_n, r.tile_k, tm_act, tm_wgt, p, grid, r.smem, st));
+  if (r.split_k > 1)
+    GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_bf16, y, st));
+  return GIEB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* gieb_last_error(void) { return g_err; }
+int gieb_version(void) { return 1; }
+
+int gieb_conv_validate(const gieb_conv_desc* desc) { return validate(desc); }
+
+int gieb_conv_query(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, int device, gieb_conv_info* out) {
+  (void)device;
+  if (out == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null output");
+  memset(out, 0, sizeof(*out));
+  const int st = validate(desc);
+  if (st != GIEB_OK) { snprintf(out->reason, sizeof(out->reason), "%s", g_err); return st; }
+  Resolved r;
+  const int rs = resolve(*desc, cfg, &r, out->reason, sizeof(out->reason));
+  if (rs != GIEB_OK) return GIEB_OK;  // a well-formed question with the answer "not supported"
+  fill_info(*desc, r, out);
+  return GIEB_OK;
+}
+
+int gieb_padded_channels(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg) {
+  gieb_conv_info info;
+  if (gieb_conv_query(desc, cfg, -1, &info) != GIEB_OK || !info.supported) return -1;
+  return info.padded_channels;
+}
+
+int gieb_conv_plan_create(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, int device, gieb_conv_plan** out) {
+  if (out == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null output");
+  *out = nullptr;
+  const int st = validate(desc);
+  if (st != GIEB_OK) return st;
+  Resolved r;
+  char why[256] = "";
+  if (resolve(*desc, cfg, &r, why, sizeof(why)) != GIEB_OK) return fail(GIEB_UNSUPPORTED, "%.255s", why);
+
+  int prev = 0;
+  GIEB_CUDA(cudaGetDevice(&prev));
+  if (device < 0) device = prev;
+  if (device != prev) GIEB_CUDA(cudaSetDevice(device));
+  struct Restore { int prev, dev; ~Restore() { if (prev != dev) cudaSetDevice(prev); } } restore{prev, device};
+
+  cudaDeviceProp prop;
+  GIEB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) return fail(GIEB_UNSUPPORTED, "this library contains sm_100a code only; device %d is sm_%d%d", device, prop.major, prop.minor);
+
+  gieb_conv_plan* pl = new (std::nothrow) gieb_conv_plan;
+  if (pl == nullptr) return fail(GIEB_INTERNAL, "out of host memory");
+  pl->desc = *desc;
+  pl->r = r;
+  pl->g = geometry(*desc);
+  pl->device = device;
+  pl->d_status = nullptr;
+
+  // Plan-owned status word, zeroed through a private stream so no other stream is waited for or delayed
+  // (the behaviour tests/test_runtime_concurrency.cu:53-73 pins for plan creation).
+  cudaError_t e = cudaMalloc(&pl->d_status, sizeof(uint32_t));
+  if (e == cudaSuccess) {
+    cudaStream_t s = nullptr;
+    e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    if (e == cudaSuccess) {
+      e = cudaMemsetAsync(pl->d_status, 0, sizeof(uint32_t), s);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+      cudaStreamDestroy(s);
+    }
+  }
+  if (e == cudaSuccess && r.variant == 1) e = conv_tc_prepare(r.tile_n, r.tile_k, kMaxDynamicSmem);
+  if (e != cudaSuccess) {
+    if (pl->d_status) cudaFree(pl->d_status);
+    delete pl;
+    return fail_cuda(e, "plan creation");
+  }
+  *out = pl;
+  return GIEB_OK;
+}
+
+void gieb_conv_plan_destroy(gieb_conv_plan* plan) {
+  if (plan == nullptr) return;
+  if (plan->d_status) cudaFree(plan->d_status);
+  delete plan;
+}
+
+int gieb_conv_plan_info(const gieb_conv_plan* plan, gieb_conv_info* out) {
+  if (plan == nullptr || out == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null argument");
+  memset(out, 0, sizeof(*out));
+  fill_info(plan->desc, plan->r, out);
+  return GIEB_OK;
+}
+
+int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  return launch_impl(plan, x, w, bias, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int gieb_conv_plan_device_status(const gieb_conv_plan* plan, uint32_t* status_out) {
+  if (plan == nullptr || status_out == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null argument");
+  cudaStream_t s = nullptr;
+  GIEB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  cudaError_t e = cudaMemcpyAsync(status_out, plan->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  cudaStreamDestroy(s);
+  if (e != cudaSuccess) return fail_cuda(e, "reading the plan status word");
+  return GIEB_OK;
+}
+
+int gieb_repack_nchw_to_nhwc(const void* src, void* dst, int batch, int channels, int hw, int c_padded, void* stream) {
+  if (src == nullptr || dst == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
+  if (batch <= 0 || channels <= 0 || hw <= 0) return fail(GIEB_INVALID_ARGUMENT, "extents must be positive");
+  if (c_padded < channels || c_padded % 8 != 0) return fail(GIEB_INVALID_ARGUMENT, "c_padded must be a multiple of 8 and >= channels");
+  if (reinterpret_cast<uintptr_t>(dst) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "destination must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(src) % 2 != 0) return fail(GIEB_INVALID_ARGUMENT, "source must be 2-byte aligned");
+  GIEB_CUDA(repack_launch(src, dst, batch, channels, hw, c_padded, static_cast<cudaStream_t>(stream)));
+  return GIEB_OK;
+}
+
+int gieb_prepack_weights(const void* src, void* dst, int out_channels, int channels, int rs, int c_padded, void* stream) {
+  return gieb_repack_nchw_to_nhwc(src, dst, out_channels, channels, rs, c_padded, stream);
+}
+
+int gieb_rmsnorm_launch(const gieb_rmsnorm_desc* d, const void* x, const void* gamma, void* y, const void* rin, void* rout,
+                        void* stream) {
+  // argument rules of rmsnorm_forward (src/transformer/rmsnorm.cu:155-160)
+  if (d == nullptr) return fail(GIEB_INVALID_ARGUMENT, "rmsnorm: null descriptor");
+  if (d->rows <= 0 || d->hidden <= 0) return fail(GIEB_INVALID_ARGUMENT, "rmsnorm: rows and hidden must be positive");
+  if (!x || !gamma || !y) return fail(GIEB_INVALID_ARGUMENT, "rmsnorm: null pointer");
+  if ((rin == nullptr) != (rout == nullptr)) return fail(GIEB_INVALID_ARGUMENT, "rmsnorm: residual_in and residual_out must be given together");
+  if (y == x || y == gamma || y == rin || y == rout) return fail(GIEB_INVALID_ARGUMENT, "rmsnorm: y must not alias x, gamma or the residual buffers");
+  if (d->dtype < 0 || d->dtype > 2) return fail(GIEB_INVALID_ARGUMENT, "rmsnorm: unknown dtype id %d", d->dtype);
+  GIEB_CUDA(rmsnorm_launch(d->rows, d->hidden, d->eps, d->dtype, int(d->flags & 1u), x, gamma, y, rin, rout, static_cast<cudaStream_t>(stream)));
+  return GIEB_OK;
+}
+
+int gieb_bias_act_launch(int precision, int batch, int channels, int hw, const void* bias, int relu, void* y, void* stream) {
+  if (y == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
+  if (batch <= 0 || channels <= 0 || hw <= 0) return fail(GIEB_INVALID_ARGUMENT, "extents must be positive");
+  if (precision < 0 || precision > 2) return fail(GIEB_INVALID_ARGUMENT, "precision must be fp32, fp16 or bf16");
+  GIEB_CUDA(bias_act_launch(precision, int64_t(batch) * channels * hw, channels, hw, bias, relu, y, static_cast<cudaStream_t>(stream)));
+  return GIEB_OK;
+}
+
+int gieb_maxpool2d_launch(int precision, int batch, int channels, int h, int w, int kernel, int stride, int pad, const void* x,
+                          void* y, void* stream) {
+  if (x == nullptr || y == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
+  if (batch <= 0 || channels <= 0 || h <= 0 || w <= 0 || kernel <= 0 || stride <= 0 || pad < 0 || pad >= kernel)
+    return fail(GIEB_INVALID_ARGUMENT, "bad pooling geometry");
+  if (h + 2 * pad < kernel || w + 2 * pad < kernel) return fail(GIEB_INVALID_ARGUMENT, "window larger than padded input");
+  if (precision < 0 || precision > 2) return fail(GIEB_INVALID_ARGUMENT, "precision must be fp32, fp16 or bf16");
+  GIEB_CUDA(maxpool2d_launch(precision, batch, channels, h, w, kernel, stride, pad, x, y, static_cast<cudaStream_t>(stream)));
+  return GIEB_OK;
+}
+
+int gieb_add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, void* stream) {
+  if (a == nullptr || b == nullptr || y == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
+  if (n <= 0) return fail(GIEB_INVALID_ARGUMENT, "element count must be positive");
+  if (precision < 0 || precision > 2) return fail(GIEB_INVALID_ARGUMENT, "precision must be fp32, fp16 or bf16");
+  GIEB_CUDA(add_relu_launch(precision, relu, a, b, y, n, static_cast<cudaStream_t>(stream)));
+  return GIEB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,312 @@
+// Implicit-GEMM convolution on the sm_100a tensor cores.
+//
+// GEMM view used here (transposed with respect to the reference's, src/kernels/tensor_core_mma.cu:99-251, which
+// puts output channels on M): rows (M) are output PIXELS, columns (N) are output CHANNELS, the reduction runs over
+// (r, s, c) with the channel fastest:
+//      D[pixel, oc] = sum_{r,s,c} Xn[pixel @ (r,s), c] * Wk[oc, (r,s), c]
+//   * Xn is the channel-contiguous (NHWC, channel-padded) copy of the activations.  One reduction slab of BK
+//     channels at one filter tap is fetched by a single TMA im2col-mode load, which also produces the zero
+//     padding, the stride and the wrap from one output row / image to the next.
+//   * Wk is the prepacked weight matrix [O][R*S*Cp]; a slab is one tiled TMA box.
+//   * Both land in shared memory in the 128/64/32-byte swizzled K-major layout tcgen05.mma reads, in a ring of
+//     `stages` buffers guarded by full/empty mbarriers.
+//   * One thread issues tcgen05.mma (128 x BN x 16 per instruction); the FP32 accumulator tile lives in tensor
+//     memory: lane = pixel, column = output channel.
+//   * Four epilogue warps read the accumulators with tcgen05.ld, add bias, apply ReLU, round once to the storage
+//     type and store to NCHW: for a fixed channel the 32 lanes of a warp hold 32 consecutive pixels, so every store
+//     instruction writes one contiguous run.  With split-K the FP32 partial tile is stored instead.
+// With pixels on M, a thread owns one pixel and all channels of the tile, which is what a contiguous-per-channel
+// NCHW store needs, and any output pointer alignment is legal (tests/test_runtime_concurrency.cu:190-216).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace gieb {
+namespace {
+
+constexpr uint32_t kCtrlBytes = 2048;  // [0,1024): bias tile as float; [1024,2048): mbarriers + TMEM address slot
+
+template <int BN, int BK>
+__global__ void __launch_bounds__(kTcThreads, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_wgt,
+               const ConvTcParams p) {
+  constexpr int ROW_BYTES = BK * 2;
+  constexpr uint32_t A_BYTES = kTileM * ROW_BYTES;
+  constexpr uint32_t B_BYTES = BN * ROW_BYTES;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int MMAS_PER_SLAB = BK / 16;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+  float* bias_s = reinterpret_cast<float*>(smem);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + 1024);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  uint64_t* accum_bar = empty_bar + kMaxStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint8_t* stage_base = smem + kCtrlBytes;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * kTileM;
+  const int n0 = blockIdx.y * BN;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_end = min(p.total_kb, kb_begin + p.kb_per_split);
+  const int num_kb = kb_end - kb_begin;
+  const int stages = p.stages;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tm_act);
+    ptx::prefetch_tensormap(&tm_wgt);
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    ptx::mbar_init(accum_bar, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  if (warp >= 2) {  // stage this tile's bias as float
+    for (int i = threadIdx.x - 64; i < BN; i += kTcThreads - 64) {
+      const int oc = n0 + i;
+      float b = 0.f;
+      if (p.has_bias && p.partial == nullptr && oc < p.out_channels) {
+        if (p.bias_fp32) b = static_cast<const float*>(p.bias)[oc];
+        else if (p.is_bf16) b = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[oc]);
+        else b = __half2float(static_cast<const __half*>(p.bias)[oc]);
+      }
+      bias_s[i] = b;
+    }
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      const int img = m0 / p.pq;
+      const int rem = m0 - img * p.pq;
+      const int p0 = rem / p.out_w;
+      const int q0 = rem - p0 * p.out_w;
+      const int base_w = q0 * p.stride_w - p.pad_w;
+      const int base_h = p0 * p.stride_h - p.pad_h;
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % stages;
+        const uint32_t phase = (i / stages) & 1;
+        if (!ptx::mbar_wait(&empty_bar[s], phase ^ 1u, p.status, kStatusProducerTimeout)) break;
+        const int kb = kb_begin + i;
+        const int tap = kb / p.kb_per_tap;
+        const int cb = kb - tap * p.kb_per_tap;
+        const int r = tap / p.kernel_w;
+        const int sx = tap - r * p.kernel_w;
+        uint8_t* a_dst = stage_base + size_t(s) * STAGE_BYTES;
+        uint8_t* b_dst = a_dst + A_BYTES;
+        ptx::mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+        ptx::tma_load_im2col_4d(a_dst, &tm_act, &full_bar[s], cb * BK, base_w, base_h, img, uint16_t(sx), uint16_t(r));
+        ptx::tma_load_2d(b_dst, &tm_wgt, &full_bar[s], tap * p.c_padded + cb * BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % stages;
+        const uint32_t phase = (i / stages) & 1;
+        if (!ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
+        const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+        for (int k = 0; k < MMAS_PER_SLAB; ++k) {
+          ptx::mma_f16_ss(tmem_base, ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + k * 32),
+                          ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32), p.idesc, (i | k) != 0);
+        }
+        ptx::mma_commit(&empty_bar[s]);  // frees the slot once these MMAs have read it
+      }
+      ptx::mma_commit(accum_bar);        // accumulator tile complete
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5 cover TMEM lane quarters 2,3,0,1) ----------------
+    const int quad = warp & 3;
+    const int m = m0 + quad * 32 + lane;
+    const bool ok = ptx::mbar_wait(accum_bar, 0, p.status, kStatusEpilogueTimeout);
+    __syncwarp();
+    ptx::tc_fence_after_sync();
+    if (__all_sync(0xffffffffu, ok)) {
+      const bool m_ok = m < p.m_total;
+      const int img = m_ok ? m / p.pq : 0;
+      const int pix = m_ok ? m - img * p.pq : 0;
+      const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
+      const int64_t total = int64_t(p.m_total) * p.out_channels;
+      float* part = p.partial ? p.partial + int64_t(blockIdx.z) * ((total + 3) & ~int64_t(3)) : nullptr;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(chunk * 32), v);
+        ptx::tmem_ld_wait();
+        if (m_ok) {
+          const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
+          if (part) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < nvalid) part[base + int64_t(chunk * 32 + j) * p.pq] = __uint_as_float(v[j]);
+          } else if (p.is_bf16) {
+            __nv_bfloat16* y = static_cast<__nv_bfloat16*>(p.y);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float a = __uint_as_float(v[j]) + bias_s[chunk * 32 + j];
+              if (p.relu) a = fmaxf(a, 0.f);
+              if (j < nvalid) y[base + int64_t(chunk * 32 + j) * p.pq] = __float2bfloat16_rn(a);
+            }
+          } else {
+            __half* y = static_cast<__half*>(p.y);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float a = __uint_as_float(v[j]) + bias_s[chunk * 32 + j];
+              if (p.relu) a = fmaxf(a, 0.f);
+              if (j < nvalid) y[base + int64_t(chunk * 32 + j) * p.pq] = __float2half_rn(a);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int BK>
+cudaError_t prepare_one(size_t smem_bytes) {
+  return cudaFuncSetAttribute(conv_tc_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
+}
+
+template <int BN, int BK>
+cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tw, const ConvTcParams& p, dim3 grid, size_t smem,
+                       cudaStream_t st) {
+  conv_tc_kernel<BN, BK><<<grid, kTcThreads, smem, st>>>(ta, tw, p);
+  return cudaGetLastError();
+}
+
+#define GIEB_TC_DISPATCH(FN, ...)                                                     \
+  switch (tile_n * 100 + tile_k) {                                                    \
+    case 32 * 100 + 16: return FN<32, 16>(__VA_ARGS__);                               \
+    case 32 * 100 + 32: return FN<32, 32>(__VA_ARGS__);                               \
+    case 32 * 100 + 64: return FN<32, 64>(__VA_ARGS__);                               \
+    case 64 * 100 + 16: return FN<64, 16>(__VA_ARGS__);                               \
+    case 64 * 100 + 32: return FN<64, 32>(__VA_ARGS__);                               \
+    case 64 * 100 + 64: return FN<64, 64>(__VA_ARGS__);                               \
+    case 128 * 100 + 16: return FN<128, 16>(__VA_ARGS__);                             \
+    case 128 * 100 + 32: return FN<128, 32>(__VA_ARGS__);                             \
+    case 128 * 100 + 64: return FN<128, 64>(__VA_ARGS__);                             \
+    case 256 * 100 + 16: return FN<256, 16>(__VA_ARGS__);                             \
+    case 256 * 100 + 32: return FN<256, 32>(__VA_ARGS__);                             \
+    case 256 * 100 + 64: return FN<256, 64>(__VA_ARGS__);                             \
+    default: return cudaErrorInvalidValue;                                            \
+  }
+
+// ---- split-K reduction: y = round(act(sum_z partial[z] + bias)) -------------------------------------------------
+// Follows the arithmetic of splitk_reduce (src/kernels/tensor_core_mma.cu:254-262): partials summed in slice order
+// in FP32, then bias, ReLU and one rounding.
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t total, int64_t slice_stride, int out_channels,
+                     int pq, const void* __restrict__ bias, int bias_fp32, int relu, T* __restrict__ y) {
+  const int64_t step = int64_t(gridDim.x) * blockDim.x;
+  const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  auto bias_of = [&](int64_t i) -> float {
+    if (bias == nullptr) return 0.f;
+    const int oc = int((i / pq) % out_channels);
+    return bias_fp32 ? static_cast<const float*>(bias)[oc] : to_f32(static_cast<const T*>(bias)[oc]);
+  };
+  if (VEC) {
+    const int64_t nvec = total >> 2;
+    for (int64_t v = first; v < nvec; v += step) {
+      float4 acc = reinterpret_cast<const float4*>(partial)[v];
+      for (int z = 1; z < splits; ++z) {
+        const float4 q = reinterpret_cast<const float4*>(partial + z * slice_stride)[v];
+        acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+      }
+      const int64_t i = v << 2;
+      float r[4] = {acc.x + bias_of(i), acc.y + bias_of(i + 1), acc.z + bias_of(i + 2), acc.w + bias_of(i + 3)};
+      if (relu) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) r[j] = fmaxf(r[j], 0.f);
+      }
+      T o[4] = {from_f32<T>(r[0]), from_f32<T>(r[1]), from_f32<T>(r[2]), from_f32<T>(r[3])};
+      reinterpret_cast<uint2*>(y)[v] = *reinterpret_cast<const uint2*>(o);
+    }
+    for (int64_t i = (nvec << 2) + first; i < total; i += step) {
+      float acc = 0.f;
+      for (int z = 0; z < splits; ++z) acc += partial[z * slice_stride + i];
+      acc += bias_of(i);
+      if (relu) acc = fmaxf(acc, 0.f);
+      y[i] = from_f32<T>(acc);
+    }
+  } else {
+    for (int64_t i = first; i < total; i += step) {
+      float acc = 0.f;
+      for (int z = 0; z < splits; ++z) acc += partial[z * slice_stride + i];
+      acc += bias_of(i);
+      if (relu) acc = fmaxf(acc, 0.f);
+      y[i] = from_f32<T>(acc);
+    }
+  }
+}
+
+}  // namespace
+
+size_t conv_tc_smem_bytes(int tile_n, int tile_k, int stages) {
+  return 1024 + kCtrlBytes + size_t(stages) * (size_t(kTileM) + tile_n) * tile_k * 2;
+}
+
+cudaError_t conv_tc_prepare(int tile_n, int tile_k, size_t smem_bytes) {
+  GIEB_TC_DISPATCH(prepare_one, smem_bytes)
+}
+
+cudaError_t conv_tc_launch(int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
+                           const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream) {
+  GIEB_TC_DISPATCH(launch_one, tm_act, tm_wgt, p, grid, smem_bytes, stream)
+}
+
+cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total, int out_channels, int pq, const void* bias,
+                                 int bias_fp32, int relu, int is_bf16, void* y, cudaStream_t stream) {
+  const int64_t slice_stride = (total + 3) & ~int64_t(3);
+  const bool vec = (reinterpret_cast<uintptr_t>(y) & 7u) == 0;
+  const int64_t work = vec ? (total + 3) / 4 : total;
+  int64_t blocks = (work + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  if (is_bf16) {
+    auto* yy = static_cast<__nv_bfloat16*>(y);
+    if (vec) splitk_reduce_kernel<__nv_bfloat16, true><<<unsigned(blocks), 256, 0, stream>>>(partial, splits, total, slice_stride, out_channels, pq, bias, bias_fp32, relu, yy);
+    else splitk_reduce_kernel<__nv_bfloat16, false><<<unsigned(blocks), 256, 0, stream>>>(partial, splits, total, slice_stride, out_channels, pq, bias, bias_fp32, relu, yy);
+  } else {
+    auto* yy = static_cast<__half*>(y);
+    if (vec) splitk_reduce_kernel<__half, true><<<unsigned(blocks), 256, 0, stream>>>(partial, splits, total, slice_stride, out_channels, pq, bias, bias_fp32, relu, yy);
+    else splitk_reduce_kernel<__half, false><<<unsigned(blocks), 256, 0, stream>>>(partial, splits, total, slice_stride, out_channels, pq, bias, bias_fp32, relu, yy);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace gieb

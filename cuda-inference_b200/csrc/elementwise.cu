@@ -1,0 +1,144 @@
+// Elementwise operators around the convolution:
+//  * bias_act: in-place y = act(y + bias[channel]) on NCHW -- stands in for bias_act_kernel
+//    (src/kernels/elementwise.cu:13-23); the unfused comparator of the fusion tests.
+//  * maxpool2d and add(+ReLU): glue of the ResNet-50-shaped chain.  The reference library has no such operators;
+//    they follow the operator definitions (window maximum ignoring padding; float add, one rounding, optional ReLU).
+// 16-bit tensors use 128-bit accesses when pointers and sizes allow, scalar accesses otherwise.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "internal.h"
+
+namespace gieb {
+namespace {
+
+__device__ __forceinline__ float cvt(float v) { return v; }
+__device__ __forceinline__ float cvt(__half v) { return __half2float(v); }
+__device__ __forceinline__ float cvt(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T rnd(float v);
+template <> __device__ __forceinline__ float rnd<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half rnd<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 rnd<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_act_kernel(T* __restrict__ y, const T* __restrict__ bias, int64_t total, int channels, int hw, int relu) {
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+    float v = cvt(y[i]);
+    if (bias != nullptr) v += cvt(bias[(i / hw) % channels]);
+    if (relu) v = fmaxf(v, 0.f);
+    y[i] = rnd<T>(v);
+  }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+add_relu_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, int64_t n, int relu) {
+  constexpr int W = 16 / sizeof(T);
+  const int64_t step = int64_t(gridDim.x) * blockDim.x;
+  const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  int64_t done = 0;
+  if (VEC) {
+    const int64_t nvec = n / W;
+    for (int64_t v = first; v < nvec; v += step) {
+      const uint4 ra = reinterpret_cast<const uint4*>(a)[v], rb = reinterpret_cast<const uint4*>(b)[v];
+      T ta[W], tb[W];
+      memcpy(ta, &ra, 16);
+      memcpy(tb, &rb, 16);
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        T s = rnd<T>(cvt(ta[j]) + cvt(tb[j]));
+        if (relu && cvt(s) < 0.f) s = rnd<T>(0.f);
+        ta[j] = s;
+      }
+      uint4 o;
+      memcpy(&o, ta, 16);
+      reinterpret_cast<uint4*>(y)[v] = o;
+    }
+    done = nvec * W;
+  }
+  for (int64_t i = done + first; i < n; i += step) {
+    T s = rnd<T>(cvt(a[i]) + cvt(b[i]));
+    if (relu && cvt(s) < 0.f) s = rnd<T>(0.f);
+    y[i] = s;
+  }
+}
+
+// One thread per output element; consecutive threads walk ow, so window reads are coalesced along w.
+template <typename T>
+__global__ void __launch_bounds__(256)
+maxpool2d_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t total, int h, int w, int oh, int ow, int k, int stride,
+                 int pad) {
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+    const int ox = int(i % ow);
+    const int oy = int((i / ow) % oh);
+    const int64_t plane = i / (int64_t(ow) * oh);
+    const T* xp = x + plane * h * w;
+    float best = -INFINITY;
+    for (int r = 0; r < k; ++r) {
+      const int iy = oy * stride - pad + r;
+      if (iy < 0 || iy >= h) continue;
+      for (int s = 0; s < k; ++s) {
+        const int ix = ox * stride - pad + s;
+        if (ix < 0 || ix >= w) continue;
+        best = fmaxf(best, cvt(xp[iy * w + ix]));
+      }
+    }
+    y[i] = rnd<T>(best);
+  }
+}
+
+unsigned grid_for(int64_t work) {
+  int64_t b = (work + 255) / 256;
+  if (b > 148 * 32) b = 148 * 32;
+  return unsigned(b < 1 ? 1 : b);
+}
+
+}  // namespace
+
+cudaError_t bias_act_launch(int precision, int64_t total, int channels, int hw, const void* bias, int relu, void* y,
+                            cudaStream_t st) {
+  const unsigned g = grid_for(total);
+  switch (precision) {
+    case 0: bias_act_kernel<float><<<g, 256, 0, st>>>(static_cast<float*>(y), static_cast<const float*>(bias), total, channels, hw, relu); break;
+    case 1: bias_act_kernel<__half><<<g, 256, 0, st>>>(static_cast<__half*>(y), static_cast<const __half*>(bias), total, channels, hw, relu); break;
+    case 2: bias_act_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(bias), total, channels, hw, relu); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t add_relu_t(int relu, const void* a, const void* b, void* y, int64_t n, cudaStream_t st) {
+  const bool vec = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0;
+  const unsigned g = grid_for(vec ? n / (16 / sizeof(T)) + 1 : n);
+  if (vec) add_relu_kernel<T, true><<<g, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(y), n, relu);
+  else add_relu_kernel<T, false><<<g, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(y), n, relu);
+  return cudaGetLastError();
+}
+
+cudaError_t add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, cudaStream_t st) {
+  switch (precision) {
+    case 0: return add_relu_t<float>(relu, a, b, y, n, st);
+    case 1: return add_relu_t<__half>(relu, a, b, y, n, st);
+    case 2: return add_relu_t<__nv_bfloat16>(relu, a, b, y, n, st);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t maxpool2d_launch(int precision, int batch, int channels, int h, int w, int k, int stride, int pad, const void* x,
+                             void* y, cudaStream_t st) {
+  const int oh = (h + 2 * pad - k) / stride + 1, ow = (w + 2 * pad - k) / stride + 1;
+  const int64_t total = int64_t(batch) * channels * oh * ow;
+  const unsigned g = grid_for(total);
+  switch (precision) {
+    case 0: maxpool2d_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), total, h, w, oh, ow, k, stride, pad); break;
+    case 1: maxpool2d_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), total, h, w, oh, ow, k, stride, pad); break;
+    case 2: maxpool2d_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), total, h, w, oh, ow, k, stride, pad); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace gieb

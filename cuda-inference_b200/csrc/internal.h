@@ -1,0 +1,71 @@
+// Internal interfaces between the C ABI layer (api.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace gieb {
+
+// Device-status codes ORed into a plan's status word by a kernel that gave up on a bounded wait.
+enum : uint32_t {
+  kStatusProducerTimeout = 1u << 0,
+  kStatusMmaTimeout = 1u << 1,
+  kStatusEpilogueTimeout = 1u << 2,
+};
+
+constexpr int kTileM = 128;        // output pixels per CTA tile = TMEM lanes = UMMA M
+constexpr int kMaxStages = 8;
+constexpr int kTcThreads = 192;    // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2..5: epilogue
+
+// Everything the tensor-core kernel needs besides the two tensor maps.  Plain data, passed by value.
+struct ConvTcParams {
+  int m_total;        // B * P * Q output pixels (GEMM M)
+  int out_channels;   // O (GEMM N)
+  int out_h, out_w;   // P, Q
+  int pq;             // P * Q
+  int kernel_w;       // S (taps are enumerated r-major: tap = r * S + s)
+  int c_padded;       // channels of the NHWC copy / prepacked weights
+  int kb_per_tap;     // c_padded / BK
+  int total_kb;       // R * S * kb_per_tap reduction slabs
+  int kb_per_split;   // slabs per split-K slice
+  int stride_h, stride_w, pad_h, pad_w;
+  int stages;
+  int relu, has_bias, is_bf16, bias_fp32;
+  uint32_t idesc;
+  const void* bias;
+  void* y;            // NCHW output in the storage type (split_k == 1)
+  float* partial;     // [splits][B*O*P*Q] FP32 partial sums in NCHW order (split_k > 1), else null
+  uint32_t* status;
+};
+
+size_t conv_tc_smem_bytes(int tile_n, int tile_k, int stages);
+cudaError_t conv_tc_prepare(int tile_n, int tile_k, size_t smem_bytes);  // opt in to large dynamic shared memory
+cudaError_t conv_tc_launch(int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
+                           const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream);
+
+// Sum of split-K partials + bias + ReLU + one rounding; `total` = B*O*P*Q elements in NCHW order.
+cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total, int out_channels, int pq,
+                                 const void* bias, int bias_fp32, int relu, int is_bf16, void* y, cudaStream_t stream);
+
+// 16-bit [B][C][HW] -> [B][HW][Cp] (zero-filled channel padding).
+cudaError_t repack_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream);
+
+// FP32 SIMT implicit GEMM straight from NCHW.
+cudaError_t conv_fp32_launch(const void* x, const void* w, const void* bias, void* y, int batch, int c, int h, int wd,
+                             int o, int r, int s, int stride_h, int stride_w, int pad_h, int pad_w, int out_h, int out_w,
+                             int relu, cudaStream_t stream);
+int conv_fp32_tile(int64_t pixels, int o);          // 64 or 32: edge of the square output tile a CTA computes
+int64_t conv_fp32_num_blocks(int64_t pixels, int o);
+
+cudaError_t rmsnorm_launch(int rows, int hidden, float eps, int dtype, int gamma_fp32, const void* x, const void* gamma,
+                           void* y, const void* res_in, void* res_out, cudaStream_t stream);
+
+cudaError_t bias_act_launch(int precision, int64_t total, int channels, int hw, const void* bias, int relu, void* y,
+                            cudaStream_t stream);
+cudaError_t maxpool2d_launch(int precision, int batch, int channels, int h, int w, int k, int stride, int pad, const void* x,
+                             void* y, cudaStream_t stream);
+cudaError_t add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, cudaStream_t stream);
+
+}  // namespace gieb

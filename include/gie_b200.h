@@ -1,0 +1,170 @@
+/*
+ * gie_b200 -- C ABI of the B200 (sm_100a) implementation of the fused Conv2D / RMSNorm path.
+ *
+ * This is the drop-in boundary: plain pointers, fixed-width integers, integer status codes, no C++ types,
+ * no exceptions.  The C++ operator layer (gie::Conv2D, gie::ExecutionPlan, gie::rmsnorm_forward, ...) and any
+ * foreign-language binding sit on top of exactly these entry points.  Each entry point names the interface of
+ * the reference library (lehendo/cuda-inference, paths relative to its root) that it stands in for.
+ *
+ * Conventions
+ *  - Every function returns a gieb_status (numeric values of gie::StatusCode, include/gpu_inference/error.h:16-26);
+ *    on failure gieb_last_error() returns a thread-local message.  Nothing is launched when a call fails.
+ *  - Tensor pointers are DEVICE pointers owned by the caller: X contiguous NCHW, W contiguous OIHW, bias [O],
+ *    Y contiguous NCHW, all in the problem's storage type (include/gpu_inference/conv2d.h:1-7, 66-69).
+ *  - `stream` is a cudaStream_t passed as void*.  Launch functions never synchronise, never allocate and are safe
+ *    to call while the stream is being captured into a CUDA graph (include/gpu_inference/conv2d.h:100-104,
+ *    include/gpu_inference/cuda_graph.h:16).  Plan creation may allocate and synchronise a private stream.
+ *  - A plan is immutable after creation and may be used concurrently from many host threads and streams as long
+ *    as each concurrent launch has its own workspace (tests/test_runtime_concurrency.cu:110-188).
+ */
+#ifndef GIE_B200_H_
+#define GIE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define GIEB_API
+#else
+#define GIEB_API __attribute__((visibility("default")))
+#endif
+
+/* Numeric values of gie::StatusCode (include/gpu_inference/error.h:16-26). */
+typedef enum gieb_status {
+  GIEB_OK = 0,
+  GIEB_INVALID_ARGUMENT = 1,
+  GIEB_UNSUPPORTED = 2,
+  GIEB_WORKSPACE_TOO_SMALL = 3,
+  GIEB_CUDA_ERROR = 4,
+  GIEB_INTERNAL = 7
+} gieb_status;
+
+/* Order of gie::Precision (include/gpu_inference/conv2d.h:26). TF32 is accepted by the descriptor and answered
+ * with GIEB_UNSUPPORTED: the reference reaches it only through cuBLAS (src/kernels/im2col.cu:108-112). */
+typedef enum gieb_precision { GIEB_FP32 = 0, GIEB_FP16 = 1, GIEB_BF16 = 2, GIEB_TF32 = 3 } gieb_precision;
+
+/* Optional behaviour beyond the reference API (all off by default = exact drop-in behaviour). */
+enum {
+  GIEB_FLAG_BIAS_FP32 = 1u << 0,        /* bias is float[O] even for 16-bit storage                              */
+  GIEB_FLAG_WEIGHTS_PREPACKED = 1u << 1 /* `w` already holds gieb_prepack_weights output (static weights)       */
+};
+
+/* Conv2DParams + ConvProblem (include/gpu_inference/conv2d.h:47-85) as fixed-width fields. */
+typedef struct gieb_conv_desc {
+  int32_t batch, in_channels, in_h, in_w;
+  int32_t out_channels, kernel_h, kernel_w;
+  int32_t stride_h, stride_w, pad_h, pad_w;
+  int32_t dilation_h, dilation_w, groups;
+  int32_t precision; /* gieb_precision */
+  int32_t has_bias;
+  int32_t relu;      /* Activation::kReLU */
+  uint32_t flags;    /* GIEB_FLAG_* */
+} gieb_conv_desc;
+
+/* One point of the single sm_100a kernel family; replaces the reference's per-backend template parameter lists
+ * (src/kernels/tensor_core_mma.cu:369-388, src/kernels/implicit_gemm.cu:243-266).  Zero / NULL = heuristic. */
+typedef struct gieb_conv_cfg {
+  int32_t tile_n;   /* output channels per CTA tile: 32, 64, 128 or 256 (tensor path); 0 = auto              */
+  int32_t tile_k;   /* reduction slab in channels: 16, 32 or 64; 0 = auto                                    */
+  int32_t stages;   /* shared-memory ring depth, 2..8; 0 = auto                                              */
+  int32_t split_k;  /* number of reduction splits, >= 1; 0 = auto                                            */
+  int32_t variant;  /* 0 = auto, 1 = repack + im2col-TMA tensor path (16-bit), 3 = FP32 SIMT                   */
+  int32_t reserved[3];
+} gieb_conv_cfg;
+
+/* What KernelDesc::supports / workspace_bytes / dynamic_smem_bytes / num_blocks answer
+ * (include/gpu_inference/kernel_registry.h:62-70). */
+typedef struct gieb_conv_info {
+  int32_t supported;
+  int32_t variant;
+  gieb_conv_cfg cfg;          /* the configuration that would run (heuristic filled in)  */
+  uint64_t workspace_bytes;   /* caller-provided per-call scratch                          */
+  uint64_t persistent_bytes;  /* plan-owned device memory                                  */
+  uint32_t dynamic_smem_bytes;
+  uint32_t threads_per_block;
+  int64_t num_blocks;
+  int32_t launches;           /* kernel launches per forward call                          */
+  int32_t padded_channels;    /* C_in rounded up for the channel-contiguous copy           */
+  char reason[256];           /* why not, when supported == 0                              */
+} gieb_conv_info;
+
+typedef struct gieb_conv_plan gieb_conv_plan;
+
+/* Thread-local text of the last failure on this thread ("" if none). */
+GIEB_API const char* gieb_last_error(void);
+
+/* Library identity: kLibraryVersion analogue (include/gpu_inference/kernel_registry.h:24). */
+GIEB_API int gieb_version(void);
+
+/* validate_problem (src/runtime/conv2d.cpp:83-109): same checks, same status codes. */
+GIEB_API int gieb_conv_validate(const gieb_conv_desc* desc);
+
+/* KernelDesc::supports + workspace_bytes + dynamic_smem_bytes + num_blocks
+ * (include/gpu_inference/kernel_registry.h:62-70; src/kernels/tensor_core_mma.cu:280-295,326-330).
+ * device < 0 = current device.  Needs no GPU work. */
+GIEB_API int gieb_conv_query(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, int device, gieb_conv_info* out);
+
+/* ExecutionPlan::create (src/runtime/execution_plan.cpp:51-76): capability check, workspace size, plan-owned
+ * state (status word), kernel attributes.  May allocate and synchronise a private stream only. */
+GIEB_API int gieb_conv_plan_create(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, int device,
+                                   gieb_conv_plan** out);
+GIEB_API void gieb_conv_plan_destroy(gieb_conv_plan* plan);
+GIEB_API int gieb_conv_plan_info(const gieb_conv_plan* plan, gieb_conv_info* out);
+
+/* ExecutionPlan::execute_unchecked -> KernelDesc::launch (src/runtime/execution_plan.cpp:121-138;
+ * src/kernels/tensor_core_mma.cu:297-324): layout repack + weight prepack + implicit-GEMM (+ split-K reduce)
+ * on `stream`.  Checks only what it needs to stay memory-safe: non-null pointers, workspace size and 256-byte
+ * alignment (src/runtime/execution_plan.cpp:103-108), current device == plan device (:113-117). */
+GIEB_API int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device-side status word of the plan: 0 = no kernel of this plan ever gave up on a bounded wait.  Synchronises
+ * nothing itself; call after the stream has been synchronised.  (No reference counterpart: the reference's
+ * kernels have no asynchronous waits.) */
+GIEB_API int gieb_conv_plan_device_status(const gieb_conv_plan* plan, uint32_t* status_out);
+
+/* transpose_c_hw as used for X (src/kernels/tensor_core_mma.cu:61-82,309): 16-bit [B][C][HW] -> [B][HW][Cp],
+ * Cp = c_padded >= C (extra channels zero).  Bit-exact permutation.  `src` needs only 2-byte alignment,
+ * `dst` 16-byte alignment and c_padded % 8 == 0. */
+GIEB_API int gieb_repack_nchw_to_nhwc(const void* src, void* dst, int batch, int channels, int hw, int c_padded,
+                                      void* stream);
+
+/* transpose_c_hw as used for W (src/kernels/tensor_core_mma.cu:310): 16-bit OIHW [O][C][RS] -> [O][RS][Cp]. */
+GIEB_API int gieb_prepack_weights(const void* src, void* dst, int out_channels, int channels, int rs, int c_padded,
+                                  void* stream);
+
+/* Channel count of the channel-contiguous copy the tensor path would use for this problem and configuration. */
+GIEB_API int gieb_padded_channels(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg);
+
+/* RmsNormParams (include/gpu_inference/rmsnorm.h:17-22). dtype: 0 = FP32, 1 = FP16, 2 = BF16 (gie::DataType). */
+typedef struct gieb_rmsnorm_desc {
+  int32_t rows, hidden;
+  float eps;
+  int32_t dtype;
+  uint32_t flags;  /* bit 0: gamma is float[hidden] even for 16-bit storage */
+} gieb_rmsnorm_desc;
+
+/* rmsnorm_forward (src/transformer/rmsnorm.cu:155-166): y = rmsnorm(x)*gamma, or with both residual pointers
+ * res_out = round(x + res_in), y = rmsnorm(res_out)*gamma.  Same argument checks and status codes. */
+GIEB_API int gieb_rmsnorm_launch(const gieb_rmsnorm_desc* desc, const void* x, const void* gamma, void* y,
+                                 const void* residual_in, void* residual_out, void* stream);
+
+/* launch_bias_act (include/gpu_inference/fused_ops.h:13-19; src/kernels/elementwise.cu:13-55): in-place
+ * y = act(y + bias[channel]) on an NCHW tensor; bias may be NULL, relu may be 0. */
+GIEB_API int gieb_bias_act_launch(int precision, int batch, int channels, int hw, const void* bias, int relu, void* y,
+                                  void* stream);
+
+/* Glue of the ResNet-50-shaped chain; the reference has neither operator (its chain benchmark is conv-only,
+ * benchmarks/graph_bench.cpp:84-91).  16-bit NCHW tensors. */
+GIEB_API int gieb_maxpool2d_launch(int precision, int batch, int channels, int h, int w, int kernel, int stride, int pad,
+                                   const void* x, void* y, void* stream);
+GIEB_API int gieb_add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GIE_B200_H_ */

@@ -1,0 +1,247 @@
+"""GPU parity tests of the convolution path, through the C ABI, against the CPU oracle on identical seeded inputs.
+
+Mirrors the reference's tests/test_tensor_core.cpp, test_implicit_gemm.cpp, test_fusion.cpp and the run_suite protocol
+(tests/conv_test_common.h:84-127): the 26 correctness shapes x precisions x cycling epilogue mode x four data
+distributions, output poisoned with NaN bytes first, reference tolerance policy (no element over tolerance)."""
+import numpy as np
+import pytest
+
+import gpu_util as gu
+
+pytestmark = pytest.mark.gpu
+
+
+def _tolfn(o, p):
+    t = o.tolerance(p)
+    k = float(t.k)
+    return lambda ref, scale: (t.c_acc * t.u_acc * np.sqrt(k) * scale + t.c_out * t.u_out * np.abs(ref) + t.abs_floor)
+
+
+def _check(o, p, got, ref, scale, what):
+    m = o.compare(p, got, ref, scale)
+    assert m.passed(), f"{what}: {m.summary()}\n" + gu.describe_mismatch(p, got, ref, scale, _tolfn(o, p))
+    return m
+
+
+def _suite_cases(orc):
+    cases = []
+    cell = 0
+    for name, args in orc.CORRECTNESS_SHAPES.items():
+        for prec in (orc.FP32, orc.FP16, orc.BF16):
+            mode = cell % 3
+            cell += 1
+            cases.append((name, args, prec, mode, cell % 4, 0xC0FFEE + cell))
+    return cases
+
+
+@pytest.mark.parametrize("prec_name", ["fp32", "fp16", "bf16"])
+def test_correctness_shape_suite(pkg, orc, oracle, prec_name):
+    prec = {"fp32": orc.FP32, "fp16": orc.FP16, "bf16": orc.BF16}[prec_name]
+    ran = 0
+    for name, args, pr, mode, dist, seed in _suite_cases(orc):
+        if pr != prec:
+            continue
+        p = orc.Problem.P(*args, precision=pr, bias=mode >= 1, relu=mode == 2)
+        x, w, b = oracle.make_conv_data(p, seed, dist)
+        ref, scale = oracle.conv2d(p, x, w, b if p.has_bias else None)
+        got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b if p.has_bias else None)
+        _check(oracle, p, got, ref, scale, f"{name} {prec_name} mode={mode} dist={dist} cfg=({plan.info.cfg.tile_n},"
+                                           f"{plan.info.cfg.tile_k},{plan.info.cfg.stages},{plan.info.cfg.split_k})")
+        ran += 1
+    assert ran == len(orc.CORRECTNESS_SHAPES)
+
+
+TILE_CASES = [
+    # (shape args, cfg kwargs)
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_n=32, tile_k=16, stages=2)),
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_n=64, tile_k=32, stages=3)),
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_n=64, tile_k=64, stages=4, split_k=3)),
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=8, split_k=2)),
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=32, stages=2)),
+    ((2, 130, 9, 9, 130, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=16, stages=5, split_k=4)),
+    ((2, 130, 9, 9, 130, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=64, stages=3)),
+    ((1, 512, 7, 7, 512, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=6, split_k=8)),
+    ((1, 512, 7, 7, 512, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=64, stages=4, split_k=16)),
+    ((2, 64, 28, 28, 128, 3, 3, 2, 2, 1, 1), dict(tile_n=128, tile_k=64, stages=4)),
+    ((2, 8, 17, 23, 12, 3, 5, 2, 1, 1, 2), dict(tile_n=32, tile_k=16, stages=3, split_k=5)),
+    ((4, 96, 27, 27, 192, 5, 5, 1, 1, 2, 2), dict(tile_n=64, tile_k=32, stages=8, split_k=2)),
+]
+
+
+@pytest.mark.parametrize("case", range(len(TILE_CASES)))
+@pytest.mark.parametrize("prec_name", ["fp16", "bf16"])
+def test_explicit_tile_configurations(pkg, orc, oracle, case, prec_name):
+    """Every tile/stage/split-K point of the kernel family must give the same answer (tcmma config sweep analogue,
+    tests/test_tensor_core.cpp:72-98)."""
+    args, kw = TILE_CASES[case]
+    prec = orc.FP16 if prec_name == "fp16" else orc.BF16
+    p = orc.Problem.P(*args, precision=prec, bias=True, relu=(case % 2 == 0))
+    x, w, b = oracle.make_conv_data(p, 1000 + case, case % 4)
+    ref, scale = oracle.conv2d(p, x, w, b)
+    cfg = pkg.make_cfg(**kw)
+    got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b, cfg=cfg)
+    for k, v in kw.items():
+        assert getattr(plan.info.cfg, k) == v or k == "split_k"
+    _check(oracle, p, got, ref, scale, f"case {case} {kw} {prec_name}")
+
+
+def test_baseline_configurations_full_size(pkg, orc, oracle):
+    """The benchmark shapes at full size with the benchmark distributions, checked with BOTH tolerances: the
+    reference's scale-aware policy and the benchmark's |err| <= a + b*|ref| bounds."""
+    bounds = {orc.FP16: (5e-3, 1e-2), orc.BF16: (2e-2, 3e-2)}
+    for name, p in orc.BASELINE_CONFIGS.items():
+        x, w, b = oracle.make_baseline_data(p, 0)
+        ref, scale = oracle.conv2d(p, x, w, b)
+        got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b)
+        _check(oracle, p, got, ref, scale, name)
+        err = np.abs(got.astype(np.float64) - ref)
+        if p.precision == orc.FP32:
+            nz = np.abs(ref) > 1e-6
+            rel = err[nz] / np.abs(ref[nz])
+            # relative error <= 1e-5 wherever the reference is not a cancellation residue
+            big = np.abs(ref) > 1e-3 * np.sqrt(np.mean(ref.astype(np.float64) ** 2))
+            assert np.all(err[big] / np.abs(ref[big]) <= 1e-5), f"{name}: fp32 relative error {rel.max():.3e}"
+        else:
+            a, r = bounds[p.precision]
+            assert np.all(err <= a + r * np.abs(ref)), f"{name}: max err {err.max():.3e}"
+
+
+def test_fp32_bias_option_matches_storage_bias(pkg, orc, oracle):
+    """GIEB_FLAG_BIAS_FP32: an FP32 bias vector holding the storage-rounded values gives bit-identical output."""
+    p = orc.Problem.P(4, 32, 12, 12, 48, 3, 3, 1, 1, 1, 1, orc.FP16, True, True)
+    x, w, b = oracle.make_conv_data(p, 77)
+    y0, _, o0 = gu.run_conv(pkg, oracle, p, x, w, b)
+    y1, _, o1 = gu.run_conv(pkg, oracle, p, x, w, b, flags=pkg.FLAG_BIAS_FP32)
+    assert np.array_equal(o0.raw_bits(), o1.raw_bits())
+
+
+def test_prepacked_weights_option(pkg, orc, oracle):
+    """GIEB_FLAG_WEIGHTS_PREPACKED: prepacking once with gieb_prepack_weights gives bit-identical output."""
+    import torch
+    p = orc.Problem.P(4, 24, 12, 12, 40, 3, 3, 1, 1, 1, 1, orc.BF16, True, False)
+    x, w, b = oracle.make_conv_data(p, 78)
+    y0, plan0, o0 = gu.run_conv(pkg, oracle, p, x, w, b)
+    cp = gu.pkg_problem(pkg, p, pkg.FLAG_WEIGHTS_PREPACKED)
+    plan = pkg.ConvPlan(cp)
+    cpad = plan.info.padded_channels
+    assert plan.workspace_bytes < plan0.workspace_bytes
+    tw, pw = gu.to_device_storage(oracle, p.precision, w)
+    wk = torch.empty(p.out_channels * 9 * cpad, dtype=torch.int16, device="cuda")
+    pkg.prepack_weights(pw, wk.data_ptr(), p.out_channels, p.in_channels, 9, cpad, torch.cuda.current_stream().cuda_stream)
+    tx, px = gu.to_device_storage(oracle, p.precision, x)
+    tb, pb = gu.to_device_storage(oracle, p.precision, b)
+    out = gu.OutBuf(p.precision, int(np.prod(p.y_shape)))
+    ws = gu.Workspace(plan.workspace_bytes)
+    plan.launch(px, wk.data_ptr(), pb, out.ptr, ws.ptr, plan.workspace_bytes, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.raw_bits(), o0.raw_bits())
+
+
+def test_misaligned_tensor_pointers(pkg, orc, oracle):
+    """X, W and Y offset by one element (2 bytes) must work (tests/test_tensor_core.cpp:38-57,
+    tests/test_runtime_concurrency.cu:190-216)."""
+    for prec in (orc.FP16, orc.BF16, orc.FP32):
+        p = orc.Problem.P(2, 16, 9, 11, 24, 3, 3, 1, 1, 1, 1, prec, True, True)
+        x, w, b = oracle.make_conv_data(p, 5)
+        ref, scale = oracle.conv2d(p, x, w, b)
+        got, _, _ = gu.run_conv(pkg, oracle, p, x, w, b, offsets=(1, 1, 1))
+        _check(oracle, p, got, ref, scale, f"misaligned prec={prec}")
+
+
+def test_relu_gives_exact_zeros_and_runs_are_deterministic(pkg, orc, oracle):
+    """ReLU outputs are exactly zero where the reference is zero-clamped well below zero (tests/test_fusion.cpp:15-30);
+    two launches give identical bits."""
+    p = orc.Problem.P(2, 32, 10, 10, 32, 3, 3, 1, 1, 1, 1, orc.FP16, True, True)
+    x, w, b = oracle.make_conv_data(p, 9, orc.DIST_NORMAL)
+    p_lin = orc.Problem.P(2, 32, 10, 10, 32, 3, 3, 1, 1, 1, 1, orc.FP16, True, False)
+    lin, _ = oracle.conv2d(p_lin, x, w, b)
+    y0, plan, o0 = gu.run_conv(pkg, oracle, p, x, w, b)
+    y1, _, o1 = gu.run_conv(pkg, oracle, p, x, w, b, plan=plan)
+    assert np.array_equal(o0.raw_bits(), o1.raw_bits())
+    assert np.all(y0[lin < -1e-2] == 0.0)
+    assert np.all(y0 >= 0.0)
+
+
+def test_launch_argument_checks(pkg, orc, oracle):
+    """Status codes of the launch-time checks (tests/test_validation.cpp:23-95 subset that lives below the C ABI)."""
+    import torch
+    p = orc.Problem.P(2, 8, 10, 10, 8, 3, 3, 1, 1, 1, 1, orc.FP16, True, False)
+    plan = pkg.ConvPlan(gu.pkg_problem(pkg, p))
+    assert plan.workspace_bytes > 0
+    buf = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    base = (buf.data_ptr() + 255) // 256 * 256
+    st = torch.cuda.current_stream().cuda_stream
+    with pytest.raises(pkg.GieError) as e:
+        plan.launch(None, base, base, base, base, plan.workspace_bytes, st)
+    assert e.value.code == pkg.INVALID_ARGUMENT
+    with pytest.raises(pkg.GieError) as e:
+        plan.launch(base, base, None, base, base, plan.workspace_bytes, st)
+    assert e.value.code == pkg.INVALID_ARGUMENT
+    with pytest.raises(pkg.GieError) as e:
+        plan.launch(base, base, base, base, None, 0, st)
+    assert e.value.code == pkg.WORKSPACE_TOO_SMALL
+    with pytest.raises(pkg.GieError) as e:
+        plan.launch(base, base, base, base, base, plan.workspace_bytes - 1, st)
+    assert e.value.code == pkg.WORKSPACE_TOO_SMALL
+    with pytest.raises(pkg.GieError) as e:
+        plan.launch(base, base, base, base, base + 16, plan.workspace_bytes, st)
+    assert e.value.code == pkg.INVALID_ARGUMENT
+    torch.cuda.synchronize()
+
+
+def test_cuda_graph_capture_matches_eager(pkg, orc, oracle):
+    """A captured launch replays bit-identically, also after the inputs change (tests/test_cuda_graph.cu:42-70)."""
+    import torch
+    p = orc.Problem.P(4, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, orc.FP16, True, True)
+    plan = pkg.ConvPlan(gu.pkg_problem(pkg, p))
+    x, w, b = oracle.make_conv_data(p, 21)
+    tx, px = gu.to_device_storage(oracle, p.precision, x)
+    tw, pw = gu.to_device_storage(oracle, p.precision, w)
+    tb, pb = gu.to_device_storage(oracle, p.precision, b)
+    out = gu.OutBuf(p.precision, int(np.prod(p.y_shape)))
+    ws = gu.Workspace(plan.workspace_bytes)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        plan.launch(px, pw, pb, out.ptr, ws.ptr, plan.workspace_bytes, s.cuda_stream)  # warm-up outside capture
+        s.synchronize()
+        eager = out.raw_bits()
+        out.t.view(torch.uint8).fill_(0xFF)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            plan.launch(px, pw, pb, out.ptr, ws.ptr, plan.workspace_bytes, torch.cuda.current_stream().cuda_stream)
+        g.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(out.raw_bits(), eager)
+        # new inputs in the same buffers
+        x2, w2, b2 = oracle.make_conv_data(p, 22)
+        raw = oracle.to_storage(p.precision, x2.ravel()).view(np.int16)
+        tx[:raw.size] = torch.from_numpy(raw).cuda()
+        raw = oracle.to_storage(p.precision, w2.ravel()).view(np.int16)
+        tw[:raw.size] = torch.from_numpy(raw).cuda()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+    ref, scale = oracle.conv2d(p, x2, w2, b)
+    got = oracle.from_bits16(p.precision, out.raw_bits().view(np.uint16)).reshape(p.y_shape)
+    _check(oracle, p, got, ref, scale, "graph replay with new inputs")
+
+
+def test_repack_is_bit_exact(pkg, orc, oracle):
+    """NCHW -> channel-padded NHWC and OIHW -> [O][RS][Cp] are pure permutations of 16-bit patterns (NaNs included)."""
+    import torch
+    rng = np.random.default_rng(3)
+    st = torch.cuda.current_stream().cuda_stream
+    for (bt, c, hw, cp, off) in [(2, 64, 196, 64, 0), (3, 5, 49, 16, 1), (1, 130, 81, 160, 0), (2, 3, 4096, 16, 0), (4, 256, 784, 256, 0),
+                                 (256, 256, 9, 256, 0), (64, 3, 49, 16, 1), (5, 17, 33, 32, 3), (1, 8, 1, 8, 0), (7, 70, 25, 128, 0),
+                                 (2, 64, 200, 64, 4)]:
+        src = rng.integers(0, 65536, size=bt * c * hw, dtype=np.uint16)
+        t = torch.empty(src.size + off + 8, dtype=torch.int16, device="cuda")
+        t[off:off + src.size] = torch.from_numpy(src.view(np.int16)).cuda()
+        dst = torch.full((bt * hw * cp + 64,), -1, dtype=torch.int16, device="cuda")
+        pkg.repack_nchw_to_nhwc(t.data_ptr() + 2 * off, dst.data_ptr(), bt, c, hw, cp, st)
+        torch.cuda.synchronize()
+        got = dst.cpu().numpy().view(np.uint16)
+        exp = np.zeros((bt, hw, cp), np.uint16)
+        exp[:, :, :c] = src.reshape(bt, c, hw).transpose(0, 2, 1)
+        assert np.array_equal(got[:exp.size].reshape(exp.shape), exp), (bt, c, hw, cp, off)
+        assert np.all(got[exp.size:] == 0xFFFF)
