@@ -1,0 +1,407 @@
+#!/usr/bin/env python
+"""Benchmark of the fused Conv2D path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
+
+A *step* is one forward pass of the hot path over one batch of synthetic input: layout repack + weight prepack +
+tensor-core convolution with fused bias + ReLU (exactly what one gie::Conv2D::forward call does).  The default
+workload is the FP16 3x3 convolution the headline metric is quoted on (N=32, C=256, 14x14, K=256).  With N GPUs every
+rank runs the same work on its own replica (weak scaling, no collective on the data path); the reported value is the
+whole-job TFLOP/s = N * K * FLOPs / max-over-ranks device time.  One JSON line is printed by rank 0.
+
+`--impl reference` times the reference library's own CPU convolution (oracle/_ref, or the C restatement when the
+reference could not be compiled) on the host cores for the same metric; that is the only place besides the
+`cpu_baseline` leg where anything under oracle/ is executed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
+# under profiles/ (None where no capture exists yet).
+NCU_TRAFFIC_BYTES = {}
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"]))}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[index]) if vis and all(t.strip().isdigit() for t in vis.split(",")) else index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        if self._thr is not None:
+            self._stop.set()
+            self._thr.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------------------
+def make_conv_sets(torch, pkg, shape, nsets, seed):
+    """Device-resident synthetic inputs with the benchmark's distributions: x ~ U[-1,1], w ~ Kaiming-uniform
+    (bound sqrt(6/fan_in)), bias ~ U[-0.1,0.1], seeded.  `nsets` independent buffer sets so that consecutive steps
+    touch different memory (the rotation is larger than L2)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    dt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[shape.precision]
+    fan_in = shape.in_channels * shape.kernel * shape.kernel
+    bound = (6.0 / fan_in) ** 0.5
+    sets = []
+    for _ in range(nsets):
+        x = (torch.rand(shape.x_elems, device="cuda", generator=g) * 2 - 1).to(dt)
+        w = ((torch.rand(shape.w_elems, device="cuda", generator=g) * 2 - 1) * bound).to(dt)
+        b = ((torch.rand(shape.out_channels, device="cuda", generator=g) * 2 - 1) * 0.1).to(dt)
+        y = torch.empty(shape.y_elems, device="cuda", dtype=dt)
+        sets.append((x, w, b, y))
+    return sets
+
+
+def conv_problem(pkg, shape, flags=0):
+    return pkg.ConvProblem(shape.batch, shape.in_channels, shape.in_h, shape.in_w, shape.out_channels, shape.kernel,
+                           shape.kernel, shape.stride, shape.stride, shape.pad, shape.pad, 1, 1, 1, shape.precision, True, True,
+                           flags)
+
+
+def aligned_ws(torch, nbytes):
+    t = torch.empty(max(int(nbytes), 256) + 256, dtype=torch.uint8, device="cuda")
+    return t, (t.data_ptr() + 255) // 256 * 256
+
+
+def time_conv(torch, pkg, shape, steps, warmup, world, barrier, max_over_ranks, cfg=None):
+    """Times exactly `steps` forward calls on rotating buffer sets; replays a CUDA graph of one rotation so the host
+    does not bound the measurement.  Returns a dict of raw measurements."""
+    plan = pkg.ConvPlan(conv_problem(pkg, shape), cfg)
+    per_set = (shape.x_elems + shape.w_elems + shape.y_elems) * shape.elem_size + plan.workspace_bytes
+    nsets = max(2, min(64, int(160e6 // per_set) + 1))      # rotation > 126 MB of L2
+    sets = make_conv_sets(torch, pkg, shape, nsets, seed=1234)
+    wss = [aligned_ws(torch, plan.workspace_bytes) for _ in range(nsets)]
+    stream = torch.cuda.Stream()
+
+    def launch(i, st):
+        x, w, b, y = sets[i % nsets]
+        plan.launch(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), wss[i % nsets][1], plan.workspace_bytes, st)
+
+    with torch.cuda.stream(stream):
+        for i in range(min(warmup, nsets)):
+            launch(i, stream.cuda_stream)
+        stream.synchronize()
+        group = min(nsets, steps)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(group):
+                launch(i, torch.cuda.current_stream().cuda_stream)
+        for _ in range(max(0, (warmup - min(warmup, nsets) + group - 1) // group)):
+            graph.replay()
+        stream.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        torch.cuda.synchronize()
+        start.record(stream)
+        for _ in range(steps // group):
+            graph.replay()
+        for i in range(steps % group):
+            launch(i, stream.cuda_stream)
+        end.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        ms = max_over_ranks(start.elapsed_time(end))
+        # per-stage device time (CUDA events between the stages, on the launching stream)
+        x, w, b, y = sets[0]
+        stage_ms = plan.time_stages(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), wss[0][1], plan.workspace_bytes,
+                                    stream.cuda_stream, iters=min(200, max(20, steps)))
+    assert plan.device_status() == 0, "a bounded device-side wait expired during the benchmark"
+    return dict(plan=plan, ms=ms, stage_ms=stage_ms, nsets=nsets, sets=sets, wss=wss, launches=steps * plan.info.launches,
+                rotation_bytes=per_set * nsets)
+
+
+def time_conv_e2e(torch, pkg, shape, plan, steps):
+    """Same metric end to end through the public call with HOST buffers: every step copies x, w and bias from pinned
+    host memory, runs the forward call, and copies y back."""
+    import numpy as np
+    rng = np.random.default_rng(7)
+    npdt = np.float32 if shape.precision == 0 else np.float16
+    tdt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[shape.precision]
+    fan_in = shape.in_channels * shape.kernel * shape.kernel
+    hx = torch.from_numpy(rng.uniform(-1, 1, shape.x_elems).astype(npdt)).to(tdt).pin_memory()
+    hw = torch.from_numpy((rng.uniform(-1, 1, shape.w_elems) * (6.0 / fan_in) ** 0.5).astype(npdt)).to(tdt).pin_memory()
+    hb = torch.from_numpy(rng.uniform(-0.1, 0.1, shape.out_channels).astype(npdt)).to(tdt).pin_memory()
+    hy = torch.empty(shape.y_elems, dtype=tdt).pin_memory()
+    dx, dw, db = (torch.empty_like(t, device="cuda") for t in (hx, hw, hb))
+    dy = torch.empty(shape.y_elems, dtype=tdt, device="cuda")
+    wst, wsp = aligned_ws(torch, plan.workspace_bytes)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        def step():
+            dx.copy_(hx, non_blocking=True)
+            dw.copy_(hw, non_blocking=True)
+            db.copy_(hb, non_blocking=True)
+            plan.launch(dx.data_ptr(), dw.data_ptr(), db.data_ptr(), dy.data_ptr(), wsp, plan.workspace_bytes, stream.cuda_stream)
+            hy.copy_(dy, non_blocking=True)
+        for _ in range(3):
+            step()
+        stream.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(stream)
+        for _ in range(steps):
+            step()
+        e.record(stream)
+        torch.cuda.synchronize()
+    ms = s.elapsed_time(e)
+    h2d = (shape.x_elems + shape.w_elems + shape.out_channels) * shape.elem_size
+    d2h = shape.y_elems * shape.elem_size
+    return ms, h2d, d2h, (hx, hw, hb, hy)
+
+
+def cpu_reference_runner():
+    """Returns (callable(problem_args, x, w, b) -> y, kind, threads) for the CPU baseline: the reference's own CPU code
+    when oracle/_ref exists, else the C restatement."""
+    orc = entry.load_oracle()
+    o = orc.Oracle()
+    threads = o.num_threads()
+    if orc.Reference.available():
+        r = orc.Reference()
+        return orc, o, (lambda p, x, w, b: r.conv2d(p, x, w, b)[0]), "reference", threads
+    return orc, o, (lambda p, x, w, b: o.conv2d(p, x, w, b, want_scale=False)[0]), "port", threads
+
+
+def cpu_baseline_leg(torch, shape, host_inputs, gpu_y, budget_s=12.0):
+    """Times the CPU convolution on a bounded sample (whole images of the workload) and checks the GPU result for
+    those images against it.  host_inputs = (x, w, b) torch host tensors in the storage type."""
+    import numpy as np
+    orc, o, conv, kind, threads = cpu_reference_runner()
+    hx, hw, hb = (t.float().numpy() for t in host_inputs)
+    per_img = shape.in_channels * shape.in_h * shape.in_w
+    n_img, reps, elapsed = 1, 0, 0.0
+    check = None
+    t_first = None
+    while True:
+        p = orc.Problem.P(n_img, shape.in_channels, shape.in_h, shape.in_w, shape.out_channels, shape.kernel, shape.kernel,
+                          shape.stride, shape.stride, shape.pad, shape.pad, shape.precision, True, True)
+        t0 = time.perf_counter()
+        y = conv(p, hx[:n_img * per_img].reshape(p.x_shape), hw.reshape(p.w_shape), hb)
+        dt = time.perf_counter() - t0
+        if t_first is None:  # first call sizes the sample: as many images as fit ~1/3 of the budget per repetition
+            t_first = dt
+            if gpu_y is not None:
+                got = gpu_y.float().numpy()[:y.size].reshape(y.shape)
+                err = np.abs(got - y)
+                tol = (5e-3 + 1e-2 * np.abs(y)) if shape.precision == 1 else ((2e-2 + 3e-2 * np.abs(y)) if shape.precision == 2
+                                                                             else 1e-5 * np.maximum(np.abs(y), np.sqrt(np.mean(y * y))))
+                check = bool(np.all(err <= tol))
+            n_img = int(max(1, min(shape.batch, (budget_s / 3) // max(dt, 1e-6))))
+            continue
+        reps += 1
+        elapsed += dt
+        if elapsed >= budget_s or reps >= 50:
+            break
+    flops = 2 * n_img * shape.out_h * shape.out_w * shape.out_channels * shape.in_channels * shape.kernel * shape.kernel
+    return {"value": flops * reps / elapsed / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+            "sample": f"{n_img} of {shape.batch} images of the workload, all output channels, {reps} repetitions, {elapsed:.1f} s",
+            "gpu_matches_cpu_on_sample": check}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank, local_rank, world = dist_env()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return float(v)
+        t = torch.tensor([float(v)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    pkg = entry.load_package()
+    from cuda_inference_b200 import workloads as wl
+    peaks, peak_kind = load_peaks()
+    shape, bound = wl.CONV_WORKLOADS[args.workload]
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    res = time_conv(torch, pkg, shape, args.steps, args.warmup, world, barrier, max_over_ranks)
+    clocks = sampler.stop()
+    plan = res["plan"]
+    ms = res["ms"]
+    value = world * args.steps * shape.flops / (ms * 1e-3) / 1e12
+
+    conv_ms = res["stage_ms"][1]
+    if bound == "hbm":
+        achieved = shape.algorithmic_bytes / (conv_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"]}
+    else:
+        achieved = shape.flops / (conv_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["bf16_tflops"]}
+    roof.update({"traffic": NCU_TRAFFIC_BYTES.get(args.workload), "kernel": "conv_tc_kernel" if shape.precision else "conv_fp32_kernel",
+                 "kernel_us": conv_ms * 1e3, "repack_us": res["stage_ms"][0] * 1e3, "splitk_reduce_us": res["stage_ms"][2] * 1e3,
+                 "peak_source": f"{peak_kind} (cuBLAS bf16 burst / STREAM copy)",
+                 "algorithmic_per_launch": shape.flops if bound != "hbm" else shape.algorithmic_bytes})
+
+    e2e_steps = min(args.steps, 1000)
+    e2e_ms, h2d, d2h, host = time_conv_e2e(torch, pkg, shape, plan, e2e_steps)
+    e2e_ms = max_over_ranks(e2e_ms)
+    e2e = {"value": world * e2e_steps * shape.flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+
+    out = {
+        "metric": "FP16 conv TFLOP/s (effective, 2*N*K*P*Q*C*R*S / time, repack + prepack + conv per step)",
+        "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": {0: "fp32", 1: "fp16", 2: "bf16"}[shape.precision] + " (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: N={shape.batch} C={shape.in_channels} {shape.in_h}x{shape.in_w} K={shape.out_channels} "
+                               f"{shape.kernel}x{shape.kernel}/s{shape.stride} p{shape.pad} NCHW, fused bias+ReLU",
+                   "tile": {"tile_n": plan.info.cfg.tile_n, "tile_k": plan.info.cfg.tile_k, "stages": plan.info.cfg.stages,
+                            "split_k": plan.info.cfg.split_k},
+                   "cold_cache": f"inputs larger than L2: {res['nsets']} rotating buffer sets, {res['rotation_bytes'] / 1e6:.0f} MB",
+                   "launch": "CUDA graph of one buffer rotation, replayed", "replicas": world},
+        "roofline": roof, "e2e": e2e, "gpu_launches": res["launches"], "clocks": clocks,
+    }
+    if world == 1 and rank == 0 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_baseline_leg(torch, shape, host[:3], host[3])
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU convolution on the host cores
+# ------------------------------------------------------------------------------------------------------------------
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    import numpy as np
+    entry.load_package()
+    from cuda_inference_b200 import workloads as wl
+    shape, _ = wl.CONV_WORKLOADS[args.workload]
+    orc, o, conv, kind, threads = cpu_reference_runner()
+    full = orc.Problem.P(shape.batch, shape.in_channels, shape.in_h, shape.in_w, shape.out_channels, shape.kernel, shape.kernel,
+                         shape.stride, shape.stride, shape.pad, shape.pad, shape.precision, True, True)
+    x, w, b = o.make_baseline_data(full, 0)
+
+    def problem(n_img, n_out):
+        return orc.Problem.P(n_img, shape.in_channels, shape.in_h, shape.in_w, n_out, shape.kernel, shape.kernel, shape.stride,
+                             shape.stride, shape.pad, shape.pad, shape.precision, True, True)
+
+    # size the per-step sample so that steps + warmup end within ~2 minutes
+    t0 = time.perf_counter()
+    conv(problem(1, shape.out_channels), x[:1], w, b)
+    t_img = time.perf_counter() - t0
+    budget = 110.0 / max(1, args.steps + args.warmup)
+    n_img, n_out = 1, shape.out_channels
+    if t_img <= budget:
+        n_img = int(min(shape.batch, max(1, budget // t_img)))
+    else:
+        n_out = int(max(1, min(shape.out_channels, shape.out_channels * budget / t_img)))
+    p = problem(n_img, n_out)
+    xs, ws, bs = x[:n_img], w[:n_out], b[:n_out]
+    for _ in range(args.warmup):
+        conv(p, xs, ws, bs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        conv(p, xs, ws, bs)
+    el = time.perf_counter() - t0
+    value = p.flops * args.steps / el / 1e12
+    sample = f"{n_img} of {shape.batch} images x {n_out} of {shape.out_channels} output channels per step"
+    print(json.dumps({
+        "impl": "reference", "metric": "FP16 conv TFLOP/s (effective, 2*N*K*P*Q*C*R*S / time)", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": el * 1e3 / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f64 accumulate over storage-rounded inputs", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: N={shape.batch} C={shape.in_channels} {shape.in_h}x{shape.in_w} K={shape.out_channels} "
+                               f"{shape.kernel}x{shape.kernel}/s{shape.stride} p{shape.pad} NCHW, fused bias+ReLU", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20000)
+    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

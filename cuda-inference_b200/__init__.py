@@ -74,6 +74,7 @@ def lib() -> C.CDLL:
         L.gieb_conv_plan_destroy.restype = None
         L.gieb_conv_plan_info.argtypes = [vp, C.POINTER(ConvInfo)]
         L.gieb_conv_launch.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp]
+        L.gieb_conv_time_stages.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp, i32, C.POINTER(C.c_float)]
         L.gieb_conv_plan_device_status.argtypes = [vp, C.POINTER(C.c_uint32)]
         L.gieb_repack_nchw_to_nhwc.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.gieb_prepack_weights.argtypes = [vp, vp, i32, i32, i32, i32, vp]
@@ -168,6 +169,12 @@ class ConvPlan:
     def launch(self, x: int, w: int, bias: int | None, y: int, workspace: int | None, workspace_bytes: int, stream: int = 0) -> None:
         """execute_unchecked: raw device pointers, asynchronous on `stream`."""
         check(lib().gieb_conv_launch(self._h, x, w, bias, y, workspace, workspace_bytes, stream))
+
+    def time_stages(self, x, w, bias, y, workspace, workspace_bytes, stream=0, iters=100):
+        """Average milliseconds per call of (repack + prepack, convolution kernel, split-K reduction)."""
+        ms = (C.c_float * 3)()
+        check(lib().gieb_conv_time_stages(self._h, x, w, bias, y, workspace, workspace_bytes, stream, iters, ms))
+        return float(ms[0]), float(ms[1]), float(ms[2])
 
     def device_status(self) -> int:
         v = C.c_uint32()

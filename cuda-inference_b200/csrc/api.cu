@@ -320,8 +320,10 @@ int encode_maps(const gieb_conv_plan* pl, const void* xn, const void* wk, CUtens
   return GIEB_OK;
 }
 
+// `ev`, when given, receives four stage marks: before the repack, before the convolution kernel, after it, and
+// after the split-K reduction (LaunchArgs::stage_events analogue, include/gpu_inference/kernel_registry.h:38-40).
 int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
-                cudaStream_t st) {
+                cudaStream_t st, cudaEvent_t* ev = nullptr) {
   if (pl == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null plan");
   const gieb_conv_desc& d = pl->desc;
   const Resolved& r = pl->r;
@@ -338,8 +340,10 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   if (cur != pl->device) return fail(GIEB_INVALID_ARGUMENT, "plan was created for device %d but device %d is current", pl->device, cur);
 
   if (r.variant == 3) {
+    if (ev) { GIEB_CUDA(cudaEventRecord(ev[0], st)); GIEB_CUDA(cudaEventRecord(ev[1], st)); }
     GIEB_CUDA(conv_fp32_launch(x, w, bias, y, d.batch, d.in_channels, d.in_h, d.in_w, d.out_channels, d.kernel_h, d.kernel_w,
                                d.stride_h, d.stride_w, d.pad_h, d.pad_w, pl->g.out_h, pl->g.out_w, d.relu, st));
+    if (ev) { GIEB_CUDA(cudaEventRecord(ev[2], st)); GIEB_CUDA(cudaEventRecord(ev[3], st)); }
     return GIEB_OK;
   }
 
@@ -357,6 +361,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   const int st_maps = encode_maps(pl, xn, wk, &tm_act, &tm_wgt);
   if (st_maps != GIEB_OK) return st_maps;
 
+  if (ev) GIEB_CUDA(cudaEventRecord(ev[0], st));
   GIEB_CUDA(repack_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, st));
   if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED))
     GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
@@ -384,9 +389,12 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.partial = part;
   p.status = pl->d_status;
   dim3 grid(unsigned(r.tiles_m), unsigned(r.tiles_n), unsigned(r.split_k));
+  if (ev) GIEB_CUDA(cudaEventRecord(ev[1], st));
   GIEB_CUDA(conv_tc_launch(r.tile_n, r.tile_k, tm_act, tm_wgt, p, grid, r.smem, st));
+  if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
   if (r.split_k > 1)
     GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_bf16, y, st));
+  if (ev) GIEB_CUDA(cudaEventRecord(ev[3], st));
   return GIEB_OK;
 }
 
@@ -483,6 +491,32 @@ int gieb_conv_plan_info(const gieb_conv_plan* plan, gieb_conv_info* out) {
 int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y, void* workspace,
                      size_t workspace_bytes, void* stream) {
   return launch_impl(plan, x, w, bias, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int gieb_conv_time_stages(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y, void* workspace,
+                          size_t workspace_bytes, void* stream, int iters, float* stage_ms) {
+  if (stage_ms == nullptr || iters <= 0 || iters > 4096) return fail(GIEB_INVALID_ARGUMENT, "iters must be in [1, 4096] and stage_ms non-null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaEvent_t* ev = new (std::nothrow) cudaEvent_t[size_t(iters) * 4];
+  if (ev == nullptr) return fail(GIEB_INTERNAL, "out of host memory");
+  int made = 0, rc = GIEB_OK;
+  for (; made < iters * 4; ++made)
+    if (cudaEventCreate(&ev[made]) != cudaSuccess) { rc = fail(GIEB_CUDA_ERROR, "cudaEventCreate failed"); break; }
+  for (int i = 0; rc == GIEB_OK && i < iters; ++i) rc = launch_impl(plan, x, w, bias, y, workspace, workspace_bytes, st, ev + size_t(i) * 4);
+  if (rc == GIEB_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(GIEB_CUDA_ERROR, "stream synchronisation failed");
+  if (rc == GIEB_OK) {
+    double acc[3] = {0, 0, 0};
+    for (int i = 0; i < iters; ++i)
+      for (int k = 0; k < 3; ++k) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, ev[size_t(i) * 4 + k], ev[size_t(i) * 4 + k + 1]);
+        acc[k] += ms;
+      }
+    for (int k = 0; k < 3; ++k) stage_ms[k] = float(acc[k] / iters);
+  }
+  for (int i = 0; i < made; ++i) cudaEventDestroy(ev[i]);
+  delete[] ev;
+  return rc;
 }
 
 int gieb_conv_plan_device_status(const gieb_conv_plan* plan, uint32_t* status_out) {

@@ -122,6 +122,14 @@ GIEB_API int gieb_conv_plan_info(const gieb_conv_plan* plan, gieb_conv_info* out
 GIEB_API int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y,
                               void* workspace, size_t workspace_bytes, void* stream);
 
+/* Measurement helper standing in for the stage_events hook of ExecutionPlan::execute
+ * (include/gpu_inference/execution_plan.h:25-31, kernel_registry.h:38-40) and time_stream_work
+ * (src/runtime/timing.cpp:21-83): runs `iters` forward calls on `stream` with CUDA events between the stages,
+ * synchronises the stream and returns average milliseconds per call of stage_ms[0] = layout repack + weight
+ * prepack, [1] = convolution kernel, [2] = split-K reduction.  Creates events and synchronises: not for hot paths. */
+GIEB_API int gieb_conv_time_stages(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y,
+                                   void* workspace, size_t workspace_bytes, void* stream, int iters, float* stage_ms);
+
 /* Device-side status word of the plan: 0 = no kernel of this plan ever gave up on a bounded wait.  Synchronises
  * nothing itself; call after the stream has been synchronised.  (No reference counterpart: the reference's
  * kernels have no asynchronous waits.) */
