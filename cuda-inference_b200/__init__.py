@@ -75,6 +75,7 @@ def lib() -> C.CDLL:
         L.gieb_conv_plan_info.argtypes = [vp, C.POINTER(ConvInfo)]
         L.gieb_conv_launch.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp]
         L.gieb_conv_time_stages.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp, i32, C.POINTER(C.c_float)]
+        L.gieb_conv_forward_static.argtypes = [C.POINTER(ConvDesc), C.POINTER(ConvCfg), vp, vp, vp, vp, vp]
         L.gieb_conv_plan_device_status.argtypes = [vp, C.POINTER(C.c_uint32)]
         L.gieb_repack_nchw_to_nhwc.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.gieb_prepack_weights.argtypes = [vp, vp, i32, i32, i32, i32, vp]
@@ -191,6 +192,14 @@ class ConvPlan:
             self.close()
         except Exception:
             pass
+
+
+def conv_forward_static(problem: ConvProblem, x: int, w: int, bias: int | None, y: int, stream: int = 0,
+                        cfg: ConvCfg | None = None) -> None:
+    """Forward call for callers that must not allocate device memory: uses the 8 MiB scratch built into the library
+    instead of a plan and a workspace.  Calls that overlap on the GPU race on that scratch; larger problems raise
+    GieError(WORKSPACE_TOO_SMALL)."""
+    check(lib().gieb_conv_forward_static(C.byref(problem.desc()), C.byref(cfg) if cfg is not None else None, x, w, bias, y, stream))
 
 
 def repack_nchw_to_nhwc(src: int, dst: int, batch: int, channels: int, hw: int, c_padded: int, stream: int = 0) -> None:

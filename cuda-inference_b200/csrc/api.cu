@@ -519,6 +519,65 @@ int gieb_conv_time_stages(const gieb_conv_plan* plan, const void* x, const void*
   return rc;
 }
 
+// ---- forward call for callers that cannot allocate device memory ------------------------------------------------
+// Scratch of gieb_conv_forward_static: the first 256 bytes hold the status word the kernels report bounded-wait
+// expiries to, the rest is the workspace (channel-padded NHWC copy, prepacked weights, split-K partials).
+// Every GPU that loads the library holds these 8 MiB + 256 B until the process exits.
+constexpr size_t kStaticScratchHeader = 256;
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchHeader + kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+unsigned char* g_static_ptr[kMaxDevices] = {};  // device address of g_static_scratch, per device
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the address a kernel can use
+// comes from cudaGetSymbolAddress, asked once per device while that device is current.
+int static_scratch_for_current_device(unsigned char** out) {
+  int dev = 0;
+  GIEB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(GIEB_UNSUPPORTED, "device ordinal %d is outside the supported range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    unsigned char* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
+    if (p == nullptr) return fail(GIEB_INTERNAL, "the runtime returned a null address for the static scratch");
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return GIEB_OK;
+}
+}  // namespace
+
+int gieb_conv_forward_static(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, const void* x, const void* w,
+                             const void* bias, void* y, void* stream) {
+  const int st = validate(desc);
+  if (st != GIEB_OK) return st;
+  gieb_conv_plan pl;  // lives on the host stack for the duration of this call only
+  char why[256] = "";
+  if (resolve(*desc, cfg, &pl.r, why, sizeof(why)) != GIEB_OK) return fail(GIEB_UNSUPPORTED, "%.255s", why);
+  if (pl.r.ws_total > kStaticScratchBytes)
+    return fail(GIEB_WORKSPACE_TOO_SMALL,
+                "this problem needs %zu bytes of scratch but the built-in scratch holds %zu bytes; "
+                "use gieb_conv_plan_create + gieb_conv_launch with a caller-provided workspace",
+                pl.r.ws_total, kStaticScratchBytes);
+  unsigned char* base = nullptr;
+  const int ss = static_scratch_for_current_device(&base);
+  if (ss != GIEB_OK) return ss;
+  pl.desc = *desc;
+  pl.g = geometry(*desc);
+  GIEB_CUDA(cudaGetDevice(&pl.device));
+  pl.d_status = reinterpret_cast<uint32_t*>(base);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pl.r.variant == 1) GIEB_CUDA(conv_tc_prepare(pl.r.tile_n, pl.r.tile_k, kMaxDynamicSmem));
+  // The array keeps whatever the previous call left: the status word must start at zero.  Everything else in the
+  // scratch is fully rewritten by the repack kernels (padding channels included) and the split-K slices before use.
+  GIEB_CUDA(cudaMemsetAsync(base, 0, kStaticScratchHeader, s));
+  return launch_impl(&pl, x, w, bias, y, base + kStaticScratchHeader, kStaticScratchBytes, s);
+}
+
 int gieb_conv_plan_device_status(const gieb_conv_plan* plan, uint32_t* status_out) {
   if (plan == nullptr || status_out == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null argument");
   cudaStream_t s = nullptr;

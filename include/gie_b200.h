@@ -130,6 +130,24 @@ GIEB_API int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const v
 GIEB_API int gieb_conv_time_stages(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y,
                                    void* workspace, size_t workspace_bytes, void* stream, int iters, float* stage_ms);
 
+/* No counterpart in the reference.  One-shot forward call for callers that are not allowed to allocate device memory
+ * -- code running inside someone else's memory budget (a serving process whose pool owns the whole GPU, a plug-in
+ * loaded into a host application, a real-time loop) where cudaMalloc either fails or stalls everything on the device.
+ * It does what gieb_conv_plan_create + gieb_conv_launch do, but the scratch the path needs (channel-contiguous copy
+ * of X, prepacked W, split-K partials, status word) lives in an 8 MiB array that is part of the library image, so the
+ * call performs no cudaMalloc/cudaFree and calls no allocating routine.  Limits and rules:
+ *   - problems whose scratch exceeds 8 MiB are refused with GIEB_WORKSPACE_TOO_SMALL (the message says how much is
+ *     needed); use the plan API with your own workspace for those;
+ *   - every GPU that loads the library carries the 8 MiB + 256 B until the process exits;
+ *   - the first call on each device looks up the array's device address (with that device current); make that first
+ *     call outside any stream capture;
+ *   - all calls on a device share the one array: two calls whose GPU work overlaps (different streams, different
+ *     threads) race on it -- serialise them on one stream or with events.  Nothing is carried from call to call:
+ *     the status word is cleared and the rest rewritten on every call.
+ * Results are bit-identical to gieb_conv_launch with the same configuration. */
+GIEB_API int gieb_conv_forward_static(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, const void* x, const void* w,
+                                      const void* bias, void* y, void* stream);
+
 /* Device-side status word of the plan: 0 = no kernel of this plan ever gave up on a bounded wait.  Synchronises
  * nothing itself; call after the stream has been synchronised.  (No reference counterpart: the reference's
  * kernels have no asynchronous waits.) */
