@@ -4,6 +4,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -96,8 +97,8 @@ int validate(const gieb_conv_desc* d) {
 // the slowest CTA: per reduction slab max(tensor-pipe time, shared-memory read time), plus fixed prologue/epilogue
 // cost, plus (for split-K) writing and re-reading FP32 partials and the extra launch.
 struct Resolved {
-  int variant;  // 1 tensor path (repack + im2col TMA), 3 FP32 SIMT
-  int tile_n, tile_k, stages, split_k;
+  int variant;  // 1 tensor path with im2col-mode TMA, 4 tensor path with tiled TMA (1x1, stride 1, pad 0), 3 FP32 SIMT
+  int tile_m, tile_n, tile_k, stages, split_k;
   int c_padded, kb_per_tap, total_kb, kb_per_split;
   int tiles_m, tiles_n;
   size_t smem;
@@ -111,22 +112,60 @@ int pick_tile_k(int c) {
   return 16;
 }
 
-double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_n, int tile_k, int split) {
+// Measured on B200 (profiles/): one SM pulls about 48 B/clk of operands from L2 through TMA, well below the 128 B/clk
+// the tensor pipe of a 128x128 tile would need, so operand bytes per slab usually decide.  CTAs that fit together on
+// an SM (shared memory and the 512 TMEM columns permitting) hide each other's prologue and epilogue.
+constexpr double kFeedBytesPerClk = 48.0;
+
+size_t stage_bytes_of(int tile_m, int tile_n, int tile_k) { return size_t(tile_m + tile_n) * tile_k * 2; }
+
+int resident_ctas(int tile_m, int tile_n, size_t smem) {
+  int by_smem = int(kMaxDynamicSmem / (smem + 1024));
+  int by_tmem = 512 / (tile_m / kTileM * tile_n < 32 ? 32 : tile_m / kTileM * tile_n);
+  int r = by_smem < by_tmem ? by_smem : by_tmem;
+  return r < 1 ? 1 : (r > 4 ? 4 : r);
+}
+
+// Ring depth: deep enough to cover L2 latency, shallow enough that two CTAs share an SM when more than one wave of
+// CTAs exists (their epilogues then overlap with another CTA's main loop).
+int pick_stages(int tile_m, int tile_n, int tile_k, int kb_per_split, int64_t ctas) {
+  const size_t sb = stage_bytes_of(tile_m, tile_n, tile_k);
+  const int cols = (tile_m / kTileM) * tile_n;
+  // measured: with >= 2.5 CTAs per SM three shallow CTAs per SM beat two deeper ones; between 1 and 2.5 two CTAs win
+  int want = 1;
+  if (ctas * 2 >= 5 * kNumSms && cols <= 128) want = 3;
+  else if (ctas > kNumSms && cols <= 256) want = 2;
+  const size_t budget = want == 1 ? kSmemBudget : (kMaxDynamicSmem / want - 2048);
+  int stages = int((budget - 3072) / sb);
+  if (stages > 6) stages = 6;
+  if (stages > kb_per_split) stages = kb_per_split;
+  if (stages < 2) stages = 2;
+  return stages;
+}
+
+double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, int tile_n, int tile_k, int split) {
   const int c_padded = round_up(d.in_channels, tile_k);
   const int total_kb = d.kernel_h * d.kernel_w * (c_padded / tile_k);
   const int kb_per_split = ceil_div(total_kb, split);
   const int real_split = ceil_div(total_kb, kb_per_split);
-  const int64_t ctas = int64_t(ceil_div(g.pixels, kTileM)) * ceil_div(d.out_channels, tile_n) * real_split;
-  const double waves = double((ctas + kNumSms - 1) / kNumSms);
-  const double mma = double(tile_n) * tile_k / 32.0;                   // 128 x N x K MACs at 4096 MAC/clk/SM
-  const double smem = double(kTileM + tile_n) * tile_k * 2.0 / 128.0;  // operand bytes at 128 B/clk/SM
-  const double slab = mma > smem ? mma : smem;
-  const double epilogue = 600.0 + 6.0 * tile_n;
-  double per_cta = 1800.0 + kb_per_split * slab + epilogue;
-  double total = waves * per_cta;
+  const int64_t ctas = int64_t(ceil_div(g.pixels, tile_m)) * ceil_div(d.out_channels, tile_n) * real_split;
+  const int stages = pick_stages(tile_m, tile_n, tile_k, kb_per_split, ctas);
+  const size_t smem = conv_tc_smem_bytes(tile_m, tile_n, tile_k, stages);
+  if (smem > kMaxDynamicSmem) return 1e300;
+  const int resident = resident_ctas(tile_m, tile_n, smem);
+  const double ctas_per_sm = double((ctas + kNumSms - 1) / kNumSms);
+  const double mma = double(tile_m) * tile_n * tile_k / 4096.0;  // MACs at 4096 MAC/clk/SM
+  const double bytes = double(stage_bytes_of(tile_m, tile_n, tile_k));
+  // All CTAs of an SM together stream operands at ~47 B/clk; one CTA alone sustains less (one producer thread,
+  // one ring), so a lone fat CTA is charged its own, slower rate.
+  const double slab_shared = fmax(mma, bytes / kFeedBytesPerClk);
+  const double slab_alone = fmax(mma, bytes / 40.0 + 180.0);
+  const double fixed = 4000.0 + double(tile_m / kTileM) * tile_n * 20.0;  // set-up, pipeline fill, serial epilogue
+  const double rounds = ceil(ctas_per_sm / resident);                     // groups of co-resident CTAs, one after another
+  double total = fmax(ctas_per_sm * kb_per_split * slab_shared, rounds * kb_per_split * slab_alone) + rounds * fixed;
   if (real_split > 1) {
     const double bytes = 2.0 * real_split * double(g.y_elems) * 4.0;
-    total += 6000.0 + bytes / 2048.0;  // extra launch + partial traffic at ~4 TB/s (L2-resident partials)
+    total += 9000.0 + bytes / 1500.0;  // extra launch + FP32 partial traffic
   }
   return total;
 }
@@ -144,15 +183,17 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
     if (c.variant != 0 && c.variant != 3) return no("FP32 runs on the SIMT kernel only (variant 3)");
     if (d.flags & (GIEB_FLAG_WEIGHTS_PREPACKED)) return no("prepacked weights apply to the 16-bit tensor path only");
     r->variant = 3;
-    r->tile_n = conv_fp32_tile(g.pixels, d.out_channels);
+    r->tile_m = r->tile_n = conv_fp32_tile(g.pixels, d.out_channels);
     r->tile_k = 16;
     r->stages = 2;
     r->split_k = 1;
     if (ceil_div(d.out_channels, 32) > 65535) return no("grid.y limit exceeded");
     return GIEB_OK;
   }
-  if (c.variant != 0 && c.variant != 1) return no("unknown kernel variant for 16-bit precision (1 = im2col-TMA tensor path)");
-  r->variant = 1;
+  const bool pointwise = d.kernel_h == 1 && d.kernel_w == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_h == 0 && d.pad_w == 0;
+  if (c.variant != 0 && c.variant != 1 && c.variant != 4) return no("unknown kernel variant for 16-bit precision (1 = im2col-mode TMA, 4 = tiled TMA for 1x1)");
+  if (c.variant == 4 && !pointwise) return no("variant 4 (tiled activation loads) needs a 1x1 kernel with stride 1 and no padding");
+  r->variant = (pointwise && c.variant != 1) ? 4 : 1;
 
   // hardware limits of the im2col-mode tensor map (rank 4): traversal strides 1..8, corners and offsets 8-bit
   if (d.stride_h > 8 || d.stride_w > 8) return no("stride > 8 cannot be expressed by the TMA im2col traversal stride");
@@ -169,40 +210,44 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
     r->tile_n = c.tile_n;
   }
   if (c.split_k < 0) return no("split_k must be >= 0");
-  // search (tile_n, split_k) unless fixed
+  if (c.tile_m != 0 && c.tile_m != 128 && c.tile_m != 256) return no("tile_m must be 128 or 256");
+  // search (tile_m, tile_n, split_k) unless fixed
   double best = 1e300;
-  int best_n = 0, best_s = 0;
+  int best_m = 0, best_n = 0, best_s = 0;
   const int n_opts[4] = {32, 64, 128, 256};
-  for (int ni = 0; ni < 4; ++ni) {
-    const int tn = n_opts[ni];
-    if (r->tile_n && tn != r->tile_n) continue;
-    if (!r->tile_n && tn > 32 && tn / 2 >= d.out_channels) continue;  // never pad channels by 2x or more
-    for (int s = 1; s <= 16; ++s) {
-      if (c.split_k && s != c.split_k) continue;
-      if (s > 1 && r->total_kb < 2 * s) break;  // reduction too short (src/kernels/tensor_core_mma.cu:292 rule)
-      if (s > 1 && size_t(s) * size_t(g.y_elems) * 4 > (size_t(1) << 31)) break;
-      const double t = estimate_cycles(d, g, tn, r->tile_k, s);
-      if (t < best) { best = t; best_n = tn; best_s = s; }
+  for (int tm = 128; tm <= 256; tm += 128) {
+    if (c.tile_m && tm != c.tile_m) continue;
+    if (!c.tile_m && tm == 256 && int64_t(ceil_div(g.pixels, 256)) * ceil_div(d.out_channels, 128) < 4 * kNumSms) continue;  // big tiles only where wave quantisation is negligible
+    for (int ni = 0; ni < 4; ++ni) {
+      const int tn = n_opts[ni];
+      if (r->tile_n && tn != r->tile_n) continue;
+      if (!r->tile_n && tn > 32 && tn / 2 >= d.out_channels) continue;  // never pad channels by 2x or more
+      for (int s = 1; s <= 16; ++s) {
+        if (c.split_k && s != c.split_k) continue;
+        if (s > 1 && r->total_kb < 2 * s) break;  // reduction too short (src/kernels/tensor_core_mma.cu:292 rule)
+        if (s > 1 && size_t(s) * size_t(g.y_elems) * 4 > (size_t(1) << 31)) break;
+        const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s);
+        if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; }
+      }
     }
   }
   if (best_n == 0) {
     if (c.split_k > 1) return no("reduction too short for this split-K factor");
     return no("no feasible tile configuration");
   }
+  r->tile_m = best_m;
   r->tile_n = best_n;
   r->kb_per_split = ceil_div(r->total_kb, best_s);
   r->split_k = ceil_div(r->total_kb, r->kb_per_split);  // every slice non-empty
-  r->tiles_m = ceil_div(g.pixels, kTileM);
+  r->tiles_m = ceil_div(g.pixels, r->tile_m);
   r->tiles_n = ceil_div(d.out_channels, r->tile_n);
   if (r->tiles_n > 65535 || r->split_k > 65535) return no("grid limit exceeded");
 
-  const size_t stage_bytes = size_t(kTileM + r->tile_n) * r->tile_k * 2;
-  int stages = c.stages ? c.stages : int((kSmemBudget - 3072) / stage_bytes);
-  if (stages > kMaxStages) stages = kMaxStages;
-  if (!c.stages && stages > r->kb_per_split) stages = r->kb_per_split < 2 ? 2 : r->kb_per_split;
+  const int stages = c.stages ? c.stages
+                              : pick_stages(r->tile_m, r->tile_n, r->tile_k, r->kb_per_split, int64_t(r->tiles_m) * r->tiles_n * r->split_k);
   if (stages < 2 || stages > kMaxStages) return no("stages must be in [2, 8]");
   r->stages = stages;
-  r->smem = conv_tc_smem_bytes(r->tile_n, r->tile_k, stages);
+  r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages);
   if (r->smem > kMaxDynamicSmem) return no("configuration needs more shared memory than one CTA may have (227 KiB)");
 
   // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
@@ -219,6 +264,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
   const Geometry g = geometry(d);
   out->supported = 1;
   out->variant = r.variant;
+  out->cfg.tile_m = r.tile_m;
   out->cfg.tile_n = r.tile_n;
   out->cfg.tile_k = r.tile_k;
   out->cfg.stages = r.stages;
@@ -236,7 +282,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
     out->dynamic_smem_bytes = uint32_t(r.smem);
     out->threads_per_block = kTcThreads;
     out->num_blocks = int64_t(r.tiles_m) * r.tiles_n * r.split_k;
-    out->launches = 2 + ((d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : 1) + (r.split_k > 1 ? 1 : 0);
+    out->launches = 2 + (r.split_k > 1 ? 1 : 0);  // repack (activations + weights in one launch), convolution, reduction
   }
 }
 
@@ -293,7 +339,16 @@ int encode_maps(const gieb_conv_plan* pl, const void* xn, const void* wk, CUtens
   const Resolved& r = pl->r;
   const CUtensorMapDataType dt = d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUtensorMapSwizzle sw = swizzle_for(r.tile_k);
-  {
+  if (r.variant == 4) {  // 1x1 / stride 1 / pad 0: the NHWC copy is the GEMM operand [pixels][Cp] itself
+    const cuuint64_t dims[2] = {cuuint64_t(r.c_padded), cuuint64_t(d.batch) * d.in_h * d.in_w};
+    const cuuint64_t strides[1] = {cuuint64_t(r.c_padded) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(r.tile_k), cuuint32_t(kTileM)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult res = g_encode_tiled(tm_act, dt, 2, const_cast<void*>(xn), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (activations) failed with CUresult %d", int(res));
+    small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * d.in_w * r.c_padded * 2);
+  } else {
     const cuuint64_t dims[4] = {cuuint64_t(r.c_padded), cuuint64_t(d.in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
     const cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(d.in_w) * r.c_padded * 2,
                                    cuuint64_t(d.in_h) * d.in_w * r.c_padded * 2};
@@ -362,9 +417,11 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   if (st_maps != GIEB_OK) return st_maps;
 
   if (ev) GIEB_CUDA(cudaEventRecord(ev[0], st));
-  GIEB_CUDA(repack_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, st));
-  if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED))
-    GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
+  if (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)
+    GIEB_CUDA(repack_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, st));
+  else
+    GIEB_CUDA(repack_pair_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, w, const_cast<void*>(wk),
+                                 d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
 
   ConvTcParams p;
   memset(&p, 0, sizeof(p));
@@ -383,6 +440,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.relu = d.relu; p.has_bias = d.has_bias;
   p.is_bf16 = d.precision == GIEB_BF16;
   p.bias_fp32 = (d.flags & GIEB_FLAG_BIAS_FP32) ? 1 : 0;
+  p.a_tiled = r.variant == 4 ? 1 : 0;
   p.idesc = ptx::make_idesc_f16(kTileM, r.tile_n, p.is_bf16, false, false);
   p.bias = bias;
   p.y = y;
@@ -390,7 +448,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.status = pl->d_status;
   dim3 grid(unsigned(r.tiles_m), unsigned(r.tiles_n), unsigned(r.split_k));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[1], st));
-  GIEB_CUDA(conv_tc_launch(r.tile_n, r.tile_k, tm_act, tm_wgt, p, grid, r.smem, st));
+  GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, tm_act, tm_wgt, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
   if (r.split_k > 1)
     GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_bf16, y, st));
@@ -465,7 +523,7 @@ int gieb_conv_plan_create(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, 
       cudaStreamDestroy(s);
     }
   }
-  if (e == cudaSuccess && r.variant == 1) e = conv_tc_prepare(r.tile_n, r.tile_k, kMaxDynamicSmem);
+  if (e == cudaSuccess && r.variant != 3) e = conv_tc_prepare(r.tile_m, r.tile_n, r.tile_k, kMaxDynamicSmem);
   if (e != cudaSuccess) {
     if (pl->d_status) cudaFree(pl->d_status);
     delete pl;
@@ -571,7 +629,7 @@ int gieb_conv_forward_static(const gieb_conv_desc* desc, const gieb_conv_cfg* cf
   GIEB_CUDA(cudaGetDevice(&pl.device));
   pl.d_status = reinterpret_cast<uint32_t*>(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (pl.r.variant == 1) GIEB_CUDA(conv_tc_prepare(pl.r.tile_n, pl.r.tile_k, kMaxDynamicSmem));
+  if (pl.r.variant != 3) GIEB_CUDA(conv_tc_prepare(pl.r.tile_m, pl.r.tile_n, pl.r.tile_k, kMaxDynamicSmem));
   // The array keeps whatever the previous call left: the status word must start at zero.  Everything else in the
   // scratch is fully rewritten by the repack kernels (padding channels included) and the split-K slices before use.
   GIEB_CUDA(cudaMemsetAsync(base, 0, kStaticScratchHeader, s));

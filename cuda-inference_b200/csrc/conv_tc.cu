@@ -28,16 +28,20 @@ namespace {
 
 constexpr uint32_t kCtrlBytes = 2048;  // [0,1024): bias tile as float; [1024,2048): mbarriers + TMEM address slot
 
-template <int BN, int BK>
+// MH = number of 128-pixel halves a CTA computes (1 or 2).  With MH = 2 the CTA owns a 256-pixel tile: two
+// activation loads and two accumulators share every weight tile, which halves the weight traffic per FLOP.
+template <int BN, int BK, int MH>
 __global__ void __launch_bounds__(kTcThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_wgt,
                const ConvTcParams p) {
   constexpr int ROW_BYTES = BK * 2;
-  constexpr uint32_t A_BYTES = kTileM * ROW_BYTES;
+  constexpr uint32_t A_HALF_BYTES = kTileM * ROW_BYTES;
+  constexpr uint32_t A_BYTES = MH * A_HALF_BYTES;
   constexpr uint32_t B_BYTES = BN * ROW_BYTES;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int MMAS_PER_SLAB = BK / 16;
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t TMEM_COLS = MH * BN < 32 ? 32 : MH * BN;
+  static_assert(MH * BN <= 512, "accumulators must fit the 512 TMEM columns");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -49,8 +53,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   uint8_t* stage_base = smem + kCtrlBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * kTileM;
+  const int m0 = blockIdx.x * (kTileM * MH);
   const int n0 = blockIdx.y * BN;
+  const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;  // a trailing tile may own one half only
   const int kb_begin = blockIdx.z * p.kb_per_split;
   const int kb_end = min(p.total_kb, kb_begin + p.kb_per_split);
   const int num_kb = kb_end - kb_begin;
@@ -90,12 +95,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const int img = m0 / p.pq;
-      const int rem = m0 - img * p.pq;
-      const int p0 = rem / p.out_w;
-      const int q0 = rem - p0 * p.out_w;
-      const int base_w = q0 * p.stride_w - p.pad_w;
-      const int base_h = p0 * p.stride_h - p.pad_h;
+      int img[MH], base_w[MH], base_h[MH];
+#pragma unroll
+      for (int h = 0; h < MH; ++h) {
+        const int mh = m0 + h * kTileM;
+        img[h] = mh / p.pq;
+        const int rem = mh - img[h] * p.pq;
+        const int p0 = rem / p.out_w;
+        const int q0 = rem - p0 * p.out_w;
+        base_w[h] = q0 * p.stride_w - p.pad_w;
+        base_h[h] = p0 * p.stride_h - p.pad_h;
+      }
+      const uint32_t tx_bytes = uint32_t(halves) * A_HALF_BYTES + B_BYTES;
       for (int i = 0; i < num_kb; ++i) {
         const int s = i % stages;
         const uint32_t phase = (i / stages) & 1;
@@ -107,8 +118,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         const int sx = tap - r * p.kernel_w;
         uint8_t* a_dst = stage_base + size_t(s) * STAGE_BYTES;
         uint8_t* b_dst = a_dst + A_BYTES;
-        ptx::mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
-        ptx::tma_load_im2col_4d(a_dst, &tm_act, &full_bar[s], cb * BK, base_w, base_h, img, uint16_t(sx), uint16_t(r));
+        ptx::mbar_arrive_expect_tx(&full_bar[s], tx_bytes);
+#pragma unroll
+        for (int h = 0; h < MH; ++h)
+          if (h < halves) {
+            if (p.a_tiled)
+              ptx::tma_load_2d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, m0 + h * kTileM);
+            else
+              ptx::tma_load_im2col_4d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, base_w[h], base_h[h], img[h],
+                                      uint16_t(sx), uint16_t(r));
+          }
         ptx::tma_load_2d(b_dst, &tm_wgt, &full_bar[s], tap * p.c_padded + cb * BK, n0);
       }
     }
@@ -123,9 +142,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
         const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-        for (int k = 0; k < MMAS_PER_SLAB; ++k) {
-          ptx::mma_f16_ss(tmem_base, ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + k * 32),
-                          ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32), p.idesc, (i | k) != 0);
+        for (int h = 0; h < MH; ++h) {
+          if (h < halves) {
+#pragma unroll
+            for (int k = 0; k < MMAS_PER_SLAB; ++k) {
+              ptx::mma_f16_ss(tmem_base + h * BN, ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32),
+                              ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32), p.idesc, (i | k) != 0);
+            }
+          }
         }
         ptx::mma_commit(&empty_bar[s]);  // frees the slot once these MMAs have read it
       }
@@ -134,11 +158,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   } else {
     // ---------------- epilogue (warps 2..5 cover TMEM lane quarters 2,3,0,1) ----------------
     const int quad = warp & 3;
-    const int m = m0 + quad * 32 + lane;
     const bool ok = ptx::mbar_wait(accum_bar, 0, p.status, kStatusEpilogueTimeout);
     __syncwarp();
     ptx::tc_fence_after_sync();
     if (__all_sync(0xffffffffu, ok)) {
+     for (int h = 0; h < halves; ++h) {
+      const int m = m0 + h * kTileM + quad * 32 + lane;
       const bool m_ok = m < p.m_total;
       const int img = m_ok ? m / p.pq : 0;
       const int pix = m_ok ? m - img * p.pq : 0;
@@ -149,7 +174,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       for (int chunk = 0; chunk < BN / 32; ++chunk) {
         if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform
         uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(chunk * 32), v);
+        ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(h * BN + chunk * 32), v);
         ptx::tmem_ld_wait();
         if (m_ok) {
           const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
@@ -176,6 +201,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           }
         }
       }
+     }
     }
   }
 
@@ -187,32 +213,44 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   }
 }
 
-template <int BN, int BK>
+template <int BN, int BK, int MH>
 cudaError_t prepare_one(size_t smem_bytes) {
-  return cudaFuncSetAttribute(conv_tc_kernel<BN, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
+  return cudaFuncSetAttribute(conv_tc_kernel<BN, BK, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
 }
 
-template <int BN, int BK>
+template <int BN, int BK, int MH>
 cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tw, const ConvTcParams& p, dim3 grid, size_t smem,
                        cudaStream_t st) {
-  conv_tc_kernel<BN, BK><<<grid, kTcThreads, smem, st>>>(ta, tw, p);
+  conv_tc_kernel<BN, BK, MH><<<grid, kTcThreads, smem, st>>>(ta, tw, p);
   return cudaGetLastError();
 }
 
 #define GIEB_TC_DISPATCH(FN, ...)                                                     \
-  switch (tile_n * 100 + tile_k) {                                                    \
-    case 32 * 100 + 16: return FN<32, 16>(__VA_ARGS__);                               \
-    case 32 * 100 + 32: return FN<32, 32>(__VA_ARGS__);                               \
-    case 32 * 100 + 64: return FN<32, 64>(__VA_ARGS__);                               \
-    case 64 * 100 + 16: return FN<64, 16>(__VA_ARGS__);                               \
-    case 64 * 100 + 32: return FN<64, 32>(__VA_ARGS__);                               \
-    case 64 * 100 + 64: return FN<64, 64>(__VA_ARGS__);                               \
-    case 128 * 100 + 16: return FN<128, 16>(__VA_ARGS__);                             \
-    case 128 * 100 + 32: return FN<128, 32>(__VA_ARGS__);                             \
-    case 128 * 100 + 64: return FN<128, 64>(__VA_ARGS__);                             \
-    case 256 * 100 + 16: return FN<256, 16>(__VA_ARGS__);                             \
-    case 256 * 100 + 32: return FN<256, 32>(__VA_ARGS__);                             \
-    case 256 * 100 + 64: return FN<256, 64>(__VA_ARGS__);                             \
+  switch (tile_m / 128 * 100000 + tile_n * 100 + tile_k) {                            \
+    case 1 * 100000 + 32 * 100 + 16: return FN<32, 16, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 32 * 100 + 16: return FN<32, 16, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 32 * 100 + 32: return FN<32, 32, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 32 * 100 + 32: return FN<32, 32, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 32 * 100 + 64: return FN<32, 64, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 32 * 100 + 64: return FN<32, 64, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 64 * 100 + 16: return FN<64, 16, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 64 * 100 + 16: return FN<64, 16, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 64 * 100 + 32: return FN<64, 32, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 64 * 100 + 32: return FN<64, 32, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 64 * 100 + 64: return FN<64, 64, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 64 * 100 + 64: return FN<64, 64, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 128 * 100 + 16: return FN<128, 16, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 128 * 100 + 16: return FN<128, 16, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 128 * 100 + 32: return FN<128, 32, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 128 * 100 + 32: return FN<128, 32, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 128 * 100 + 64: return FN<128, 64, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 128 * 100 + 64: return FN<128, 64, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 256 * 100 + 16: return FN<256, 16, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 256 * 100 + 16: return FN<256, 16, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 256 * 100 + 32: return FN<256, 32, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 256 * 100 + 32: return FN<256, 32, 2>(__VA_ARGS__);                \
+    case 1 * 100000 + 256 * 100 + 64: return FN<256, 64, 1>(__VA_ARGS__);                \
+    case 2 * 100000 + 256 * 100 + 64: return FN<256, 64, 2>(__VA_ARGS__);                \
     default: return cudaErrorInvalidValue;                                            \
   }
 
@@ -276,15 +314,15 @@ splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t tota
 
 }  // namespace
 
-size_t conv_tc_smem_bytes(int tile_n, int tile_k, int stages) {
-  return 1024 + kCtrlBytes + size_t(stages) * (size_t(kTileM) + tile_n) * tile_k * 2;
+size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages) {
+  return 1024 + kCtrlBytes + size_t(stages) * (size_t(tile_m) + tile_n) * tile_k * 2;
 }
 
-cudaError_t conv_tc_prepare(int tile_n, int tile_k, size_t smem_bytes) {
+cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, size_t smem_bytes) {
   GIEB_TC_DISPATCH(prepare_one, smem_bytes)
 }
 
-cudaError_t conv_tc_launch(int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
+cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
                            const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream) {
   GIEB_TC_DISPATCH(launch_one, tm_act, tm_wgt, p, grid, smem_bytes, stream)
 }

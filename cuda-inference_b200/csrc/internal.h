@@ -33,6 +33,7 @@ struct ConvTcParams {
   int stride_h, stride_w, pad_h, pad_w;
   int stages;
   int relu, has_bias, is_bf16, bias_fp32;
+  int a_tiled;        // 1x1 / stride 1 / pad 0: activations are the plain matrix [pixels][c_padded], fetched with tiled loads
   uint32_t idesc;
   const void* bias;
   void* y;            // NCHW output in the storage type (split_k == 1)
@@ -40,9 +41,10 @@ struct ConvTcParams {
   uint32_t* status;
 };
 
-size_t conv_tc_smem_bytes(int tile_n, int tile_k, int stages);
-cudaError_t conv_tc_prepare(int tile_n, int tile_k, size_t smem_bytes);  // opt in to large dynamic shared memory
-cudaError_t conv_tc_launch(int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
+// tile_m is 128 or 256 output pixels per CTA (one or two TMEM accumulators sharing each weight tile).
+size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages);
+cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, size_t smem_bytes);  // opt in to large dynamic shared memory
+cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
                            const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream);
 
 // Sum of split-K partials + bias + ReLU + one rounding; `total` = B*O*P*Q elements in NCHW order.
@@ -51,6 +53,9 @@ cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total
 
 // 16-bit [B][C][HW] -> [B][HW][Cp] (zero-filled channel padding).
 cudaError_t repack_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream);
+// Two repacks (activations + weights) in ONE launch; src_b == nullptr runs only the first.
+cudaError_t repack_pair_launch(const void* src_a, void* dst_a, int batch_a, int ch_a, int hw_a, int cp_a, const void* src_b,
+                               void* dst_b, int batch_b, int ch_b, int hw_b, int cp_b, cudaStream_t stream);
 
 // FP32 SIMT implicit GEMM straight from NCHW.
 cudaError_t conv_fp32_launch(const void* x, const void* w, const void* bias, void* y, int batch, int c, int h, int wd,

@@ -16,14 +16,12 @@ namespace {
 constexpr int kTile = 64;          // channels and pixels per CTA tile
 constexpr int kLdWords = 33;       // 32-bit words per shared-memory row (64 px + 1 word of padding)
 
-// Tiled transpose, 256 threads. grid = (ceil(HW/64), ceil(Cp/64), B).
+// Tiled transpose of one 64-channel x 64-pixel tile by 256 threads; `tile` is kTile * kLdWords words of shared memory.
 template <bool VEC_LOAD>
-__global__ void __launch_bounds__(256)
-repack_tiled_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int C, int HW, int Cp) {
-  __shared__ uint32_t tile[kTile * kLdWords];  // [channel][pixel pair]
-  const int px0 = blockIdx.x * kTile;
-  const int c0 = blockIdx.y * kTile;
-  const int b = blockIdx.z;
+__device__ __forceinline__ void repack_tile(uint32_t* tile, const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int C,
+                                            int HW, int Cp, int hw_tile, int c_tile, int b) {
+  const int px0 = hw_tile * kTile;
+  const int c0 = c_tile * kTile;
   const uint16_t* s = src + (size_t(b) * C + c0) * HW + px0;
   const int t = threadIdx.x;
 
@@ -73,14 +71,13 @@ repack_tiled_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst
   }
 }
 
-// Small-HW variant (filter taps: HW = R*S <= 256).  One CTA handles 64 channels of one batch entry: the source
-// slab [64][HW] is contiguous, so it is read linearly, then written as [HW][64].
-constexpr int kSmallHwMax = 256;
-__global__ void __launch_bounds__(256)
-repack_small_hw_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int C, int HW, int Cp) {
-  __shared__ uint16_t slab[kTile * kSmallHwMax];
-  const int c0 = blockIdx.x * kTile;
-  const int b = blockIdx.y;
+// Small-HW variant (filter taps: HW = R*S <= 64).  One CTA handles 64 channels of one batch entry: the source
+// slab [64][HW] is contiguous, so it is read linearly, then written as [HW][64].  `slab` holds kTile * kSmallHwMax
+// 16-bit words (the same shared memory as the tiled variant's tile).
+constexpr int kSmallHwMax = 64;
+__device__ __forceinline__ void repack_small_hw(uint16_t* slab, const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
+                                                int C, int HW, int Cp, int c_tile, int b) {
+  const int c0 = c_tile * kTile;
   const int nch = min(kTile, C - c0);  // may be <= 0 for pure padding tiles
   const int n = nch > 0 ? nch * HW : 0;
   const uint16_t* s = src + (size_t(b) * C + c0) * HW;
@@ -104,29 +101,69 @@ repack_small_hw_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ 
   }
 }
 
+// One repack job: a whole tensor.  mode 0 = tiled with 2-byte loads, 1 = tiled with 128-bit loads, 2 = small-HW slab.
+struct RepackJob {
+  const uint16_t* src;
+  uint16_t* dst;
+  int C, HW, Cp, batch;
+  int mode;
+  int hw_tiles, c_tiles;
+  unsigned blocks;  // hw_tiles * c_tiles * batch
+};
+
+// Up to two jobs in one launch (activations + weights): block indices [0, a.blocks) belong to job a, the rest to job b.
+__global__ void __launch_bounds__(256) repack_jobs_kernel(const RepackJob a, const RepackJob b) {
+  __shared__ __align__(16) uint32_t smem[kTile * kLdWords];  // 8448 B >= kTile * kSmallHwMax * 2 = 8192 B
+  const bool first = blockIdx.x < a.blocks;
+  const RepackJob& j = first ? a : b;
+  unsigned id = first ? blockIdx.x : blockIdx.x - a.blocks;
+  const int hw_tile = int(id % unsigned(j.hw_tiles));
+  id /= unsigned(j.hw_tiles);
+  const int c_tile = int(id % unsigned(j.c_tiles));
+  const int bi = int(id / unsigned(j.c_tiles));
+  if (j.mode == 2) repack_small_hw(reinterpret_cast<uint16_t*>(smem), j.src, j.dst, j.C, j.HW, j.Cp, c_tile, bi);
+  else if (j.mode == 1) repack_tile<true>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
+  else repack_tile<false>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
+}
+
+RepackJob make_job(const void* src, void* dst, int batch, int channels, int hw, int c_padded) {
+  RepackJob j;
+  j.src = static_cast<const uint16_t*>(src);
+  j.dst = static_cast<uint16_t*>(dst);
+  j.C = channels; j.HW = hw; j.Cp = c_padded; j.batch = batch;
+  j.c_tiles = (c_padded + kTile - 1) / kTile;
+  if (hw < 32 && hw <= kSmallHwMax) {
+    j.mode = 2;
+    j.hw_tiles = 1;
+  } else {
+    j.mode = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (hw & 7) == 0) ? 1 : 0;
+    j.hw_tiles = (hw + kTile - 1) / kTile;
+  }
+  j.blocks = 0;
+  return j;
+}
+
 }  // namespace
 
+cudaError_t repack_pair_launch(const void* src_a, void* dst_a, int batch_a, int ch_a, int hw_a, int cp_a, const void* src_b,
+                               void* dst_b, int batch_b, int ch_b, int hw_b, int cp_b, cudaStream_t stream) {
+  RepackJob a = make_job(src_a, dst_a, batch_a, ch_a, hw_a, cp_a);
+  RepackJob b = a;
+  const int64_t na = int64_t(a.hw_tiles) * a.c_tiles * batch_a;
+  int64_t nb = 0;
+  if (src_b != nullptr) {
+    b = make_job(src_b, dst_b, batch_b, ch_b, hw_b, cp_b);
+    nb = int64_t(b.hw_tiles) * b.c_tiles * batch_b;
+  }
+  if (na + nb > 2147483647LL) return cudaErrorInvalidValue;
+  a.blocks = unsigned(na);
+  b.blocks = unsigned(nb);
+  repack_jobs_kernel<<<unsigned(na + nb), 256, 0, stream>>>(a, b);
+  return cudaGetLastError();
+}
+
 cudaError_t repack_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream) {
-  const auto* s = static_cast<const uint16_t*>(src);
-  auto* d = static_cast<uint16_t*>(dst);
-  const int ctiles = (c_padded + kTile - 1) / kTile;
-  if (hw < 32 && hw <= kSmallHwMax && batch <= 65535) {
-    repack_small_hw_kernel<<<dim3(unsigned(ctiles), unsigned(batch)), 256, 0, stream>>>(s, d, channels, hw, c_padded);
-    return cudaGetLastError();
-  }
-  // grid.z carries the batch: chunk it to stay inside the 65535 limit.
-  const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (hw & 7) == 0;
-  for (int b0 = 0; b0 < batch; b0 += 65535) {
-    const int nb = batch - b0 < 65535 ? batch - b0 : 65535;
-    dim3 grid(unsigned((hw + kTile - 1) / kTile), unsigned(ctiles), unsigned(nb));
-    const uint16_t* sb = s + size_t(b0) * channels * hw;
-    uint16_t* db = d + size_t(b0) * hw * c_padded;
-    if (vec) repack_tiled_kernel<true><<<grid, 256, 0, stream>>>(sb, db, channels, hw, c_padded);
-    else repack_tiled_kernel<false><<<grid, 256, 0, stream>>>(sb, db, channels, hw, c_padded);
-    const cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-  }
-  return cudaSuccess;
+  return repack_pair_launch(src, dst, batch, channels, hw, c_padded, nullptr, nullptr, 0, 0, 0, 0, stream);
 }
 
 }  // namespace gieb

@@ -72,8 +72,10 @@ typedef struct gieb_conv_cfg {
   int32_t tile_k;   /* reduction slab in channels: 16, 32 or 64; 0 = auto                                    */
   int32_t stages;   /* shared-memory ring depth, 2..8; 0 = auto                                              */
   int32_t split_k;  /* number of reduction splits, >= 1; 0 = auto                                            */
-  int32_t variant;  /* 0 = auto, 1 = repack + im2col-TMA tensor path (16-bit), 3 = FP32 SIMT                   */
-  int32_t reserved[3];
+  int32_t variant;  /* 0 = auto, 1 = tensor path with im2col-mode TMA, 4 = tensor path with tiled TMA (1x1, stride 1,
+                       pad 0 only), 3 = FP32 SIMT                                                            */
+  int32_t tile_m;   /* output pixels per CTA tile: 128 or 256 (two accumulators share each weight tile); 0 = auto */
+  int32_t reserved[2];
 } gieb_conv_cfg;
 
 /* What KernelDesc::supports / workspace_bytes / dynamic_smem_bytes / num_blocks answer

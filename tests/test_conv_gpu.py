@@ -65,6 +65,13 @@ TILE_CASES = [
     ((2, 64, 28, 28, 128, 3, 3, 2, 2, 1, 1), dict(tile_n=128, tile_k=64, stages=4)),
     ((2, 8, 17, 23, 12, 3, 5, 2, 1, 1, 2), dict(tile_n=32, tile_k=16, stages=3, split_k=5)),
     ((4, 96, 27, 27, 192, 5, 5, 1, 1, 2, 2), dict(tile_n=64, tile_k=32, stages=8, split_k=2)),
+    # 256-pixel tiles: two accumulators per CTA share each weight tile
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=64, tile_k=64, stages=3)),
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=256, tile_k=64, stages=3, split_k=2)),
+    ((3, 64, 14, 14, 130, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=128, tile_k=32, stages=2)),   # 588 px: last tile owns one half
+    ((2, 130, 9, 9, 130, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=32, tile_k=16, stages=4, split_k=3)),
+    ((2, 64, 28, 28, 128, 3, 3, 2, 2, 1, 1), dict(tile_m=256, tile_n=128, tile_k=64, stages=2)),
+    ((1, 16, 5, 5, 8, 1, 1, 1, 1, 0, 0), dict(tile_m=256, tile_n=32, tile_k=16, stages=2)),         # 25 px: one half, mostly empty
 ]
 
 
