@@ -68,13 +68,19 @@ class Problem:
                         self.kernel_w, self.stride_h, self.stride_w, self.pad_h, self.pad_w, self.dilation_h,
                         self.dilation_w, self.groups, int(self.precision), int(self.has_bias), int(self.relu))
 
+    @staticmethod
+    def _cdiv(a: int, b: int) -> int:
+        """C integer division (truncation toward zero), as in the reference's int arithmetic."""
+        q = abs(a) // abs(b)
+        return q if (a >= 0) == (b >= 0) else -q
+
     @property
     def out_h(self) -> int:
-        return int(np.trunc((self.in_h + 2 * self.pad_h - self.dilation_h * (self.kernel_h - 1) - 1) / self.stride_h)) + 1
+        return self._cdiv(self.in_h + 2 * self.pad_h - self.dilation_h * (self.kernel_h - 1) - 1, self.stride_h) + 1
 
     @property
     def out_w(self) -> int:
-        return int(np.trunc((self.in_w + 2 * self.pad_w - self.dilation_w * (self.kernel_w - 1) - 1) / self.stride_w)) + 1
+        return self._cdiv(self.in_w + 2 * self.pad_w - self.dilation_w * (self.kernel_w - 1) - 1, self.stride_w) + 1
 
     @property
     def x_shape(self):
@@ -154,6 +160,8 @@ class Oracle:
         L.orc_conv2d.argtypes = [C.POINTER(ConvDesc)] + [C.POINTER(C.c_float)] * 5
         L.orc_flops.argtypes = [C.POINTER(ConvDesc)]
         L.orc_flops.restype = C.c_int64
+        L.orc_out_h.argtypes = [C.POINTER(ConvDesc)]
+        L.orc_out_w.argtypes = [C.POINTER(ConvDesc)]
         L.orc_rng_next_u64.argtypes = [C.POINTER(C.c_uint64)]
         L.orc_rng_next_u64.restype = C.c_uint64
         L.orc_fill_dist.argtypes = [C.POINTER(C.c_uint64), C.c_int, C.c_float, C.POINTER(C.c_float), C.c_int64]
