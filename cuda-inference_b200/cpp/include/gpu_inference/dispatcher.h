@@ -1,0 +1,37 @@
+// Kernel selection -- drop-in for the reference's dispatcher.h, reduced to what one kernel family needs:
+// an explicit kernel name wins, otherwise the first compatible registry entry of the requested backend (the
+// "auto" entries come first; the library's own cost model then picks tile, stages and split-K).
+#pragma once
+
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "gpu_inference/kernel_registry.h"
+
+namespace gie {
+
+enum class SelectionSource { kForcedKernel, kForcedBackend, kTuningCache, kTuned, kCostModel };
+const char* to_string(SelectionSource s);
+
+struct Selection {
+  const KernelDesc* kernel = nullptr;
+  SelectionSource source = SelectionSource::kCostModel;
+  double predicted_us = 0;
+  std::string reason;
+};
+
+struct Rejection {
+  std::string kernel;
+  std::string reason;
+};
+
+class Dispatcher {
+ public:
+  static std::vector<const KernelDesc*> compatible_kernels(const ConvProblem& prob, const DeviceInfo& dev,
+                                                           Backend only = Backend::kAuto,
+                                                           std::vector<Rejection>* rejected = nullptr);
+  static Selection select(const ConvProblem& prob, const DeviceInfo& dev, const Conv2DOptions& opt);
+};
+
+}  // namespace gie
