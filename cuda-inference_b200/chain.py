@@ -1,0 +1,119 @@
+"""The ResNet-50-shaped convolution chain as a sequence of C-ABI launches (convolutions with fused bias + ReLU, one
+max-pool, residual adds), enqueued on a caller's stream and capturable as ONE CUDA graph.
+
+Device buffers come from torch (plumbing only); every kernel that runs is this library's.  One ``ConvChain`` lives on
+one GPU; multi-GPU runs are independent replicas over a batch shard (no collective, no peer access)."""
+from __future__ import annotations
+
+import math
+
+from . import ConvPlan, ConvProblem, add_relu, maxpool2d
+from .workloads import FP16, BF16, chain_flops, resnet50_chain
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def shard_batch(global_batch: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous batch shard of `rank`: (first image, image count).  Earlier ranks take the remainder."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad rank/world")
+    base, rem = divmod(global_batch, world)
+    count = base + (1 if rank < rem else 0)
+    first = rank * base + min(rank, rem)
+    return first, count
+
+
+def layer_weight_bound(shape, relu: bool) -> float:
+    """Kaiming-uniform bound for a layer followed by ReLU (gain sqrt 2); layers without ReLU (block outputs and
+    projection shortcuts, i.e. where a folded batch-norm would sit) use gain 1 / 0.5 so activations stay in FP16
+    range through 16 residual blocks."""
+    fan_in = shape.in_channels * shape.kernel * shape.kernel
+    return math.sqrt(6.0 / fan_in) if relu else 0.5 * math.sqrt(3.0 / fan_in)
+
+
+class ConvChain:
+    def __init__(self, batch: int, precision: int = FP16, image: int = 224, seed: int = 0, weights=None, device=None):
+        """weights: optional list of (w, b) host numpy arrays in storage bit patterns per convolution (tests); when
+        None, weights are generated on the device from `seed` + layer index with the benchmark distributions."""
+        torch = _torch()
+        self.torch = torch
+        self.batch, self.precision, self.image = batch, precision, image
+        self.dtype = torch.float16 if precision == FP16 else torch.bfloat16
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.ops, self.slot_shapes = resnet50_chain(batch, precision, image)
+        self.flops = chain_flops(self.ops)
+        self.slots = {i: torch.empty(batch * c * h * w, dtype=self.dtype, device=self.device) for i, (c, h, w) in self.slot_shapes.items()}
+        self.convs = []  # (op, plan, w, b)
+        ws_bytes = 256
+        li = 0
+        for op in self.ops:
+            if op.kind != "conv":
+                continue
+            s = op.shape
+            plan = ConvPlan(ConvProblem(s.batch, s.in_channels, s.in_h, s.in_w, s.out_channels, s.kernel, s.kernel, s.stride, s.stride,
+                                        s.pad, s.pad, 1, 1, 1, precision, True, op.relu))
+            if weights is not None:
+                import numpy as np
+                w = torch.from_numpy(weights[li][0].view(np.int16)).to(self.device).view(self.dtype)
+                b = torch.from_numpy(weights[li][1].view(np.int16)).to(self.device).view(self.dtype)
+            else:
+                g = torch.Generator(device=self.device)
+                g.manual_seed(seed + li)
+                bound = layer_weight_bound(s, op.relu)
+                w = ((torch.rand(s.w_elems, device=self.device, generator=g) * 2 - 1) * bound).to(self.dtype)
+                b = ((torch.rand(s.out_channels, device=self.device, generator=g) * 2 - 1) * 0.1).to(self.dtype)
+            self.convs.append((op, plan, w, b))
+            ws_bytes = max(ws_bytes, plan.workspace_bytes)
+            li += 1
+        self._ws = torch.empty(ws_bytes + 256, dtype=torch.uint8, device=self.device)
+        self.ws_ptr = (self._ws.data_ptr() + 255) // 256 * 256
+        self.ws_bytes = ws_bytes
+        self.launches = sum(p.info.launches for _, p, _, _ in self.convs) + sum(1 for op in self.ops if op.kind != "conv")
+        self.graph = None
+
+    @property
+    def input(self):
+        return self.slots[0]
+
+    @property
+    def output(self):
+        return self.slots[len(self.slots) - 1]
+
+    def enqueue(self, stream: int) -> None:
+        """All launches of one forward pass on `stream` (capture-safe: no allocation, no synchronisation)."""
+        ci = 0
+        for op in self.ops:
+            if op.kind == "conv":
+                _, plan, w, b = self.convs[ci]
+                ci += 1
+                plan.launch(self.slots[op.src].data_ptr(), w.data_ptr(), b.data_ptr(), self.slots[op.dst].data_ptr(), self.ws_ptr,
+                            self.ws_bytes, stream)
+            elif op.kind == "maxpool":
+                c, h, w, k, s, p = op.pool
+                maxpool2d(self.precision, self.batch, c, h, w, k, s, p, self.slots[op.src].data_ptr(), self.slots[op.dst].data_ptr(), stream)
+            else:
+                n = self.slots[op.dst].numel()
+                add_relu(self.precision, op.relu, self.slots[op.src].data_ptr(), self.slots[op.other].data_ptr(),
+                         self.slots[op.dst].data_ptr(), n, stream)
+
+    def capture(self, stream) -> None:
+        """Runs the chain once eagerly on `stream` (a torch.cuda.Stream), then captures it as one CUDA graph."""
+        torch = self.torch
+        with torch.cuda.stream(stream):
+            self.enqueue(stream.cuda_stream)
+            stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=stream):
+                self.enqueue(torch.cuda.current_stream().cuda_stream)
+
+    def replay(self) -> None:
+        self.graph.replay()
+
+    def device_status(self) -> int:
+        st = 0
+        for _, plan, _, _ in self.convs:
+            st |= plan.device_status()
+        return st
