@@ -97,6 +97,73 @@ def dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
 
+def time_rmsnorm(torch, pkg, steps, warmup):
+    """Fused residual-add + RMSNorm, BF16 8192 x 4096, FP32 gamma = 1 + N(0, 0.02): GB/s of algorithmic bytes (x and
+    residual in, residual and y out).  Buffers rotate over more than L2."""
+    from cuda_inference_b200 import workloads as wl
+    cfg = wl.RMSNORM_WORKLOAD
+    rows, hidden = cfg["rows"], cfg["hidden"]
+    n = rows * hidden
+    nsets = 3  # 3 x 268 MB
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0)
+    sets = [(torch.randn(n, device="cuda", generator=g).to(torch.bfloat16), torch.randn(n, device="cuda", generator=g).to(torch.bfloat16),
+             torch.empty(n, device="cuda", dtype=torch.bfloat16), torch.empty(n, device="cuda", dtype=torch.bfloat16)) for _ in range(nsets)]
+    gamma = (1.0 + 0.02 * torch.randn(hidden, device="cuda", generator=g)).float()
+    stream = torch.cuda.Stream()
+
+    def launch(i):
+        x, r, y, ro = sets[i % nsets]
+        pkg.rmsnorm_forward(rows, hidden, cfg["eps"], 2, x.data_ptr(), gamma.data_ptr(), y.data_ptr(), r.data_ptr(), ro.data_ptr(),
+                            stream.cuda_stream, gamma_fp32=True)
+
+    with torch.cuda.stream(stream):
+        for i in range(max(3, warmup)):
+            launch(i)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        s.record(stream)
+        for i in range(steps):
+            launch(i)
+        e.record(stream)
+        torch.cuda.synchronize()
+    us = s.elapsed_time(e) * 1e3 / steps
+    bytes_ = 4 * n * 2 + hidden * 4
+    return {"us": us, "gbs": bytes_ / (us * 1e-6) / 1e9, "bytes": bytes_, "launches": steps}
+
+
+def time_chain(torch, pkg, ranks, steps, warmup, global_batch=256):
+    """ResNet-50-shaped FP16 chain, one CUDA graph per replica, batch sharded contiguously over the ranks."""
+    from cuda_inference_b200.chain import ConvChain, shard_batch
+    _, count = shard_batch(global_batch, ranks.world, ranks.rank)
+    chain = ConvChain(max(count, 1), 1, 224, seed=0)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(100 + ranks.rank)
+    chain.input.copy_(torch.randn(chain.input.numel(), device="cuda", generator=g).to(torch.float16))
+    stream = torch.cuda.Stream()
+    chain.capture(stream)
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, warmup)):
+            chain.replay()
+        stream.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ranks.barrier()
+        torch.cuda.synchronize()
+        s.record(stream)
+        for _ in range(steps):
+            chain.replay()
+        e.record(stream)
+        torch.cuda.synchronize()
+        ranks.barrier()
+    ms = ranks.max(s.elapsed_time(e))
+    assert chain.device_status() == 0
+    finite = bool(torch.isfinite(chain.output.float()).all().item())
+    per_pass_ms = ms / steps
+    return {"images_per_s": global_batch / (per_pass_ms * 1e-3), "ms_per_pass": per_pass_ms, "global_batch": global_batch,
+            "images_per_rank": count, "tflops": (chain.flops / max(count, 1)) * global_batch / (per_pass_ms * 1e-3) / 1e12,
+            "launches_per_pass": chain.launches, "graph": "one CUDA graph per replica", "output_finite": finite, "steps": steps}
+
+
 # ------------------------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------------------------
@@ -265,23 +332,13 @@ def cpu_baseline_leg(torch, shape, host_inputs, gpu_y, budget_s=12.0):
 
 def run_ours(args):
     import torch
-    import torch.distributed as dist
 
     rank, local_rank, world = dist_env()
     torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-
-    def max_over_ranks(v):
-        if world == 1:
-            return float(v)
-        t = torch.tensor([float(v)], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    entry.load_package()
+    from cuda_inference_b200.dist import Ranks
+    ranks = Ranks("nccl")
+    barrier, max_over_ranks = ranks.barrier, ranks.max
 
     pkg = entry.load_package()
     from cuda_inference_b200 import workloads as wl
@@ -321,19 +378,47 @@ def run_ours(args):
         "dtype": {0: "fp32", 1: "fp16", 2: "bf16"}[shape.precision] + " (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"{args.workload}: N={shape.batch} C={shape.in_channels} {shape.in_h}x{shape.in_w} K={shape.out_channels} "
                                f"{shape.kernel}x{shape.kernel}/s{shape.stride} p{shape.pad} NCHW, fused bias+ReLU",
-                   "tile": {"tile_n": plan.info.cfg.tile_n, "tile_k": plan.info.cfg.tile_k, "stages": plan.info.cfg.stages,
+                   "tile": {"tile_m": plan.info.cfg.tile_m, "tile_n": plan.info.cfg.tile_n, "tile_k": plan.info.cfg.tile_k, "stages": plan.info.cfg.stages,
                             "split_k": plan.info.cfg.split_k},
                    "cold_cache": f"inputs larger than L2: {res['nsets']} rotating buffer sets, {res['rotation_bytes'] / 1e6:.0f} MB",
                    "launch": "CUDA graph of one buffer rotation, replayed", "replicas": world},
         "roofline": roof, "e2e": e2e, "gpu_launches": res["launches"], "clocks": clocks,
     }
+    # Secondary measurements (not the headline): the other benchmark shapes on one GPU, and the conv chain on all ranks.
+    if not args.no_secondary:
+        sec = {}
+        if world == 1:
+            for name in ("c1", "c3_fp16", "c3_bf16", "c4a", "c4b"):
+                if name == args.workload:
+                    continue
+                sh, bd = wl.CONV_WORKLOADS[name]
+                r2 = time_conv(torch, pkg, sh, min(args.steps, 2000), 20, 1, lambda: None, float)
+                k_us = r2["stage_ms"][1] * 1e3
+                entry_ = {"us_per_step": r2["ms"] * 1e3 / min(args.steps, 2000), "tflops": sh.flops * min(args.steps, 2000) / (r2["ms"] * 1e-3) / 1e12,
+                          "kernel_us": k_us, "repack_us": r2["stage_ms"][0] * 1e3, "bound": bd,
+                          "tile": [r2["plan"].info.cfg.tile_m, r2["plan"].info.cfg.tile_n, r2["plan"].info.cfg.tile_k, r2["plan"].info.cfg.stages,
+                                   r2["plan"].info.cfg.split_k]}
+                if bd == "hbm":
+                    entry_["pipeline_gbs"] = sh.algorithmic_bytes / (entry_["us_per_step"] * 1e-6) / 1e9
+                    entry_["frac_of_hbm"] = entry_["pipeline_gbs"] / peaks["hbm_gbs"]
+                elif bd == "tensor":
+                    entry_["frac_of_tensor"] = entry_["tflops"] / peaks["bf16_tflops"]
+                sec[name] = entry_
+                del r2
+                torch.cuda.empty_cache()
+            rms = time_rmsnorm(torch, pkg, min(args.steps, 300), 10)
+            rms["frac_of_hbm"] = rms["gbs"] / peaks["hbm_gbs"]
+            sec["rmsnorm_bf16_8192x4096_residual"] = rms
+            torch.cuda.empty_cache()
+        ch = time_chain(torch, pkg, ranks, steps=max(3, min(args.steps, 10)), warmup=3)
+        ch["frac_of_tensor"] = ch["tflops"] / world / peaks["bf16_tflops"]
+        sec["chain_resnet50_fp16_batch256"] = ch
+        out["secondary"] = sec
     if world == 1 and rank == 0 and not args.no_cpu:
         out["cpu_baseline"] = cpu_baseline_leg(torch, shape, host[:3], host[3])
     if rank == 0:
         print(json.dumps(out))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    ranks.close()
 
 
 # ------------------------------------------------------------------------------------------------------------------
@@ -395,6 +480,7 @@ def main():
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (other shapes, RMSNorm, conv chain)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

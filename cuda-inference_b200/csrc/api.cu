@@ -97,7 +97,10 @@ int validate(const gieb_conv_desc* d) {
 // the slowest CTA: per reduction slab max(tensor-pipe time, shared-memory read time), plus fixed prologue/epilogue
 // cost, plus (for split-K) writing and re-reading FP32 partials and the extra launch.
 struct Resolved {
-  int variant;  // 1 tensor path with im2col-mode TMA, 4 tensor path with tiled TMA (1x1, stride 1, pad 0), 3 FP32 SIMT
+  // 1 tensor path with im2col-mode TMA; 4 tensor path with tiled TMA over the NHWC copy (1x1, stride 1, pad 0);
+  // 2 tensor path reading the caller's NCHW activations directly (1x1, stride 1, pad 0, H*W % 8 == 0); 3 FP32 SIMT
+  int variant;
+  int boxes_per_image;  // variant 2: ceil(H*W / 64)
   int tile_m, tile_n, tile_k, stages, split_k;
   int c_padded, kb_per_tap, total_kb, kb_per_split;
   int tiles_m, tiles_n;
@@ -191,9 +194,15 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
     return GIEB_OK;
   }
   const bool pointwise = d.kernel_h == 1 && d.kernel_w == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_h == 0 && d.pad_w == 0;
-  if (c.variant != 0 && c.variant != 1 && c.variant != 4) return no("unknown kernel variant for 16-bit precision (1 = im2col-mode TMA, 4 = tiled TMA for 1x1)");
+  const bool direct_ok = pointwise && (d.in_h * d.in_w) % 8 == 0;
+  if (c.variant != 0 && c.variant != 1 && c.variant != 2 && c.variant != 4)
+    return no("unknown kernel variant for 16-bit precision (1 = im2col-mode TMA, 2 = direct NCHW 1x1, 4 = tiled TMA for 1x1)");
   if (c.variant == 4 && !pointwise) return no("variant 4 (tiled activation loads) needs a 1x1 kernel with stride 1 and no padding");
-  r->variant = (pointwise && c.variant != 1) ? 4 : 1;
+  if (c.variant == 2 && !direct_ok) return no("variant 2 (direct NCHW loads) needs a 1x1 kernel, stride 1, no padding and H*W % 8 == 0");
+  r->variant = c.variant ? c.variant : (direct_ok ? 2 : (pointwise ? 4 : 1));
+  r->boxes_per_image = ceil_div(int64_t(d.in_h) * d.in_w, 64);
+  // GEMM rows: output pixels, or (variant 2) 64-pixel boxes that never straddle an image
+  const int64_t rows = r->variant == 2 ? int64_t(d.batch) * r->boxes_per_image * 64 : g.pixels;
 
   // hardware limits of the im2col-mode tensor map (rank 4): traversal strides 1..8, corners and offsets 8-bit
   if (d.stride_h > 8 || d.stride_w > 8) return no("stride > 8 cannot be expressed by the TMA im2col traversal stride");
@@ -226,7 +235,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
         if (c.split_k && s != c.split_k) continue;
         if (s > 1 && r->total_kb < 2 * s) break;  // reduction too short (src/kernels/tensor_core_mma.cu:292 rule)
         if (s > 1 && size_t(s) * size_t(g.y_elems) * 4 > (size_t(1) << 31)) break;
-        const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s);
+        const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s) + (r->variant == 2 && tn < d.out_channels && tn < 256 ? 1e6 : 0.0);
         if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; }
       }
     }
@@ -239,7 +248,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   r->tile_n = best_n;
   r->kb_per_split = ceil_div(r->total_kb, best_s);
   r->split_k = ceil_div(r->total_kb, r->kb_per_split);  // every slice non-empty
-  r->tiles_m = ceil_div(g.pixels, r->tile_m);
+  r->tiles_m = ceil_div(rows, r->tile_m);
   r->tiles_n = ceil_div(d.out_channels, r->tile_n);
   if (r->tiles_n > 65535 || r->split_k > 65535) return no("grid limit exceeded");
 
@@ -334,12 +343,23 @@ struct gieb_conv_plan {
 
 namespace {
 
-int encode_maps(const gieb_conv_plan* pl, const void* xn, const void* wk, CUtensorMap* tm_act, CUtensorMap* tm_wgt) {
+// mode: 0 im2col over the NHWC copy `xn`, 1 tiled over the NHWC copy, 2 tiled straight over the caller's NCHW tensor `xn`.
+int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* wk, CUtensorMap* tm_act, CUtensorMap* tm_wgt) {
   const gieb_conv_desc& d = pl->desc;
   const Resolved& r = pl->r;
   const CUtensorMapDataType dt = d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUtensorMapSwizzle sw = swizzle_for(r.tile_k);
-  if (r.variant == 4) {  // 1x1 / stride 1 / pad 0: the NHWC copy is the GEMM operand [pixels][Cp] itself
+  if (mode == 2) {  // NCHW seen as {HW, C, N}: one box = 64 pixels (128 bytes, the swizzle span) x tile_k channels
+    const cuuint64_t hw = cuuint64_t(d.in_h) * d.in_w;
+    const cuuint64_t dims[3] = {hw, cuuint64_t(d.in_channels), cuuint64_t(d.batch)};
+    const cuuint64_t strides[2] = {hw * 2, hw * d.in_channels * 2};
+    const cuuint32_t box[3] = {64, cuuint32_t(r.tile_k), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult res = g_encode_tiled(tm_act, dt, 3, const_cast<void*>(xn), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (NCHW activations) failed with CUresult %d", int(res));
+    small_tensor_fixup(tm_act, size_t(hw) * d.in_channels * d.batch * 2);
+  } else if (mode == 1) {  // 1x1 / stride 1 / pad 0: the NHWC copy is the GEMM operand [pixels][Cp] itself
     const cuuint64_t dims[2] = {cuuint64_t(r.c_padded), cuuint64_t(d.batch) * d.in_h * d.in_w};
     const cuuint64_t strides[1] = {cuuint64_t(r.c_padded) * 2};
     const cuuint32_t box[2] = {cuuint32_t(r.tile_k), cuuint32_t(kTileM)};
@@ -412,12 +432,20 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   else if (reinterpret_cast<uintptr_t>(w) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "prepacked weights must be 16-byte aligned");
   float* part = r.split_k > 1 ? reinterpret_cast<float*>(wsb + r.ws_x + r.ws_w) : nullptr;
 
+  // A direct-NCHW plan needs a 16-byte aligned x (TMA base address rule); otherwise this call takes the repack route.
+  int mode = r.variant == 1 ? 0 : (r.variant == 4 ? 1 : 2);
+  if (mode == 2 && reinterpret_cast<uintptr_t>(x) % 16 != 0) mode = 1;
+  const int64_t rows = mode == 2 ? int64_t(d.batch) * r.boxes_per_image * 64 : pl->g.pixels;
+
   CUtensorMap tm_act, tm_wgt;
-  const int st_maps = encode_maps(pl, xn, wk, &tm_act, &tm_wgt);
+  const int st_maps = encode_maps(pl, mode, mode == 2 ? x : xn, wk, &tm_act, &tm_wgt);
   if (st_maps != GIEB_OK) return st_maps;
 
   if (ev) GIEB_CUDA(cudaEventRecord(ev[0], st));
-  if (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)
+  if (mode == 2) {
+    if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED))
+      GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, 1, r.c_padded, st));
+  } else if (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)
     GIEB_CUDA(repack_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, st));
   else
     GIEB_CUDA(repack_pair_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, w, const_cast<void*>(wk),
@@ -425,7 +453,9 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
 
   ConvTcParams p;
   memset(&p, 0, sizeof(p));
-  p.m_total = int(pl->g.pixels);
+  p.m_total = int(rows);
+  p.y_elems = pl->g.y_elems;
+  p.boxes_per_image = r.boxes_per_image;
   p.out_channels = d.out_channels;
   p.out_h = pl->g.out_h;
   p.out_w = pl->g.out_w;
@@ -440,13 +470,13 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.relu = d.relu; p.has_bias = d.has_bias;
   p.is_bf16 = d.precision == GIEB_BF16;
   p.bias_fp32 = (d.flags & GIEB_FLAG_BIAS_FP32) ? 1 : 0;
-  p.a_tiled = r.variant == 4 ? 1 : 0;
-  p.idesc = ptx::make_idesc_f16(kTileM, r.tile_n, p.is_bf16, false, false);
+  p.a_mode = mode;
+  p.idesc = ptx::make_idesc_f16(kTileM, r.tile_n, p.is_bf16, mode == 2, false);
   p.bias = bias;
   p.y = y;
   p.partial = part;
   p.status = pl->d_status;
-  dim3 grid(unsigned(r.tiles_m), unsigned(r.tiles_n), unsigned(r.split_k));
+  dim3 grid(unsigned(ceil_div(rows, r.tile_m)), unsigned(r.tiles_n), unsigned(r.split_k));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[1], st));
   GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, tm_act, tm_wgt, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));

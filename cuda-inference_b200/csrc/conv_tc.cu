@@ -122,7 +122,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 #pragma unroll
         for (int h = 0; h < MH; ++h)
           if (h < halves) {
-            if (p.a_tiled)
+            if (p.a_mode == 2) {
+              // two boxes of 64 pixels x BK channels each, [channel][pixel] in shared memory
+              const int box0 = (m0 + h * kTileM) >> 6;
+#pragma unroll
+              for (int b = 0; b < 2; ++b) {
+                const int box = box0 + b;
+                const int bimg = box / p.boxes_per_image;
+                const int bpix = (box - bimg * p.boxes_per_image) << 6;
+                ptx::tma_load_3d(a_dst + h * A_HALF_BYTES + b * (A_HALF_BYTES / 2), &tm_act, &full_bar[s], bpix, cb * BK, bimg);
+              }
+            } else if (p.a_mode == 1)
               ptx::tma_load_2d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, m0 + h * kTileM);
             else
               ptx::tma_load_im2col_4d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, base_w[h], base_h[h], img[h],
@@ -146,8 +156,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           if (h < halves) {
 #pragma unroll
             for (int k = 0; k < MMAS_PER_SLAB; ++k) {
-              ptx::mma_f16_ss(tmem_base + h * BN, ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32),
-                              ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32), p.idesc, (i | k) != 0);
+              // K-major A: 16 channels = 32 bytes along a row.  Pixel-major A (mode 2): 16 channels = 16 rows of 128 B.
+              const uint64_t adesc = p.a_mode == 2
+                                         ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
+                                         : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
+              ptx::mma_f16_ss(tmem_base + h * BN, adesc, ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32), p.idesc, (i | k) != 0);
             }
           }
         }
@@ -164,11 +177,20 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     if (__all_sync(0xffffffffu, ok)) {
      for (int h = 0; h < halves; ++h) {
       const int m = m0 + h * kTileM + quad * 32 + lane;
-      const bool m_ok = m < p.m_total;
-      const int img = m_ok ? m / p.pq : 0;
-      const int pix = m_ok ? m - img * p.pq : 0;
+      bool m_ok = m < p.m_total;
+      int img = 0, pix = 0;
+      if (p.a_mode == 2) {  // rows are numbered in 64-pixel boxes per image
+        const int box = m >> 6;
+        img = box / p.boxes_per_image;
+        pix = ((box - img * p.boxes_per_image) << 6) + (m & 63);
+        m_ok = m_ok && pix < p.pq;
+        if (!m_ok) img = pix = 0;
+      } else if (m_ok) {
+        img = m / p.pq;
+        pix = m - img * p.pq;
+      }
       const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
-      const int64_t total = int64_t(p.m_total) * p.out_channels;
+      const int64_t total = p.y_elems;
       float* part = p.partial ? p.partial + int64_t(blockIdx.z) * ((total + 3) & ~int64_t(3)) : nullptr;
 #pragma unroll 1
       for (int chunk = 0; chunk < BN / 32; ++chunk) {

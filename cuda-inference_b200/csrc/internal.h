@@ -21,7 +21,8 @@ constexpr int kTcThreads = 192;    // warp 0: TMA producer, warp 1: MMA issuer +
 
 // Everything the tensor-core kernel needs besides the two tensor maps.  Plain data, passed by value.
 struct ConvTcParams {
-  int m_total;        // B * P * Q output pixels (GEMM M)
+  int m_total;        // GEMM rows: B * P * Q output pixels (modes 0, 1) or box-numbered rows (mode 2)
+  int64_t y_elems;    // B * O * P * Q
   int out_channels;   // O (GEMM N)
   int out_h, out_w;   // P, Q
   int pq;             // P * Q
@@ -33,7 +34,14 @@ struct ConvTcParams {
   int stride_h, stride_w, pad_h, pad_w;
   int stages;
   int relu, has_bias, is_bf16, bias_fp32;
-  int a_tiled;        // 1x1 / stride 1 / pad 0: activations are the plain matrix [pixels][c_padded], fetched with tiled loads
+  // How the activation operand reaches shared memory:
+  //   0  im2col-mode TMA over the channel-padded NHWC copy (any kernel / stride / padding)
+  //   1  tiled TMA over the same copy seen as the matrix [pixels][c_padded] (1x1, stride 1, pad 0)
+  //   2  tiled TMA straight from the caller's NCHW tensor, pixels contiguous (MN-major operand; 1x1, stride 1,
+  //      pad 0, H*W % 8 == 0, 16-byte aligned x): no repack of the activations at all.  Rows of the GEMM are then
+  //      numbered in 64-pixel boxes that never straddle an image: m_total = batch * boxes_per_image * 64.
+  int a_mode;
+  int boxes_per_image;  // mode 2: ceil(H*W / 64)
   uint32_t idesc;
   const void* bias;
   void* y;            // NCHW output in the storage type (split_k == 1)

@@ -72,8 +72,11 @@ typedef struct gieb_conv_cfg {
   int32_t tile_k;   /* reduction slab in channels: 16, 32 or 64; 0 = auto                                    */
   int32_t stages;   /* shared-memory ring depth, 2..8; 0 = auto                                              */
   int32_t split_k;  /* number of reduction splits, >= 1; 0 = auto                                            */
-  int32_t variant;  /* 0 = auto, 1 = tensor path with im2col-mode TMA, 4 = tensor path with tiled TMA (1x1, stride 1,
-                       pad 0 only), 3 = FP32 SIMT                                                            */
+  int32_t variant;  /* 0 = auto; 1 = tensor path, im2col-mode TMA over the channel-contiguous copy (any geometry);
+                       4 = tensor path, tiled TMA over that copy (1x1, stride 1, pad 0);
+                       2 = tensor path reading the caller's NCHW activations directly, no activation repack
+                           (1x1, stride 1, pad 0, H*W % 8 == 0; a call whose x is not 16-byte aligned takes route 4);
+                       3 = FP32 SIMT                                                                          */
   int32_t tile_m;   /* output pixels per CTA tile: 128 or 256 (two accumulators share each weight tile); 0 = auto */
   int32_t reserved[2];
 } gieb_conv_cfg;

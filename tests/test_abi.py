@@ -68,6 +68,9 @@ def test_query_precision_routing_and_reasons(pkg):
     assert i16.supported and i16.variant == 1 and i16.threads_per_block == 192 and i16.padded_channels == 64
     ipw = pkg.query(P(pkg, 2, 64, 14, 14, 64, 1, 1, precision=pkg.BF16))
     assert ipw.supported and ipw.variant == 4                       # 1x1 / stride 1 / pad 0 -> tiled activation loads
+    idr = pkg.query(P(pkg, 2, 64, 28, 28, 64, 1, 1, precision=pkg.BF16))
+    assert idr.supported and idr.variant == 2                       # H*W % 8 == 0 -> straight from NCHW, no activation repack
+    assert not pkg.query(P(pkg, 2, 64, 14, 14, 64, 1, 1, precision=pkg.FP16), pkg.make_cfg(variant=2)).supported
     tf = pkg.query(P(pkg, *base, precision=pkg.TF32))
     assert not tf.supported and b"TF32" in tf.reason
     big_stride = pkg.query(P(pkg, 1, 16, 64, 64, 16, 3, 3, 9, 9, 1, 1, precision=pkg.FP16))
@@ -124,7 +127,8 @@ def test_selection_is_deterministic_and_fills_the_machine(pkg):
         total_kb = a[5] * a[6] * (i1.padded_channels // c.tile_k)
         assert 1 <= c.split_k <= max(1, total_kb // 2)
         pixels = a[0] * p.out_h * p.out_w
-        assert i1.num_blocks == -(-pixels // c.tile_m) * -(-a[4] // c.tile_n) * c.split_k
+        rows = a[0] * -(-(a[2] * a[3]) // 64) * 64 if i1.variant == 2 else pixels   # direct NCHW route counts 64-pixel boxes
+        assert i1.num_blocks == -(-rows // c.tile_m) * -(-a[4] // c.tile_n) * c.split_k
     # the small deep layer gets split-K, the big ones do not
     assert pkg.query(P(pkg, 1, 512, 7, 7, 512, 3, 3, 1, 1, 1, 1, precision=pkg.FP16)).cfg.split_k > 1
     assert pkg.query(P(pkg, 256, 64, 56, 56, 256, 1, 1, precision=pkg.FP16)).cfg.split_k == 1

@@ -92,6 +92,33 @@ def test_explicit_tile_configurations(pkg, orc, oracle, case, prec_name):
     _check(oracle, p, got, ref, scale, f"case {case} {kw} {prec_name}")
 
 
+DIRECT_CASES = [
+    # 1x1 / stride 1 / pad 0 with H*W % 8 == 0: activations are read straight from NCHW (pixel-major operand)
+    ((2, 64, 8, 8, 64, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=64, tile_k=64, stages=2), 0),
+    ((1, 64, 56, 56, 64, 1, 1, 1, 1, 0, 0), dict(variant=2), 0),
+    ((3, 70, 10, 20, 255, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=256, tile_k=32, stages=3), 0),     # C tail, 200 px = 3 boxes + 8
+    ((2, 512, 28, 28, 128, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_m=256, tile_n=128, tile_k=64, stages=2), 0),
+    ((2, 96, 4, 6, 40, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_k=16, tile_n=64, split_k=3, stages=2), 0),  # 24 px per image
+    ((5, 256, 28, 28, 96, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_m=256, tile_n=128, split_k=2, tile_k=64), 0),
+    ((2, 64, 16, 16, 48, 1, 1, 1, 1, 0, 0), dict(variant=2), 1),                                         # x off by 2 bytes: repack route
+    ((2, 64, 16, 16, 48, 1, 1, 1, 1, 0, 0), dict(variant=4), 0),
+    ((2, 64, 16, 16, 48, 1, 1, 1, 1, 0, 0), dict(variant=1), 0),
+]
+
+
+@pytest.mark.parametrize("case", range(len(DIRECT_CASES)))
+@pytest.mark.parametrize("prec_name", ["fp16", "bf16"])
+def test_pointwise_routes(pkg, orc, oracle, case, prec_name):
+    args, kw, xoff = DIRECT_CASES[case]
+    prec = orc.FP16 if prec_name == "fp16" else orc.BF16
+    p = orc.Problem.P(*args, precision=prec, bias=True, relu=(case % 2 == 1))
+    x, w, b = oracle.make_conv_data(p, 2000 + case, case % 4)
+    ref, scale = oracle.conv2d(p, x, w, b)
+    got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b, cfg=pkg.make_cfg(**kw), offsets=(xoff, 0, 0))
+    assert plan.info.variant == kw["variant"]
+    _check(oracle, p, got, ref, scale, f"pointwise case {case} {kw} {prec_name}")
+
+
 def test_baseline_configurations_full_size(pkg, orc, oracle):
     """The benchmark shapes at full size with the benchmark distributions, checked with BOTH tolerances: the
     reference's scale-aware policy and the benchmark's |err| <= a + b*|ref| bounds."""
