@@ -343,6 +343,8 @@ def run_ours(args):
     pkg = entry.load_package()
     from cuda_inference_b200 import workloads as wl
     peaks, peak_kind = load_peaks()
+    if args.workload == "chain":
+        return run_chain_primary(args, torch, pkg, ranks, peaks, peak_kind, local_rank)
     shape, bound = wl.CONV_WORKLOADS[args.workload]
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -421,6 +423,26 @@ def run_ours(args):
     ranks.close()
 
 
+def run_chain_primary(args, torch, pkg, ranks, peaks, peak_kind, local_rank):
+    """`--workload chain`: the conv chain as the headline (images/s, batch 256 sharded over the ranks: strong scaling)."""
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ch = time_chain(torch, pkg, ranks, steps=args.steps, warmup=args.warmup)
+    clocks = sampler.stop()
+    out = {"metric": "conv-chain images/s (ResNet-50-shaped FP16 inference chain, batch 256)", "value": ch["images_per_s"], "unit": "images/s",
+           "n_gpus": ranks.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ch["ms_per_pass"], "higher_is_better": True,
+           "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)", "data": "synthetic",
+           "config": {"workload": "c5: 53-conv ResNet-50-shaped chain, 224x224x3 input N(0,1), batch 256 sharded contiguously over the ranks, "
+                                  "replicated random weights, one CUDA graph per replica", "cold_cache": "activations per pass exceed L2 (5.6 GB)"},
+           "roofline": {"bound": "tensor", "achieved": ch["tflops"] / ranks.world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                        "frac": ch["tflops"] / ranks.world / peaks["bf16_tflops"], "traffic": None, "kernel": "whole chain (per GPU)",
+                        "peak_source": peak_kind},
+           "gpu_launches": ch["launches_per_pass"] * args.steps, "clocks": clocks, "chain": ch}
+    if ranks.rank == 0:
+        print(json.dumps(out))
+    ranks.close()
+
+
 # ------------------------------------------------------------------------------------------------------------------
 # reference arm: the reference's CPU convolution on the host cores
 # ------------------------------------------------------------------------------------------------------------------
@@ -477,7 +499,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20000)
     ap.add_argument("--warmup", type=int, default=200)
-    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--workload", default="c2", help="c1 | c2 | c3_fp16 | c3_bf16 | c4a | c4b | chain")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (other shapes, RMSNorm, conv chain)")

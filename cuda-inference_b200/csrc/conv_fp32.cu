@@ -24,16 +24,22 @@ struct Fp32Args {
   int k;       // c * r * s
 };
 
-template <int TP, int TO>
-__global__ void __launch_bounds__((TP / 4) * (TO / 4))
+// KG = number of thread groups that split the reduction inside one CTA (slab s goes to group s % KG); their partial
+// accumulators are summed in a fixed order at the end, so results are deterministic.  KG > 1 gives small problems
+// (few CTAs, long dependent slab chains) enough warps per SM to hide global-load latency.
+template <int TP, int TO, int KG>
+__global__ void __launch_bounds__((TP / 4) * (TO / 4) * KG)
 conv_fp32_kernel(const Fp32Args a) {
-  constexpr int NT = (TP / 4) * (TO / 4);
-  constexpr int XE = kBK * TP / NT;  // X-slab elements loaded per thread
-  constexpr int WE = kBK * TO / NT;  // W-slab elements loaded per thread
-  __shared__ __align__(16) float xs[kBK][TP];
-  __shared__ __align__(16) float ws[kBK][TO + 4];
+  constexpr int NT = (TP / 4) * (TO / 4);  // threads per group
+  constexpr int XE = kBK * TP / NT;        // X-slab elements loaded per thread
+  constexpr int WE = kBK * TO / NT;        // W-slab elements loaded per thread
+  constexpr int XS_FLOATS = KG * kBK * TP, WS_FLOATS = KG * kBK * (TO + 4);
+  __shared__ __align__(16) float tiles[XS_FLOATS + WS_FLOATS];  // operand tiles; reused for the group reduction
+  float (*xs)[kBK][TP] = reinterpret_cast<float (*)[kBK][TP]>(tiles);
+  float (*ws)[kBK][TO + 4] = reinterpret_cast<float (*)[kBK][TO + 4]>(tiles + XS_FLOATS);
 
-  const int t = threadIdx.x;
+  const int grp = threadIdx.x / NT;
+  const int t = threadIdx.x - grp * NT;
   const int tx = t % (TP / 4), ty = t / (TP / 4);
   const int pix0 = blockIdx.x * TP, oc0 = blockIdx.y * TO;
   const int rs = a.r * a.s;
@@ -79,9 +85,9 @@ conv_fp32_kernel(const Fp32Args a) {
   };
   auto stash = [&]() {
 #pragma unroll
-    for (int i = 0; i < XE; ++i) xs[t / TP + i * (NT / TP)][lp] = xr[i];
+    for (int i = 0; i < XE; ++i) xs[grp][t / TP + i * (NT / TP)][lp] = xr[i];
 #pragma unroll
-    for (int i = 0; i < WE; ++i) ws[wk][t / kBK + i * (NT / kBK)] = wr[i];
+    for (int i = 0; i < WE; ++i) ws[grp][wk][t / kBK + i * (NT / kBK)] = wr[i];
   };
 
   float acc[4][4];
@@ -90,15 +96,17 @@ conv_fp32_kernel(const Fp32Args a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-  fetch(0);
-  for (int k0 = 0; k0 < a.k; k0 += kBK) {
+  // every group runs the same number of rounds (slabs beyond K load zeros), so the barriers stay uniform
+  const int rounds = (a.k + kBK * KG - 1) / (kBK * KG);
+  fetch(grp * kBK);
+  for (int rd = 0; rd < rounds; ++rd) {
     stash();
     __syncthreads();
-    if (k0 + kBK < a.k) fetch(k0 + kBK);
+    if (rd + 1 < rounds) fetch(((rd + 1) * KG + grp) * kBK);
 #pragma unroll
     for (int kk = 0; kk < kBK; ++kk) {
-      const float4 xv = *reinterpret_cast<const float4*>(&xs[kk][tx * 4]);
-      const float4 wv = *reinterpret_cast<const float4*>(&ws[kk][ty * 4]);
+      const float4 xv = *reinterpret_cast<const float4*>(&xs[grp][kk][tx * 4]);
+      const float4 wv = *reinterpret_cast<const float4*>(&ws[grp][kk][ty * 4]);
       const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
       const float wa[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
@@ -107,6 +115,24 @@ conv_fp32_kernel(const Fp32Args a) {
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wa[j], acc[i][j]);
     }
     __syncthreads();
+  }
+
+  if (KG > 1) {  // fold groups 1..KG-1 into group 0, in group order (the operand tiles are free now)
+    float* red = tiles;
+    static_assert(KG == 1 || (KG - 1) * NT * 16 <= XS_FLOATS + WS_FLOATS, "reduction scratch must fit the operand tiles");
+    if (grp > 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) red[((grp - 1) * 16 + i * 4 + j) * NT + t] = acc[i][j];
+    }
+    __syncthreads();
+    if (grp > 0) return;
+    for (int g = 0; g < KG - 1; ++g)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += red[(g * 16 + i * 4 + j) * NT + t];
   }
 
   // Epilogue (fused_epilogue.cuh:11-16 order): + bias, ReLU, store.  Pixels are the fast index of NCHW.
@@ -155,10 +181,10 @@ cudaError_t conv_fp32_launch(const void* x, const void* w, const void* bias, voi
   a.k = c * r * s;
   if (use_small_tile(a.pixels, o)) {
     dim3 grid(unsigned((a.pixels + 31) / 32), unsigned((o + 31) / 32));
-    conv_fp32_kernel<32, 32><<<grid, 64, 0, stream>>>(a);
+    conv_fp32_kernel<32, 32, 4><<<grid, 256, 0, stream>>>(a);
   } else {
     dim3 grid(unsigned((a.pixels + 63) / 64), unsigned((o + 63) / 64));
-    conv_fp32_kernel<64, 64><<<grid, 256, 0, stream>>>(a);
+    conv_fp32_kernel<64, 64, 1><<<grid, 256, 0, stream>>>(a);
   }
   return cudaGetLastError();
 }

@@ -65,27 +65,23 @@ add_relu_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict_
   }
 }
 
-// One thread per output element; consecutive threads walk ow, so window reads are coalesced along w.
+// One thread per output position of a plane (32-bit index arithmetic only), grid.y strides over the B*C planes;
+// consecutive threads walk ow, so window reads are coalesced along w and served from L1 across the 3 taps.
 template <typename T>
 __global__ void __launch_bounds__(256)
-maxpool2d_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t total, int h, int w, int oh, int ow, int k, int stride,
-                 int pad) {
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
-    const int ox = int(i % ow);
-    const int oy = int((i / ow) % oh);
-    const int64_t plane = i / (int64_t(ow) * oh);
-    const T* xp = x + plane * h * w;
+maxpool2d_kernel(const T* __restrict__ x, T* __restrict__ y, int planes, int h, int w, int oh, int ow, int k, int stride, int pad) {
+  const int pos = blockIdx.x * blockDim.x + threadIdx.x;
+  if (pos >= oh * ow) return;
+  const int oy = pos / ow, ox = pos - oy * ow;
+  const int iy0 = oy * stride - pad, ix0 = ox * stride - pad;
+  const int r0 = iy0 < 0 ? -iy0 : 0, r1 = min(k, h - iy0);
+  const int s0 = ix0 < 0 ? -ix0 : 0, s1 = min(k, w - ix0);
+  for (int plane = blockIdx.y; plane < planes; plane += gridDim.y) {
+    const T* xp = x + size_t(plane) * h * w + iy0 * w + ix0;
     float best = -INFINITY;
-    for (int r = 0; r < k; ++r) {
-      const int iy = oy * stride - pad + r;
-      if (iy < 0 || iy >= h) continue;
-      for (int s = 0; s < k; ++s) {
-        const int ix = ox * stride - pad + s;
-        if (ix < 0 || ix >= w) continue;
-        best = fmaxf(best, cvt(xp[iy * w + ix]));
-      }
-    }
-    y[i] = rnd<T>(best);
+    for (int r = r0; r < r1; ++r)
+      for (int s = s0; s < s1; ++s) best = fmaxf(best, cvt(xp[r * w + s]));
+    y[size_t(plane) * oh * ow + pos] = rnd<T>(best);
   }
 }
 
@@ -130,12 +126,14 @@ cudaError_t add_relu_launch(int precision, int relu, const void* a, const void* 
 cudaError_t maxpool2d_launch(int precision, int batch, int channels, int h, int w, int k, int stride, int pad, const void* x,
                              void* y, cudaStream_t st) {
   const int oh = (h + 2 * pad - k) / stride + 1, ow = (w + 2 * pad - k) / stride + 1;
-  const int64_t total = int64_t(batch) * channels * oh * ow;
-  const unsigned g = grid_for(total);
+  const int64_t planes64 = int64_t(batch) * channels;
+  if (planes64 > 2147483647LL || int64_t(oh) * ow > 2147483647LL) return cudaErrorInvalidValue;
+  const int planes = int(planes64);
+  const dim3 g(unsigned((oh * ow + 255) / 256), unsigned(planes < 32768 ? planes : 32768));
   switch (precision) {
-    case 0: maxpool2d_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), total, h, w, oh, ow, k, stride, pad); break;
-    case 1: maxpool2d_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), total, h, w, oh, ow, k, stride, pad); break;
-    case 2: maxpool2d_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), total, h, w, oh, ow, k, stride, pad); break;
+    case 0: maxpool2d_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), planes, h, w, oh, ow, k, stride, pad); break;
+    case 1: maxpool2d_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(y), planes, h, w, oh, ow, k, stride, pad); break;
+    case 2: maxpool2d_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), planes, h, w, oh, ow, k, stride, pad); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
