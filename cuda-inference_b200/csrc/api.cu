@@ -122,9 +122,16 @@ constexpr double kFeedBytesPerClk = 48.0;
 
 size_t stage_bytes_of(int tile_m, int tile_n, int tile_k) { return size_t(tile_m + tile_n) * tile_k * 2; }
 
+// TMEM columns one CTA allocates: one accumulator set per 128-pixel half, doubled when two sets fit 256 columns.
+int tmem_cols_of(int tile_m, int tile_n) {
+  const int one = tile_m / kTileM * tile_n;
+  const int cols = one <= 256 ? 2 * one : one;
+  return cols < 32 ? 32 : cols;
+}
+
 int resident_ctas(int tile_m, int tile_n, size_t smem) {
   int by_smem = int(kMaxDynamicSmem / (smem + 1024));
-  int by_tmem = 512 / (tile_m / kTileM * tile_n < 32 ? 32 : tile_m / kTileM * tile_n);
+  int by_tmem = 512 / tmem_cols_of(tile_m, tile_n);
   int r = by_smem < by_tmem ? by_smem : by_tmem;
   return r < 1 ? 1 : (r > 4 ? 4 : r);
 }
@@ -133,11 +140,12 @@ int resident_ctas(int tile_m, int tile_n, size_t smem) {
 // CTAs exists (their epilogues then overlap with another CTA's main loop).
 int pick_stages(int tile_m, int tile_n, int tile_k, int kb_per_split, int64_t ctas) {
   const size_t sb = stage_bytes_of(tile_m, tile_n, tile_k);
-  const int cols = (tile_m / kTileM) * tile_n;
-  // measured: with >= 2.5 CTAs per SM three shallow CTAs per SM beat two deeper ones; between 1 and 2.5 two CTAs win
+  const int by_tmem = 512 / tmem_cols_of(tile_m, tile_n);
+  // measured: with >= 2.5 tiles per SM three shallow CTAs per SM beat two deeper ones; between 1 and 2.5 two CTAs win
   int want = 1;
-  if (ctas * 2 >= 5 * kNumSms && cols <= 128) want = 3;
-  else if (ctas > kNumSms && cols <= 256) want = 2;
+  if (ctas * 2 >= 5 * kNumSms) want = 3;
+  else if (ctas > kNumSms) want = 2;
+  if (want > by_tmem) want = by_tmem;
   const size_t budget = want == 1 ? kSmemBudget : (kMaxDynamicSmem / want - 2048);
   int stages = int((budget - 3072) / sb);
   if (stages > 6) stages = 6;
@@ -250,7 +258,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   r->split_k = ceil_div(r->total_kb, r->kb_per_split);  // every slice non-empty
   r->tiles_m = ceil_div(rows, r->tile_m);
   r->tiles_n = ceil_div(d.out_channels, r->tile_n);
-  if (r->tiles_n > 65535 || r->split_k > 65535) return no("grid limit exceeded");
+  if (int64_t(r->tiles_m) * r->tiles_n * r->split_k > 2147483647LL) return no("tile count exceeds 32-bit indexing");
 
   const int stages = c.stages ? c.stages
                               : pick_stages(r->tile_m, r->tile_n, r->tile_k, r->kb_per_split, int64_t(r->tiles_m) * r->tiles_n * r->split_k);
@@ -476,7 +484,12 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.y = y;
   p.partial = part;
   p.status = pl->d_status;
-  dim3 grid(unsigned(ceil_div(rows, r.tile_m)), unsigned(r.tiles_n), unsigned(r.split_k));
+  p.tiles_m = ceil_div(rows, r.tile_m);
+  p.tiles_n = r.tiles_n;
+  p.num_tiles = p.tiles_m * p.tiles_n * r.split_k;
+  // persistent CTAs: as many as can be resident at once, each walking the tile list
+  const int64_t resident = int64_t(kNumSms) * resident_ctas(r.tile_m, r.tile_n, r.smem);
+  dim3 grid(unsigned(p.num_tiles < resident ? p.num_tiles : resident));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[1], st));
   GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, tm_act, tm_wgt, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));

@@ -11,7 +11,7 @@
 //   * Both land in shared memory in the 128/64/32-byte swizzled K-major layout tcgen05.mma reads, in a ring of
 //     `stages` buffers guarded by full/empty mbarriers.
 //   * One thread issues tcgen05.mma (128 x BN x 16 per instruction); the FP32 accumulator tile lives in tensor
-//     memory: lane = pixel, column = output channel.
+//     memory: lane = pixel, column = output channel.  CTAs are persistent and the accumulator is double-buffered.
 //   * Four epilogue warps read the accumulators with tcgen05.ld, add bias, apply ReLU, round once to the storage
 //     type and store to NCHW: for a fixed channel the 32 lanes of a warp hold 32 consecutive pixels, so every store
 //     instruction writes one contiguous run.  With split-K the FP32 partial tile is stored instead.
@@ -26,10 +26,14 @@
 namespace gieb {
 namespace {
 
-constexpr uint32_t kCtrlBytes = 2048;  // [0,1024): bias tile as float; [1024,2048): mbarriers + TMEM address slot
+constexpr uint32_t kCtrlBytes = 3072;  // [0,2048): two bias tiles as float; [2048,3072): mbarriers + TMEM address slot
 
-// MH = number of 128-pixel halves a CTA computes (1 or 2).  With MH = 2 the CTA owns a 256-pixel tile: two
-// activation loads and two accumulators share every weight tile, which halves the weight traffic per FLOP.
+// Persistent CTAs: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; output-channel tiles fastest, then
+// pixel tiles, then split-K slices).  The operand ring and its phases run on across tiles, and the accumulator is
+// double-buffered in tensor memory whenever two tiles fit the 512 columns, so the epilogue of tile t overlaps the
+// loads and MMAs of tile t+1.
+// MH = number of 128-pixel halves per tile (1 or 2).  With MH = 2 the tile is 256 pixels: two activation loads and two
+// accumulators share every weight tile, which halves the weight traffic per FLOP.
 template <int BN, int BK, int MH>
 __global__ void __launch_bounds__(kTcThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_wgt,
@@ -40,26 +44,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   constexpr uint32_t B_BYTES = BN * ROW_BYTES;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int MMAS_PER_SLAB = BK / 16;
-  constexpr uint32_t TMEM_COLS = MH * BN < 32 ? 32 : MH * BN;
-  static_assert(MH * BN <= 512, "accumulators must fit the 512 TMEM columns");
+  constexpr uint32_t ACC_COLS = MH * BN;                       // columns of one accumulator set
+  constexpr int ACC_BUFS = ACC_COLS <= 256 ? 2 : 1;            // double-buffer when it fits
+  constexpr uint32_t TMEM_COLS = ACC_COLS * ACC_BUFS < 32 ? 32 : ACC_COLS * ACC_BUFS;
+  static_assert(TMEM_COLS <= 512, "accumulators must fit the 512 TMEM columns");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
-  float* bias_s = reinterpret_cast<float*>(smem);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + 1024);
+  float* bias_s = reinterpret_cast<float*>(smem);  // [2][256]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + 2048);
   uint64_t* empty_bar = full_bar + kMaxStages;
-  uint64_t* accum_bar = empty_bar + kMaxStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  uint64_t* acc_full = empty_bar + kMaxStages;     // [2] MMA -> epilogue: accumulator complete
+  uint64_t* acc_empty = acc_full + 2;              // [2] epilogue -> MMA: accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   uint8_t* stage_base = smem + kCtrlBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * (kTileM * MH);
-  const int n0 = blockIdx.y * BN;
-  const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;  // a trailing tile may own one half only
-  const int kb_begin = blockIdx.z * p.kb_per_split;
-  const int kb_end = min(p.total_kb, kb_begin + p.kb_per_split);
-  const int num_kb = kb_end - kb_begin;
   const int stages = p.stages;
+  const int tiles_mn = p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_act);
@@ -68,24 +70,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       ptx::mbar_init(&full_bar[s], 1);
       ptx::mbar_init(&empty_bar[s], 1);
     }
-    ptx::mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
     ptx::fence_mbar_init();
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, TMEM_COLS);
     ptx::tmem_relinquish();
-  }
-  if (warp >= 2) {  // stage this tile's bias as float
-    for (int i = threadIdx.x - 64; i < BN; i += kTcThreads - 64) {
-      const int oc = n0 + i;
-      float b = 0.f;
-      if (p.has_bias && p.partial == nullptr && oc < p.out_channels) {
-        if (p.bias_fp32) b = static_cast<const float*>(p.bias)[oc];
-        else if (p.is_bf16) b = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[oc]);
-        else b = __half2float(static_cast<const __half*>(p.bias)[oc]);
-      }
-      bias_s[i] = b;
-    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -95,135 +88,195 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      int img[MH], base_w[MH], base_h[MH];
+      int it = 0;  // slabs issued so far by this CTA: ring slot and phase continue across tiles
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
+        const int z = tile / tiles_mn;
+        const int rest = tile - z * tiles_mn;
+        const int m_blk = rest / p.tiles_n;
+        const int n0 = (rest - m_blk * p.tiles_n) * BN;
+        const int m0 = m_blk * (kTileM * MH);
+        const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;  // a trailing tile may own one half only
+        const int kb_begin = z * p.kb_per_split;
+        const int num_kb = min(p.total_kb, kb_begin + p.kb_per_split) - kb_begin;
+        int img[MH], base_w[MH], base_h[MH];
 #pragma unroll
-      for (int h = 0; h < MH; ++h) {
-        const int mh = m0 + h * kTileM;
-        img[h] = mh / p.pq;
-        const int rem = mh - img[h] * p.pq;
-        const int p0 = rem / p.out_w;
-        const int q0 = rem - p0 * p.out_w;
-        base_w[h] = q0 * p.stride_w - p.pad_w;
-        base_h[h] = p0 * p.stride_h - p.pad_h;
-      }
-      const uint32_t tx_bytes = uint32_t(halves) * A_HALF_BYTES + B_BYTES;
-      for (int i = 0; i < num_kb; ++i) {
-        const int s = i % stages;
-        const uint32_t phase = (i / stages) & 1;
-        if (!ptx::mbar_wait(&empty_bar[s], phase ^ 1u, p.status, kStatusProducerTimeout)) break;
-        const int kb = kb_begin + i;
-        const int tap = kb / p.kb_per_tap;
-        const int cb = kb - tap * p.kb_per_tap;
-        const int r = tap / p.kernel_w;
-        const int sx = tap - r * p.kernel_w;
-        uint8_t* a_dst = stage_base + size_t(s) * STAGE_BYTES;
-        uint8_t* b_dst = a_dst + A_BYTES;
-        ptx::mbar_arrive_expect_tx(&full_bar[s], tx_bytes);
+        for (int h = 0; h < MH; ++h) {
+          const int mh = m0 + h * kTileM;
+          img[h] = mh / p.pq;
+          const int rem = mh - img[h] * p.pq;
+          const int p0 = rem / p.out_w;
+          const int q0 = rem - p0 * p.out_w;
+          base_w[h] = q0 * p.stride_w - p.pad_w;
+          base_h[h] = p0 * p.stride_h - p.pad_h;
+        }
+        const uint32_t tx_bytes = uint32_t(halves) * A_HALF_BYTES + B_BYTES;
+        for (int i = 0; i < num_kb; ++i, ++it) {
+          const int s = it % stages;
+          const uint32_t phase = (it / stages) & 1;
+          if (!ptx::mbar_wait(&empty_bar[s], phase ^ 1u, p.status, kStatusProducerTimeout)) { alive = false; break; }
+          const int kb = kb_begin + i;
+          const int tap = kb / p.kb_per_tap;
+          const int cb = kb - tap * p.kb_per_tap;
+          const int r = tap / p.kernel_w;
+          const int sx = tap - r * p.kernel_w;
+          uint8_t* a_dst = stage_base + size_t(s) * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_BYTES;
+          ptx::mbar_arrive_expect_tx(&full_bar[s], tx_bytes);
 #pragma unroll
-        for (int h = 0; h < MH; ++h)
-          if (h < halves) {
-            if (p.a_mode == 2) {
-              // two boxes of 64 pixels x BK channels each, [channel][pixel] in shared memory
-              const int box0 = (m0 + h * kTileM) >> 6;
+          for (int h = 0; h < MH; ++h) {
+            if (h < halves) {
+              if (p.a_mode == 2) {
+                // two boxes of 64 pixels x BK channels each, [channel][pixel] in shared memory
+                const int box0 = (m0 + h * kTileM) >> 6;
 #pragma unroll
-              for (int b = 0; b < 2; ++b) {
-                const int box = box0 + b;
-                const int bimg = box / p.boxes_per_image;
-                const int bpix = (box - bimg * p.boxes_per_image) << 6;
-                ptx::tma_load_3d(a_dst + h * A_HALF_BYTES + b * (A_HALF_BYTES / 2), &tm_act, &full_bar[s], bpix, cb * BK, bimg);
+                for (int b = 0; b < 2; ++b) {
+                  const int box = box0 + b;
+                  const int bimg = box / p.boxes_per_image;
+                  const int bpix = (box - bimg * p.boxes_per_image) << 6;
+                  ptx::tma_load_3d(a_dst + h * A_HALF_BYTES + b * (A_HALF_BYTES / 2), &tm_act, &full_bar[s], bpix, cb * BK, bimg);
+                }
+              } else if (p.a_mode == 1) {
+                ptx::tma_load_2d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, m0 + h * kTileM);
+              } else {
+                ptx::tma_load_im2col_4d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, base_w[h], base_h[h], img[h],
+                                        uint16_t(sx), uint16_t(r));
               }
-            } else if (p.a_mode == 1)
-              ptx::tma_load_2d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, m0 + h * kTileM);
-            else
-              ptx::tma_load_im2col_4d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, base_w[h], base_h[h], img[h],
-                                      uint16_t(sx), uint16_t(r));
+            }
           }
-        ptx::tma_load_2d(b_dst, &tm_wgt, &full_bar[s], tap * p.c_padded + cb * BK, n0);
+          ptx::tma_load_2d(b_dst, &tm_wgt, &full_bar[s], tap * p.c_padded + cb * BK, n0);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      for (int i = 0; i < num_kb; ++i) {
-        const int s = i % stages;
-        const uint32_t phase = (i / stages) & 1;
-        if (!ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout)) break;
+      int it = 0, tcount = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+        const int z = tile / tiles_mn;
+        const int rest = tile - z * tiles_mn;
+        const int m0 = (rest / p.tiles_n) * (kTileM * MH);
+        const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;
+        const int kb_begin = z * p.kb_per_split;
+        const int num_kb = min(p.total_kb, kb_begin + p.kb_per_split) - kb_begin;
+        const int buf = tcount % ACC_BUFS;
+        const uint32_t acc_phase = (tcount / ACC_BUFS) & 1;
+        // the epilogue must have drained this accumulator set (first use passes at once)
+        if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1u, p.status, kStatusMmaTimeout)) break;
         ptx::tc_fence_after_sync();
-        const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
-        const uint32_t b_addr = a_addr + A_BYTES;
+        const uint32_t acc = tmem_base + buf * ACC_COLS;
+        for (int i = 0; i < num_kb; ++i, ++it) {
+          const int s = it % stages;
+          const uint32_t phase = (it / stages) & 1;
+          if (!ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout)) { alive = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-        for (int h = 0; h < MH; ++h) {
-          if (h < halves) {
+          for (int h = 0; h < MH; ++h) {
+            if (h < halves) {
 #pragma unroll
-            for (int k = 0; k < MMAS_PER_SLAB; ++k) {
-              // K-major A: 16 channels = 32 bytes along a row.  Pixel-major A (mode 2): 16 channels = 16 rows of 128 B.
-              const uint64_t adesc = p.a_mode == 2
-                                         ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
-                                         : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
-              ptx::mma_f16_ss(tmem_base + h * BN, adesc, ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32), p.idesc, (i | k) != 0);
+              for (int k = 0; k < MMAS_PER_SLAB; ++k) {
+                // K-major A: 16 channels = 32 bytes along a row.  Pixel-major A (mode 2): 16 channels = 16 rows of 128 B.
+                const uint64_t adesc = p.a_mode == 2
+                                           ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
+                                           : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
+                ptx::mma_f16_ss(acc + h * BN, adesc, ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32), p.idesc, (i | k) != 0);
+              }
             }
           }
+          ptx::mma_commit(&empty_bar[s]);  // frees the slot once these MMAs have read it
         }
-        ptx::mma_commit(&empty_bar[s]);  // frees the slot once these MMAs have read it
+        ptx::mma_commit(&acc_full[buf]);   // accumulator set complete (also reached after a time-out, so nobody hangs)
       }
-      ptx::mma_commit(accum_bar);        // accumulator tile complete
     }
   } else {
     // ---------------- epilogue (warps 2..5 cover TMEM lane quarters 2,3,0,1) ----------------
     const int quad = warp & 3;
-    const bool ok = ptx::mbar_wait(accum_bar, 0, p.status, kStatusEpilogueTimeout);
-    __syncwarp();
-    ptx::tc_fence_after_sync();
-    if (__all_sync(0xffffffffu, ok)) {
-     for (int h = 0; h < halves; ++h) {
-      const int m = m0 + h * kTileM + quad * 32 + lane;
-      bool m_ok = m < p.m_total;
-      int img = 0, pix = 0;
-      if (p.a_mode == 2) {  // rows are numbered in 64-pixel boxes per image
-        const int box = m >> 6;
-        img = box / p.boxes_per_image;
-        pix = ((box - img * p.boxes_per_image) << 6) + (m & 63);
-        m_ok = m_ok && pix < p.pq;
-        if (!m_ok) img = pix = 0;
-      } else if (m_ok) {
-        img = m / p.pq;
-        pix = m - img * p.pq;
+    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    int tcount = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+      const int z = tile / tiles_mn;
+      const int rest = tile - z * tiles_mn;
+      const int m_blk = rest / p.tiles_n;
+      const int n0 = (rest - m_blk * p.tiles_n) * BN;
+      const int m0 = m_blk * (kTileM * MH);
+      const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;
+      const int buf = tcount % ACC_BUFS;
+      const uint32_t acc_phase = (tcount / ACC_BUFS) & 1;
+      float* bias_t = bias_s + (tcount & 1) * 256;
+
+      // stage this tile's bias as float (two buffers: a fast warp may already be one tile ahead of a slow one)
+      for (int i = et; i < BN; i += 128) {
+        const int oc = n0 + i;
+        float b = 0.f;
+        if (p.has_bias && p.partial == nullptr && oc < p.out_channels) {
+          if (p.bias_fp32) b = static_cast<const float*>(p.bias)[oc];
+          else if (p.is_bf16) b = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[oc]);
+          else b = __half2float(static_cast<const __half*>(p.bias)[oc]);
+        }
+        bias_t[i] = b;
       }
-      const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
-      const int64_t total = p.y_elems;
-      float* part = p.partial ? p.partial + int64_t(blockIdx.z) * ((total + 3) & ~int64_t(3)) : nullptr;
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+
+      const bool ok = ptx::mbar_wait(&acc_full[buf], acc_phase, p.status, kStatusEpilogueTimeout);
+      __syncwarp();
+      ptx::tc_fence_after_sync();
+      if (!__all_sync(0xffffffffu, ok)) break;
+      const uint32_t acc = tmem_base + buf * ACC_COLS;
+      float* part = p.partial ? p.partial + int64_t(z) * ((p.y_elems + 3) & ~int64_t(3)) : nullptr;
+      for (int h = 0; h < halves; ++h) {
+        const int m = m0 + h * kTileM + quad * 32 + lane;
+        bool m_ok = m < p.m_total;
+        int img = 0, pix = 0;
+        if (p.a_mode == 2) {  // rows are numbered in 64-pixel boxes per image
+          const int box = m >> 6;
+          img = box / p.boxes_per_image;
+          pix = ((box - img * p.boxes_per_image) << 6) + (m & 63);
+          m_ok = m_ok && pix < p.pq;
+          if (!m_ok) img = pix = 0;
+        } else if (m_ok) {
+          img = m / p.pq;
+          pix = m - img * p.pq;
+        }
+        const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
 #pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(h * BN + chunk * 32), v);
-        ptx::tmem_ld_wait();
-        if (m_ok) {
-          const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
-          if (part) {
+        for (int chunk = 0; chunk < BN / 32; ++chunk) {
+          if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(h * BN + chunk * 32), v);
+          ptx::tmem_ld_wait();
+          if (m_ok) {
+            const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
+            if (part) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < nvalid) part[base + int64_t(chunk * 32 + j) * p.pq] = __uint_as_float(v[j]);
-          } else if (p.is_bf16) {
-            __nv_bfloat16* y = static_cast<__nv_bfloat16*>(p.y);
+              for (int j = 0; j < 32; ++j)
+                if (j < nvalid) part[base + int64_t(chunk * 32 + j) * p.pq] = __uint_as_float(v[j]);
+            } else if (p.is_bf16) {
+              __nv_bfloat16* y = static_cast<__nv_bfloat16*>(p.y);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float a = __uint_as_float(v[j]) + bias_s[chunk * 32 + j];
-              if (p.relu) a = fmaxf(a, 0.f);
-              if (j < nvalid) y[base + int64_t(chunk * 32 + j) * p.pq] = __float2bfloat16_rn(a);
-            }
-          } else {
-            __half* y = static_cast<__half*>(p.y);
+              for (int j = 0; j < 32; ++j) {
+                float a = __uint_as_float(v[j]) + bias_t[chunk * 32 + j];
+                if (p.relu) a = fmaxf(a, 0.f);
+                if (j < nvalid) y[base + int64_t(chunk * 32 + j) * p.pq] = __float2bfloat16_rn(a);
+              }
+            } else {
+              __half* y = static_cast<__half*>(p.y);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float a = __uint_as_float(v[j]) + bias_s[chunk * 32 + j];
-              if (p.relu) a = fmaxf(a, 0.f);
-              if (j < nvalid) y[base + int64_t(chunk * 32 + j) * p.pq] = __float2half_rn(a);
+              for (int j = 0; j < 32; ++j) {
+                float a = __uint_as_float(v[j]) + bias_t[chunk * 32 + j];
+                if (p.relu) a = fmaxf(a, 0.f);
+                if (j < nvalid) y[base + int64_t(chunk * 32 + j) * p.pq] = __float2half_rn(a);
+              }
             }
           }
         }
       }
-     }
+      // all TMEM reads of this warp are complete (wait::ld above): hand the accumulator set back to the MMA issuer
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
     }
   }
 

@@ -31,6 +31,8 @@ struct ConvTcParams {
   int kb_per_tap;     // c_padded / BK
   int total_kb;       // R * S * kb_per_tap reduction slabs
   int kb_per_split;   // slabs per split-K slice
+  int tiles_m, tiles_n;  // tile grid over (pixels, output channels)
+  int num_tiles;      // tiles_m * tiles_n * split_k: the list every persistent CTA walks with stride gridDim.x
   int stride_h, stride_w, pad_h, pad_w;
   int stages;
   int relu, has_bias, is_bf16, bias_fp32;
