@@ -133,7 +133,7 @@ int resident_ctas(int tile_m, int tile_n, size_t smem) {
   int by_smem = int(kMaxDynamicSmem / (smem + 1024));
   int by_tmem = 512 / tmem_cols_of(tile_m, tile_n);
   int r = by_smem < by_tmem ? by_smem : by_tmem;
-  return r < 1 ? 1 : (r > 4 ? 4 : r);
+  return r < 1 ? 1 : (r > 2 ? 2 : r);  // 320 threads x ~84 registers: two CTAs fill the register file
 }
 
 // Ring depth: deep enough to cover L2 latency, shallow enough that two CTAs share an SM when more than one wave of
@@ -143,8 +143,7 @@ int pick_stages(int tile_m, int tile_n, int tile_k, int kb_per_split, int64_t ct
   const int by_tmem = 512 / tmem_cols_of(tile_m, tile_n);
   // measured: with >= 2.5 tiles per SM three shallow CTAs per SM beat two deeper ones; between 1 and 2.5 two CTAs win
   int want = 1;
-  if (ctas * 2 >= 5 * kNumSms) want = 3;
-  else if (ctas > kNumSms) want = 2;
+  if (ctas > kNumSms) want = 2;  // two CTAs per SM (the register file holds no more)
   if (want > by_tmem) want = by_tmem;
   const size_t budget = want == 1 ? kSmemBudget : (kMaxDynamicSmem / want - 2048);
   int stages = int((budget - 3072) / sb);

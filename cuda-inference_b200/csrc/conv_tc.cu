@@ -20,6 +20,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -27,6 +29,53 @@ namespace gieb {
 namespace {
 
 constexpr uint32_t kCtrlBytes = 3072;  // [0,2048): two bias tiles as float; [2048,3072): mbarriers + TMEM address slot
+
+// Epilogue of one 32-column chunk for one accumulator row (= one output pixel): + bias, optional ReLU, one rounding,
+// 32 stores that are `stride` elements apart (consecutive output channels of an NCHW tensor).  Branch-free body:
+// the ReLU / storage-type / full-chunk decisions are made once per chunk by the caller.
+template <typename T, bool RELU>
+__device__ __forceinline__ void store_chunk_full(const uint32_t (&v)[32], const float* __restrict__ bias, T* __restrict__ dst,
+                                                 int64_t stride) {
+  const float4* b4 = reinterpret_cast<const float4*>(bias);
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float4 b = b4[q];
+    const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float a = __uint_as_float(v[q * 4 + t]) + bb[t];
+      if (RELU) a = fmaxf(a, 0.f);
+      if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) *dst = __float2half_rn(a);
+      else *dst = __float2bfloat16_rn(a);
+      dst += stride;
+    }
+  }
+}
+
+template <typename T, bool RELU>
+__device__ __forceinline__ void store_chunk_tail(const uint32_t (&v)[32], const float* __restrict__ bias, T* __restrict__ dst,
+                                                 int64_t stride, int nvalid) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float a = __uint_as_float(v[j]) + bias[j];
+    if (RELU) a = fmaxf(a, 0.f);
+    if (j < nvalid) {
+      if constexpr (std::is_same<T, __half>::value) dst[int64_t(j) * stride] = __float2half_rn(a);
+      else dst[int64_t(j) * stride] = __float2bfloat16_rn(a);
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const float* bias, T* dst, int64_t stride, int nvalid, int relu) {
+  if (nvalid == 32) {
+    if (relu) store_chunk_full<T, true>(v, bias, dst, stride);
+    else store_chunk_full<T, false>(v, bias, dst, stride);
+  } else {
+    if (relu) store_chunk_tail<T, true>(v, bias, dst, stride, nvalid);
+    else store_chunk_tail<T, false>(v, bias, dst, stride, nvalid);
+  }
+}
 
 // Persistent CTAs: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; output-channel tiles fastest, then
 // pixel tiles, then split-K slices).  The operand ring and its phases run on across tiles, and the accumulator is
@@ -72,7 +121,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&acc_full[b], 1);
-      ptx::mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
     ptx::fence_mbar_init();
   }
@@ -192,9 +241,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5 cover TMEM lane quarters 2,3,0,1) ----------------
+    // ---------------- epilogue: 8 warps.  Warp w may read TMEM lanes 32*(w%4)..+31; warps 2..5 take the even
+    // 32-column chunks of a tile, warps 6..9 the odd ones (two warps per scheduler hide each other's latencies).
     const int quad = warp & 3;
-    const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+    const int par = (warp - 2) >> 2;  // 0 or 1: which chunks this warp owns
+    const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
     int tcount = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
       const int z = tile / tiles_mn;
@@ -208,7 +259,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       float* bias_t = bias_s + (tcount & 1) * 256;
 
       // stage this tile's bias as float (two buffers: a fast warp may already be one tile ahead of a slow one)
-      for (int i = et; i < BN; i += 128) {
+      for (int i = et; i < BN; i += kTcThreads - 64) {
         const int oc = n0 + i;
         float b = 0.f;
         if (p.has_bias && p.partial == nullptr && oc < p.out_channels) {
@@ -218,7 +269,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         }
         bias_t[i] = b;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // epilogue warps only
 
       const bool ok = ptx::mbar_wait(&acc_full[buf], acc_phase, p.status, kStatusEpilogueTimeout);
       __syncwarp();
@@ -242,33 +293,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         }
         const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
 #pragma unroll 1
-        for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        for (int chunk = par; chunk < BN / 32; chunk += 2) {
           if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform
           uint32_t v[32];
           ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(h * BN + chunk * 32), v);
           ptx::tmem_ld_wait();
           if (m_ok) {
             const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
+            const int64_t off = base + int64_t(chunk * 32) * p.pq;
             if (part) {
+              float* dst = part + off;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (j < nvalid) part[base + int64_t(chunk * 32 + j) * p.pq] = __uint_as_float(v[j]);
+                if (j < nvalid) dst[int64_t(j) * p.pq] = __uint_as_float(v[j]);
             } else if (p.is_bf16) {
-              __nv_bfloat16* y = static_cast<__nv_bfloat16*>(p.y);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                float a = __uint_as_float(v[j]) + bias_t[chunk * 32 + j];
-                if (p.relu) a = fmaxf(a, 0.f);
-                if (j < nvalid) y[base + int64_t(chunk * 32 + j) * p.pq] = __float2bfloat16_rn(a);
-              }
+              store_chunk<__nv_bfloat16>(v, bias_t + chunk * 32, static_cast<__nv_bfloat16*>(p.y) + off, p.pq, nvalid, p.relu);
             } else {
-              __half* y = static_cast<__half*>(p.y);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                float a = __uint_as_float(v[j]) + bias_t[chunk * 32 + j];
-                if (p.relu) a = fmaxf(a, 0.f);
-                if (j < nvalid) y[base + int64_t(chunk * 32 + j) * p.pq] = __float2half_rn(a);
-              }
+              store_chunk<__half>(v, bias_t + chunk * 32, static_cast<__half*>(p.y) + off, p.pq, nvalid, p.relu);
             }
           }
         }

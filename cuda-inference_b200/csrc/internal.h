@@ -17,7 +17,7 @@ enum : uint32_t {
 
 constexpr int kTileM = 128;        // output pixels per CTA tile = TMEM lanes = UMMA M
 constexpr int kMaxStages = 8;
-constexpr int kTcThreads = 192;    // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2..5: epilogue
+constexpr int kTcThreads = 320;    // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2..9: epilogue
 
 // Everything the tensor-core kernel needs besides the two tensor maps.  Plain data, passed by value.
 struct ConvTcParams {
