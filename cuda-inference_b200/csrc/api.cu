@@ -133,7 +133,7 @@ int resident_ctas(int tile_m, int tile_n, size_t smem) {
   int by_smem = int(kMaxDynamicSmem / (smem + 1024));
   int by_tmem = 512 / tmem_cols_of(tile_m, tile_n);
   int r = by_smem < by_tmem ? by_smem : by_tmem;
-  return r < 1 ? 1 : (r > 2 ? 2 : r);  // 320 threads x ~84 registers: two CTAs fill the register file
+  return r < 1 ? 1 : (r > 2 ? 2 : r);  // 384 threads x 80 registers: two CTAs fill the register file
 }
 
 // Ring depth: deep enough to cover L2 latency, shallow enough that two CTAs share an SM when more than one wave of

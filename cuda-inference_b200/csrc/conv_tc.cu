@@ -84,7 +84,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const float
 // MH = number of 128-pixel halves per tile (1 or 2).  With MH = 2 the tile is 256 pixels: two activation loads and two
 // accumulators share every weight tile, which halves the weight traffic per FLOP.
 template <int BN, int BK, int MH>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)  // at most 80 registers: two CTAs of 12 warps fit the register file
 conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_wgt,
                const ConvTcParams p) {
   constexpr int ROW_BYTES = BK * 2;
@@ -125,7 +125,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     }
     ptx::fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == kProducerWarps) {
     ptx::tmem_alloc(tmem_slot, TMEM_COLS);
     ptx::tmem_relinquish();
   }
@@ -134,94 +134,116 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int it = 0;  // slabs issued so far by this CTA: ring slot and phase continue across tiles
-      bool alive = true;
-      for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
-        const int z = tile / tiles_mn;
-        const int rest = tile - z * tiles_mn;
-        const int m_blk = rest / p.tiles_n;
-        const int n0 = (rest - m_blk * p.tiles_n) * BN;
-        const int m0 = m_blk * (kTileM * MH);
-        const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;  // a trailing tile may own one half only
-        const int kb_begin = z * p.kb_per_split;
-        const int num_kb = min(p.total_kb, kb_begin + p.kb_per_split) - kb_begin;
-        int img[MH], base_w[MH], base_h[MH];
-#pragma unroll
-        for (int h = 0; h < MH; ++h) {
-          const int mh = m0 + h * kTileM;
-          img[h] = mh / p.pq;
-          const int rem = mh - img[h] * p.pq;
-          const int p0 = rem / p.out_w;
-          const int q0 = rem - p0 * p.out_w;
-          base_w[h] = q0 * p.stride_w - p.pad_w;
-          base_h[h] = p0 * p.stride_h - p.pad_h;
-        }
-        const uint32_t tx_bytes = uint32_t(halves) * A_HALF_BYTES + B_BYTES;
-        for (int i = 0; i < num_kb; ++i, ++it) {
-          const int s = it % stages;
-          const uint32_t phase = (it / stages) & 1;
-          if (!ptx::mbar_wait(&empty_bar[s], phase ^ 1u, p.status, kStatusProducerTimeout)) { alive = false; break; }
-          const int kb = kb_begin + i;
-          const int tap = kb / p.kb_per_tap;
-          const int cb = kb - tap * p.kb_per_tap;
-          const int r = tap / p.kernel_w;
-          const int sx = tap - r * p.kernel_w;
-          uint8_t* a_dst = stage_base + size_t(s) * STAGE_BYTES;
-          uint8_t* b_dst = a_dst + A_BYTES;
-          ptx::mbar_arrive_expect_tx(&full_bar[s], tx_bytes);
-#pragma unroll
-          for (int h = 0; h < MH; ++h) {
-            if (h < halves) {
-              if (p.a_mode == 2) {
-                // two boxes of 64 pixels x BK channels each, [channel][pixel] in shared memory
-                const int box0 = (m0 + h * kTileM) >> 6;
-#pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                  const int box = box0 + b;
-                  const int bimg = box / p.boxes_per_image;
-                  const int bpix = (box - bimg * p.boxes_per_image) << 6;
-                  ptx::tma_load_3d(a_dst + h * A_HALF_BYTES + b * (A_HALF_BYTES / 2), &tm_act, &full_bar[s], bpix, cb * BK, bimg);
-                }
-              } else if (p.a_mode == 1) {
-                ptx::tma_load_2d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, m0 + h * kTileM);
-              } else {
-                ptx::tma_load_im2col_4d(a_dst + h * A_HALF_BYTES, &tm_act, &full_bar[s], cb * BK, base_w[h], base_h[h], img[h],
-                                        uint16_t(sx), uint16_t(r));
-              }
-            }
-          }
-          ptx::tma_load_2d(b_dst, &tm_wgt, &full_bar[s], tap * p.c_padded + cb * BK, n0);
-        }
+  if (warp < kProducerWarps) {
+    // ---------------- TMA producers ----------------
+    // One TMA instruction keeps its issuing warp busy for a few hundred cycles whatever the box size, so a single
+    // producer cannot feed the ring faster than about one slab per 600 cycles.  kProducerWarps warps therefore take
+    // the slabs round-robin (warp j owns the CTA's slabs j, j + np, ...), each issuing the activation
+    // boxes and the weight tile of its slab.  A warp walks its loop converged (every lane polls the barrier); lane l
+    // issues activation box l, so the boxes of one slab leave in ONE instruction.  Ring slot, phase and filter-tap
+    // counters advance incrementally: no integer division inside the slab loop.
+    // No more producers than ring slots: a warp must never be a full ring ahead of its own previous slab, or the
+    // parity of the slot's barrier could not tell its phases apart.
+    const int np = min(kProducerWarps, stages);
+    int s = warp;        // ring slot of this warp's next slab (the ring and its phases continue across tiles)
+    uint32_t phase = 0;
+    while (s >= stages) { s -= stages; phase ^= 1u; }
+    int skip = warp;     // slabs of the coming tile that belong to other warps before this warp's first one
+    bool alive = warp < np;
+    for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
+      const int z = tile / tiles_mn;
+      const int rest = tile - z * tiles_mn;
+      const int m_blk = rest / p.tiles_n;
+      const int n0 = (rest - m_blk * p.tiles_n) * BN;
+      const int m0 = m_blk * (kTileM * MH);
+      const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;  // a trailing tile may own one half only
+      const int kb_begin = z * p.kb_per_split;
+      const int num_kb = min(p.total_kb, kb_begin + p.kb_per_split) - kb_begin;
+      // this lane's activation box: a 128-pixel half (modes 0, 1) or a 64-pixel box of one image (mode 2)
+      const int nbox = p.a_mode == 2 ? 2 * halves : halves;
+      uint32_t a_off;
+      int c1, c2, c3;  // box coordinates besides the channel coordinate
+      if (p.a_mode == 2) {
+        const int box = (m0 >> 6) + lane;
+        c3 = box / p.boxes_per_image;                   // image
+        c1 = (box - c3 * p.boxes_per_image) << 6;       // first pixel
+        c2 = 0;
+        a_off = uint32_t(lane) * (A_HALF_BYTES / 2);
+      } else {
+        const int mh = m0 + lane * kTileM;
+        c3 = mh / p.pq;                                 // image
+        const int rem = mh - c3 * p.pq;
+        const int p0 = rem / p.out_w;
+        c1 = (rem - p0 * p.out_w) * p.stride_w - p.pad_w;  // leftmost input column of the first pixel
+        c2 = p0 * p.stride_h - p.pad_h;                    // topmost input row
+        if (p.a_mode == 1) c1 = mh;                        // row of the pixel matrix
+        a_off = uint32_t(lane) * A_HALF_BYTES;
       }
+      // filter tap (r, sx), channel block cb and weight column k0 of this warp's first slab in the tile
+      int tap = (kb_begin + skip) / p.kb_per_tap;
+      int cb = kb_begin + skip - tap * p.kb_per_tap;
+      int r = tap / p.kernel_w;
+      int sx = tap - r * p.kernel_w;
+      int k0 = tap * p.c_padded;
+      const uint32_t tx_bytes = uint32_t(halves) * A_HALF_BYTES + B_BYTES;
+      int i = skip;
+      for (; i < num_kb; i += np) {
+        const bool ok = ptx::mbar_wait(&empty_bar[s], phase ^ 1u, p.status, kStatusProducerTimeout);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+        uint8_t* a_dst = stage_base + size_t(s) * STAGE_BYTES;
+        if (lane == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], tx_bytes);
+        __syncwarp();
+        if (lane < nbox) {
+          if (p.a_mode == 2) {
+            // 64 pixels x BK channels, [channel][pixel] in shared memory
+            ptx::tma_load_3d(a_dst + a_off, &tm_act, &full_bar[s], c1, cb * BK, c3);
+          } else if (p.a_mode == 1) {
+            ptx::tma_load_2d(a_dst + a_off, &tm_act, &full_bar[s], cb * BK, c1);
+          } else {
+            ptx::tma_load_im2col_4d(a_dst + a_off, &tm_act, &full_bar[s], cb * BK, c1, c2, c3, uint16_t(sx), uint16_t(r));
+          }
+        }
+        if (lane == 0) ptx::tma_load_2d(a_dst + A_BYTES, &tm_wgt, &full_bar[s], k0 + cb * BK, n0);
+        cb += np;
+        while (cb >= p.kb_per_tap) {
+          cb -= p.kb_per_tap;
+          k0 += p.c_padded;
+          if (++sx == p.kernel_w) { sx = 0; ++r; }
+        }
+        s += np;
+        while (s >= stages) { s -= stages; phase ^= 1u; }
+      }
+      skip = i - num_kb;  // how far this warp's next slab lies into the next tile
     }
-  } else if (warp == 1) {
+  } else if (warp == kProducerWarps) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      int it = 0, tcount = 0;
-      bool alive = true;
-      for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
-        const int z = tile / tiles_mn;
-        const int rest = tile - z * tiles_mn;
-        const int m0 = (rest / p.tiles_n) * (kTileM * MH);
-        const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;
-        const int kb_begin = z * p.kb_per_split;
-        const int num_kb = min(p.total_kb, kb_begin + p.kb_per_split) - kb_begin;
-        const int buf = tcount % ACC_BUFS;
-        const uint32_t acc_phase = (tcount / ACC_BUFS) & 1;
-        // the epilogue must have drained this accumulator set (first use passes at once)
-        if (!ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1u, p.status, kStatusMmaTimeout)) break;
+    // The warp stays converged (all lanes wait and compute the descriptors); one elected lane issues the MMAs and
+    // the commits.  A single diverged lane pays markedly more issue latency per tcgen05.mma than an elected lane
+    // of a converged warp, enough to make 128-column tiles issue-bound.
+    int s = 0, tcount = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
+      const int z = tile / tiles_mn;
+      const int rest = tile - z * tiles_mn;
+      const int m0 = (rest / p.tiles_n) * (kTileM * MH);
+      const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;
+      const int kb_begin = z * p.kb_per_split;
+      const int num_kb = min(p.total_kb, kb_begin + p.kb_per_split) - kb_begin;
+      const int buf = ACC_BUFS == 2 ? (tcount & 1) : 0;
+      const uint32_t acc_phase = (ACC_BUFS == 2 ? (tcount >> 1) : tcount) & 1;
+      // the epilogue must have drained this accumulator set (first use passes at once)
+      const bool drained = ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1u, p.status, kStatusMmaTimeout);
+      if (!__all_sync(0xffffffffu, drained)) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t acc = tmem_base + buf * ACC_COLS;
+      for (int i = 0; i < num_kb; ++i) {
+        const bool ok = ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout);
+        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
         ptx::tc_fence_after_sync();
-        const uint32_t acc = tmem_base + buf * ACC_COLS;
-        for (int i = 0; i < num_kb; ++i, ++it) {
-          const int s = it % stages;
-          const uint32_t phase = (it / stages) & 1;
-          if (!ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout)) { alive = false; break; }
-          ptx::tc_fence_after_sync();
-          const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
+        const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
+        const uint32_t b_addr = a_addr + A_BYTES;
+        if (ptx::elect_one()) {
 #pragma unroll
           for (int h = 0; h < MH; ++h) {
             if (h < halves) {
@@ -237,15 +259,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           }
           ptx::mma_commit(&empty_bar[s]);  // frees the slot once these MMAs have read it
         }
-        ptx::mma_commit(&acc_full[buf]);   // accumulator set complete (also reached after a time-out, so nobody hangs)
+        __syncwarp();
+        if (++s == stages) { s = 0; phase ^= 1u; }
       }
+      // accumulator set complete (also reached after a time-out in the slab loop, so nobody hangs)
+      if (ptx::elect_one()) ptx::mma_commit(&acc_full[buf]);
+      __syncwarp();
     }
   } else {
-    // ---------------- epilogue: 8 warps.  Warp w may read TMEM lanes 32*(w%4)..+31; warps 2..5 take the even
-    // 32-column chunks of a tile, warps 6..9 the odd ones (two warps per scheduler hide each other's latencies).
+    // ---------------- epilogue: 8 warps.  Warp w may read TMEM lanes 32*(w%4)..+31; warps 4..7 take the even
+    // 32-column chunks of a tile, warps 8..11 the odd ones (two warps per scheduler hide each other's latencies).
     const int quad = warp & 3;
-    const int par = (warp - 2) >> 2;  // 0 or 1: which chunks this warp owns
-    const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
+    const int par = (warp - kProducerWarps - 1) >> 2;  // 0 or 1: which chunks this warp owns
+    const int et = threadIdx.x - 32 * (kProducerWarps + 1);  // 0..255 among the epilogue threads
     int tcount = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
       const int z = tile / tiles_mn;
@@ -259,7 +285,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       float* bias_t = bias_s + (tcount & 1) * 256;
 
       // stage this tile's bias as float (two buffers: a fast warp may already be one tile ahead of a slow one)
-      for (int i = et; i < BN; i += kTcThreads - 64) {
+      for (int i = et; i < BN; i += 256) {
         const int oc = n0 + i;
         float b = 0.f;
         if (p.has_bias && p.partial == nullptr && oc < p.out_channels) {
@@ -323,7 +349,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kProducerWarps) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }

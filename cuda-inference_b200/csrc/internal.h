@@ -17,7 +17,9 @@ enum : uint32_t {
 
 constexpr int kTileM = 128;        // output pixels per CTA tile = TMEM lanes = UMMA M
 constexpr int kMaxStages = 8;
-constexpr int kTcThreads = 320;    // warp 0: TMA producer, warp 1: MMA issuer + TMEM owner, warps 2..9: epilogue
+constexpr int kProducerWarps = 3;  // warps 0..2 issue the TMA loads, slab by slab in turn
+constexpr int kTcThreads = 384;    // + warp 3: MMA issuer and TMEM owner, warps 4..11: epilogue
+static_assert((kProducerWarps + 1) % 4 == 0, "epilogue warp w must sit on TMEM lane quarter w % 4");
 
 // Everything the tensor-core kernel needs besides the two tensor maps.  Plain data, passed by value.
 struct ConvTcParams {

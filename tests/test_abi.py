@@ -65,7 +65,7 @@ def test_query_precision_routing_and_reasons(pkg):
     i32 = pkg.query(P(pkg, *base, precision=pkg.FP32))
     assert i32.supported and i32.variant == 3 and i32.workspace_bytes == 0 and i32.launches == 1
     i16 = pkg.query(P(pkg, *base, precision=pkg.FP16))
-    assert i16.supported and i16.variant == 1 and i16.threads_per_block == 320 and i16.padded_channels == 64
+    assert i16.supported and i16.variant == 1 and i16.threads_per_block == 384 and i16.padded_channels == 64
     ipw = pkg.query(P(pkg, 2, 64, 14, 14, 64, 1, 1, precision=pkg.BF16))
     assert ipw.supported and ipw.variant == 4                       # 1x1 / stride 1 / pad 0 -> tiled activation loads
     idr = pkg.query(P(pkg, 2, 64, 28, 28, 64, 1, 1, precision=pkg.BF16))
