@@ -486,6 +486,13 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.tiles_m = ceil_div(rows, r.tile_m);
   p.tiles_n = r.tiles_n;
   p.num_tiles = p.tiles_m * p.tiles_n * r.split_k;
+  p.fd_tiles_mn = FastDiv::make(p.tiles_m * p.tiles_n);
+  p.fd_tiles_n = FastDiv::make(p.tiles_n);
+  p.fd_pq = FastDiv::make(p.pq);
+  p.fd_out_w = FastDiv::make(p.out_w);
+  p.fd_kb_per_tap = FastDiv::make(p.kb_per_tap);
+  p.fd_kernel_w = FastDiv::make(p.kernel_w);
+  p.fd_boxes = FastDiv::make(p.boxes_per_image > 0 ? p.boxes_per_image : 1);
   // persistent CTAs: as many as can be resident at once, each walking the tile list
   const int64_t resident = int64_t(kNumSms) * resident_ctas(r.tile_m, r.tile_n, r.smem);
   dim3 grid(unsigned(p.num_tiles < resident ? p.num_tiles : resident));

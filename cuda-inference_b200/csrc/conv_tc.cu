@@ -111,6 +111,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
   const int tiles_mn = p.tiles_m * p.tiles_n;
+  ptx::grid_dep_launch();  // the next kernel of the stream may begin its own set-up (it orders itself with grid_dep_wait)
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_act);
@@ -129,10 +130,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     ptx::tmem_alloc(tmem_slot, TMEM_COLS);
     ptx::tmem_relinquish();
   }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  // The set-up barrier (mbarriers initialised, TMEM allocated) is joined by every warp exactly once, from inside its
+  // role and only after it has decoded its first tile, so the decode overlaps the set-up instead of following it.
+  // The kernel is launched with programmatic stream serialization: up to this join it may run beside the previous
+  // kernel of the stream (the repack), so the join also waits for that kernel's completion.
+  bool joined = false;
+  uint32_t tmem_base = 0;
+  auto join_setup = [&]() {
+    if (!joined) {
+      ptx::tc_fence_before_sync();
+      asm volatile("bar.sync 0;" ::: "memory");
+      ptx::tc_fence_after_sync();
+      tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+      joined = true;
+      ptx::grid_dep_wait();  // everything above overlapped the previous kernel; global memory is touched only below
+    }
+  };
 
   if (warp < kProducerWarps) {
     // ---------------- TMA producers ----------------
@@ -151,9 +164,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     int skip = warp;     // slabs of the coming tile that belong to other warps before this warp's first one
     bool alive = warp < np;
     for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
-      const int z = tile / tiles_mn;
+      const int z = p.fd_tiles_mn.div(tile);
       const int rest = tile - z * tiles_mn;
-      const int m_blk = rest / p.tiles_n;
+      const int m_blk = p.fd_tiles_n.div(rest);
       const int n0 = (rest - m_blk * p.tiles_n) * BN;
       const int m0 = m_blk * (kTileM * MH);
       const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;  // a trailing tile may own one half only
@@ -165,28 +178,29 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       int c1, c2, c3;  // box coordinates besides the channel coordinate
       if (p.a_mode == 2) {
         const int box = (m0 >> 6) + lane;
-        c3 = box / p.boxes_per_image;                   // image
+        c3 = p.fd_boxes.div(box);                        // image
         c1 = (box - c3 * p.boxes_per_image) << 6;       // first pixel
         c2 = 0;
         a_off = uint32_t(lane) * (A_HALF_BYTES / 2);
       } else {
         const int mh = m0 + lane * kTileM;
-        c3 = mh / p.pq;                                 // image
+        c3 = p.fd_pq.div(mh);                            // image
         const int rem = mh - c3 * p.pq;
-        const int p0 = rem / p.out_w;
+        const int p0 = p.fd_out_w.div(rem);
         c1 = (rem - p0 * p.out_w) * p.stride_w - p.pad_w;  // leftmost input column of the first pixel
         c2 = p0 * p.stride_h - p.pad_h;                    // topmost input row
         if (p.a_mode == 1) c1 = mh;                        // row of the pixel matrix
         a_off = uint32_t(lane) * A_HALF_BYTES;
       }
       // filter tap (r, sx), channel block cb and weight column k0 of this warp's first slab in the tile
-      int tap = (kb_begin + skip) / p.kb_per_tap;
+      int tap = p.fd_kb_per_tap.div(kb_begin + skip);
       int cb = kb_begin + skip - tap * p.kb_per_tap;
-      int r = tap / p.kernel_w;
+      int r = p.fd_kernel_w.div(tap);
       int sx = tap - r * p.kernel_w;
       int k0 = tap * p.c_padded;
       const uint32_t tx_bytes = uint32_t(halves) * A_HALF_BYTES + B_BYTES;
       int i = skip;
+      join_setup();
       for (; i < num_kb; i += np) {
         const bool ok = ptx::mbar_wait(&empty_bar[s], phase ^ 1u, p.status, kStatusProducerTimeout);
         if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
@@ -215,6 +229,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       }
       skip = i - num_kb;  // how far this warp's next slab lies into the next tile
     }
+    join_setup();  // warps without a slab of their own
   } else if (warp == kProducerWarps) {
     // ---------------- MMA issuer ----------------
     // The warp stays converged (all lanes wait and compute the descriptors); one elected lane issues the MMAs and
@@ -224,14 +239,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     uint32_t phase = 0;
     bool alive = true;
     for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
-      const int z = tile / tiles_mn;
+      const int z = p.fd_tiles_mn.div(tile);
       const int rest = tile - z * tiles_mn;
-      const int m0 = (rest / p.tiles_n) * (kTileM * MH);
+      const int m0 = p.fd_tiles_n.div(rest) * (kTileM * MH);
       const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;
       const int kb_begin = z * p.kb_per_split;
       const int num_kb = min(p.total_kb, kb_begin + p.kb_per_split) - kb_begin;
       const int buf = ACC_BUFS == 2 ? (tcount & 1) : 0;
       const uint32_t acc_phase = (ACC_BUFS == 2 ? (tcount >> 1) : tcount) & 1;
+      join_setup();
       // the epilogue must have drained this accumulator set (first use passes at once)
       const bool drained = ptx::mbar_wait(&acc_empty[buf], acc_phase ^ 1u, p.status, kStatusMmaTimeout);
       if (!__all_sync(0xffffffffu, drained)) break;
@@ -274,9 +290,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     const int et = threadIdx.x - 32 * (kProducerWarps + 1);  // 0..255 among the epilogue threads
     int tcount = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
-      const int z = tile / tiles_mn;
+      const int z = p.fd_tiles_mn.div(tile);
       const int rest = tile - z * tiles_mn;
-      const int m_blk = rest / p.tiles_n;
+      const int m_blk = p.fd_tiles_n.div(rest);
       const int n0 = (rest - m_blk * p.tiles_n) * BN;
       const int m0 = m_blk * (kTileM * MH);
       const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;
@@ -284,6 +300,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const uint32_t acc_phase = (tcount / ACC_BUFS) & 1;
       float* bias_t = bias_s + (tcount & 1) * 256;
 
+      join_setup();
       // stage this tile's bias as float (two buffers: a fast warp may already be one tile ahead of a slow one)
       for (int i = et; i < BN; i += 256) {
         const int oc = n0 + i;
@@ -309,12 +326,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         int img = 0, pix = 0;
         if (p.a_mode == 2) {  // rows are numbered in 64-pixel boxes per image
           const int box = m >> 6;
-          img = box / p.boxes_per_image;
+          img = p.fd_boxes.div(box);
           pix = ((box - img * p.boxes_per_image) << 6) + (m & 63);
           m_ok = m_ok && pix < p.pq;
           if (!m_ok) img = pix = 0;
         } else if (m_ok) {
-          img = m / p.pq;
+          img = p.fd_pq.div(m);
           pix = m - img * p.pq;
         }
         const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
@@ -347,6 +364,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     }
   }
 
+  join_setup();  // no-op for every warp that had a tile (all of them: the grid never exceeds the tile count)
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (warp == kProducerWarps) {
@@ -363,7 +381,8 @@ cudaError_t prepare_one(size_t smem_bytes) {
 template <int BN, int BK, int MH>
 cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tw, const ConvTcParams& p, dim3 grid, size_t smem,
                        cudaStream_t st) {
-  conv_tc_kernel<BN, BK, MH><<<grid, kTcThreads, smem, st>>>(ta, tw, p);
+  cudaError_t e = launch_pdl(conv_tc_kernel<BN, BK, MH>, grid, dim3(kTcThreads), smem, st, ta, tw, p);
+  if (e != cudaSuccess) return e;
   return cudaGetLastError();
 }
 
@@ -411,12 +430,20 @@ __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162flo
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t total, int64_t slice_stride, int out_channels,
-                     int pq, const void* __restrict__ bias, int bias_fp32, int relu, T* __restrict__ y) {
+                     int pq, FastDiv fd_pq, FastDiv fd_oc, const void* __restrict__ bias, int bias_fp32, int relu,
+                     T* __restrict__ y) {
+  ptx::grid_dep_wait();  // launched with programmatic stream serialization right behind the convolution kernel
   const int64_t step = int64_t(gridDim.x) * blockDim.x;
   const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   auto bias_of = [&](int64_t i) -> float {
     if (bias == nullptr) return 0.f;
-    const int oc = int((i / pq) % out_channels);
+    int oc;
+    if (total < (int64_t(1) << 31)) {  // the usual case: two multiply-high divisions
+      const int plane = fd_pq.div(int(i));
+      oc = plane - fd_oc.div(plane) * out_channels;
+    } else {
+      oc = int((i / pq) % out_channels);
+    }
     return bias_fp32 ? static_cast<const float*>(bias)[oc] : to_f32(static_cast<const T*>(bias)[oc]);
   };
   if (VEC) {
@@ -477,16 +504,18 @@ cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total
   int64_t blocks = (work + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
+  const FastDiv fd_pq = FastDiv::make(pq), fd_oc = FastDiv::make(out_channels);
+  cudaError_t e;
   if (is_bf16) {
     auto* yy = static_cast<__nv_bfloat16*>(y);
-    if (vec) splitk_reduce_kernel<__nv_bfloat16, true><<<unsigned(blocks), 256, 0, stream>>>(partial, splits, total, slice_stride, out_channels, pq, bias, bias_fp32, relu, yy);
-    else splitk_reduce_kernel<__nv_bfloat16, false><<<unsigned(blocks), 256, 0, stream>>>(partial, splits, total, slice_stride, out_channels, pq, bias, bias_fp32, relu, yy);
+    if (vec) e = launch_pdl(splitk_reduce_kernel<__nv_bfloat16, true>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, yy);
+    else e = launch_pdl(splitk_reduce_kernel<__nv_bfloat16, false>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, yy);
   } else {
     auto* yy = static_cast<__half*>(y);
-    if (vec) splitk_reduce_kernel<__half, true><<<unsigned(blocks), 256, 0, stream>>>(partial, splits, total, slice_stride, out_channels, pq, bias, bias_fp32, relu, yy);
-    else splitk_reduce_kernel<__half, false><<<unsigned(blocks), 256, 0, stream>>>(partial, splits, total, slice_stride, out_channels, pq, bias, bias_fp32, relu, yy);
+    if (vec) e = launch_pdl(splitk_reduce_kernel<__half, true>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, yy);
+    else e = launch_pdl(splitk_reduce_kernel<__half, false>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, yy);
   }
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace gieb

@@ -21,6 +21,58 @@ constexpr int kProducerWarps = 3;  // warps 0..2 issue the TMA loads, slab by sl
 constexpr int kTcThreads = 384;    // + warp 3: MMA issuer and TMEM owner, warps 4..11: epilogue
 static_assert((kProducerWarps + 1) % 4 == 0, "epilogue warp w must sit on TMEM lane quarter w % 4");
 
+// Division by a run-time constant as multiply-high + shift (round-up reciprocal method): exact for 0 <= n < 2^31 and
+// 1 <= d < 2^31.  The host builds it once per launch; a device-side divide costs a few cycles instead of ~150.
+struct FastDiv {
+  uint32_t d, mul, shr;
+#if defined(__CUDACC__)
+  __host__ __device__
+#endif
+  static FastDiv make(int divisor) {
+    FastDiv f;
+    f.d = uint32_t(divisor);
+    if (divisor <= 1) {
+      f.mul = 0;
+      f.shr = 0;
+    } else {
+      uint32_t lg = 0;  // ceil(log2(d))
+      while ((1ull << lg) < uint64_t(f.d)) ++lg;
+      const uint32_t p = 31 + lg;
+      f.mul = uint32_t(((1ull << p) + f.d - 1) / f.d);
+      f.shr = p - 32;
+    }
+    return f;
+  }
+#if defined(__CUDACC__)
+  __device__ __forceinline__ int div(int n) const { return d == 1 ? n : int(__umulhi(uint32_t(n), mul) >> shr); }
+  __device__ __forceinline__ void divmod(int n, int& q, int& r) const {
+    q = div(n);
+    r = n - q * int(d);
+  }
+#endif
+  int div_host(int n) const { return d == 1 ? n : int((uint64_t(uint32_t(n)) * mul >> 32) >> shr); }
+};
+
+#if defined(__CUDACC__)
+// Launch with programmatic stream serialization: the grid may be scheduled before the previous kernel of the stream
+// has finished; the kernel orders itself with ptx::grid_dep_wait().  Works under stream capture (the edge becomes a
+// programmatic dependency of the graph).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 // Everything the tensor-core kernel needs besides the two tensor maps.  Plain data, passed by value.
 struct ConvTcParams {
   int m_total;        // GEMM rows: B * P * Q output pixels (modes 0, 1) or box-numbered rows (mode 2)
@@ -47,6 +99,7 @@ struct ConvTcParams {
   int a_mode;
   int boxes_per_image;  // mode 2: ceil(H*W / 64)
   uint32_t idesc;
+  FastDiv fd_tiles_mn, fd_tiles_n, fd_pq, fd_out_w, fd_kb_per_tap, fd_kernel_w, fd_boxes;  // reciprocals of the fields above
   const void* bias;
   void* y;            // NCHW output in the storage type (split_k == 1)
   float* partial;     // [splits][B*O*P*Q] FP32 partial sums in NCHW order (split_k > 1), else null

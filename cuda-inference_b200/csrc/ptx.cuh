@@ -26,6 +26,13 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in the
+// stream is still running; it must execute grid_dep_wait() before its first access to global memory that the earlier
+// kernel may write (or still read).  grid_dep_launch() lets the NEXT such kernel start its own preamble early.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

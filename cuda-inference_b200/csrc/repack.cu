@@ -9,6 +9,7 @@
 #include <stdint.h>
 
 #include "internal.h"
+#include "ptx.cuh"
 
 namespace gieb {
 namespace {
@@ -114,6 +115,10 @@ struct RepackJob {
 // Up to two jobs in one launch (activations + weights): block indices [0, a.blocks) belong to job a, the rest to job b.
 __global__ void __launch_bounds__(256) repack_jobs_kernel(const RepackJob a, const RepackJob b) {
   __shared__ __align__(16) uint32_t smem[kTile * kLdWords];  // 8448 B >= kTile * kSmallHwMax * 2 = 8192 B
+  // Launched with programmatic stream serialization: wait for the previous kernel of the stream (it may still read
+  // the destination or write the source), then let the convolution kernel behind this one begin its set-up.
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
   const bool first = blockIdx.x < a.blocks;
   const RepackJob& j = first ? a : b;
   unsigned id = first ? blockIdx.x : blockIdx.x - a.blocks;
@@ -158,7 +163,8 @@ cudaError_t repack_pair_launch(const void* src_a, void* dst_a, int batch_a, int 
   if (na + nb > 2147483647LL) return cudaErrorInvalidValue;
   a.blocks = unsigned(na);
   b.blocks = unsigned(nb);
-  repack_jobs_kernel<<<unsigned(na + nb), 256, 0, stream>>>(a, b);
+  const cudaError_t e = launch_pdl(repack_jobs_kernel, dim3(unsigned(na + nb)), dim3(256), 0, stream, a, b);
+  if (e != cudaSuccess) return e;
   return cudaGetLastError();
 }
 
