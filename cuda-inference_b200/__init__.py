@@ -40,7 +40,7 @@ class ConvDesc(C.Structure):
 
 class ConvCfg(C.Structure):
     _fields_ = [("tile_n", C.c_int32), ("tile_k", C.c_int32), ("stages", C.c_int32), ("split_k", C.c_int32),
-                ("variant", C.c_int32), ("tile_m", C.c_int32), ("reserved", C.c_int32 * 2)]
+                ("variant", C.c_int32), ("tile_m", C.c_int32), ("reduce", C.c_int32), ("reserved", C.c_int32)]
 
 
 class ConvInfo(C.Structure):
@@ -137,8 +137,8 @@ class ConvProblem:
         return 2 * self.out_channels * self.batch * self.out_h * self.out_w * self.in_channels * self.kernel_h * self.kernel_w
 
 
-def make_cfg(tile_n=0, tile_k=0, stages=0, split_k=0, variant=0, tile_m=0) -> ConvCfg:
-    return ConvCfg(tile_n, tile_k, stages, split_k, variant, tile_m, (C.c_int32 * 2)(0, 0))
+def make_cfg(tile_n=0, tile_k=0, stages=0, split_k=0, variant=0, tile_m=0, reduce=0) -> ConvCfg:
+    return ConvCfg(tile_n, tile_k, stages, split_k, variant, tile_m, reduce, 0)
 
 
 def validate_problem(p: ConvProblem) -> None:

@@ -58,7 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
     objs = [os.path.join(OBJ, src[:-3] + ".o") for src in _sources()]
     if force or jobs or _stale(LIB, objs):
-        cmd = [_nvcc(), "-shared", "-cudart", "static", "-o", LIB] + objs
+        cmd = [_nvcc(), "-shared", "-cudart", "static", "-Xlinker", "--no-undefined", "-o", LIB] + objs
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

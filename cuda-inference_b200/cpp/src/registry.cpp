@@ -32,7 +32,7 @@ struct PlanHandle {
 template <int PREC, int TM, int TN, int TK, int ST, int SK>
 struct Point {
   static const gieb_conv_cfg* cfg() {
-    static const gieb_conv_cfg c = {TN, TK, ST, SK, 0, TM, {0, 0}};
+    static const gieb_conv_cfg c = {TN, TK, ST, SK, 0, TM, 0, 0};
     return (TM | TN | TK | ST | SK) ? &c : nullptr;
   }
   static gieb_conv_info query(const ConvProblem& pr, int device = -1) {

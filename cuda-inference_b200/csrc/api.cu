@@ -102,6 +102,7 @@ struct Resolved {
   int variant;
   int boxes_per_image;  // variant 2: ceil(H*W / 64)
   int tile_m, tile_n, tile_k, stages, split_k;
+  int reduce;  // 1 workspace partials + reduction launch, 2 cluster (distributed shared memory); 0 when split_k == 1
   int c_padded, kb_per_tap, total_kb, kb_per_split;
   int tiles_m, tiles_n;
   size_t smem;
@@ -153,7 +154,22 @@ int pick_stages(int tile_m, int tile_n, int tile_k, int kb_per_split, int64_t ct
   return stages;
 }
 
-double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, int tile_n, int tile_k, int split) {
+// Whether the split-K slices of one tile may be summed inside a cluster (distributed shared memory).
+bool cluster_reduce_ok(int tile_m, int tile_n, int tile_k, int stages, int split) {
+  const int chunks = tile_n / 32;
+  return tile_m == kTileM && (split == 2 || split == 4 || split == 8) && chunks % split == 0 &&
+         size_t(split - 1) * (tile_n / split) * kTileM * 4 <= size_t(stages) * stage_bytes_of(tile_m, tile_n, tile_k);
+}
+
+// Cost model in SM cycles, fitted to per-CTA clock stamps of the kernel on B200:
+//  * a converged issuer needs >= 78 cycles per tcgen05.mma plus ~215 per slab for the commit and the barrier wait;
+//    256-column instructions (128 pipe cycles each) hide all of that behind the tensor pipe;
+//  * with every SM busy, L2 delivers ~74 B/clk of operands to each SM;
+//  * CTAs that share an SM interleave their issue latencies but share pipe and feed;
+//  * ~4500 cycles from launch to the first MMA, ~500 + 16 per accumulator column for an epilogue, which is hidden
+//    behind the next tile's main loop when the accumulator is double-buffered or a second CTA shares the SM.
+// reduce: 0 none, 1 FP32 partials in the workspace + reduction launch, 2 cluster.
+double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, int tile_n, int tile_k, int split, int reduce) {
   const int c_padded = round_up(d.in_channels, tile_k);
   const int total_kb = d.kernel_h * d.kernel_w * (c_padded / tile_k);
   const int kb_per_split = ceil_div(total_kb, split);
@@ -162,23 +178,40 @@ double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, i
   const int stages = pick_stages(tile_m, tile_n, tile_k, kb_per_split, ctas);
   const size_t smem = conv_tc_smem_bytes(tile_m, tile_n, tile_k, stages);
   if (smem > kMaxDynamicSmem) return 1e300;
+  const int mh = tile_m / kTileM;
   const int resident = resident_ctas(tile_m, tile_n, smem);
-  const double ctas_per_sm = double((ctas + kNumSms - 1) / kNumSms);
-  const double mma = double(tile_m) * tile_n * tile_k / 4096.0;  // MACs at 4096 MAC/clk/SM
-  const double bytes = double(stage_bytes_of(tile_m, tile_n, tile_k));
-  // All CTAs of an SM together stream operands at ~47 B/clk; one CTA alone sustains less (one producer thread,
-  // one ring), so a lone fat CTA is charged its own, slower rate.
-  const double slab_shared = fmax(mma, bytes / kFeedBytesPerClk);
-  const double slab_alone = fmax(mma, bytes / 40.0 + 180.0);
-  const double fixed = 4000.0 + double(tile_m / kTileM) * tile_n * 20.0;  // set-up, pipeline fill, serial epilogue
-  const double rounds = ceil(ctas_per_sm / resident);                     // groups of co-resident CTAs, one after another
-  double total = fmax(ctas_per_sm * kb_per_split * slab_shared, rounds * kb_per_split * slab_alone) + rounds * fixed;
+  const double tiles_per_sm = double((ctas + kNumSms - 1) / kNumSms);
+  const double sharing = fmin(double(resident), tiles_per_sm);   // CTAs that really run side by side on an SM
+  const double mmas = double(mh) * (tile_k / 16);
+  const double pipe = mmas * (tile_n / 2.0);
+  const double issue = tile_n >= 256 ? pipe : mmas * 78.0 + 215.0;
+  const double feed = double(stage_bytes_of(tile_m, tile_n, tile_k)) / 74.0;
+  const double slab = fmax(fmax(pipe, feed), issue / sharing);
+  double epilogue = 500.0 + 16.0 * mh * tile_n;
+  if (real_split > 1 && reduce == 1) epilogue *= 2.0;  // FP32 partials: twice the bytes
+  const bool overlapped = sharing >= 2.0 || (mh * tile_n <= 256 && tiles_per_sm >= 2.0);
+  double total = 4500.0 + tiles_per_sm * kb_per_split * slab + (overlapped ? epilogue : tiles_per_sm * epilogue);
   if (real_split > 1) {
-    const double bytes = 2.0 * real_split * double(g.y_elems) * 4.0;
-    total += 9000.0 + bytes / 1500.0;  // extra launch + FP32 partial traffic
+    if (reduce == 2)  // two cluster barriers + pushing all but the own share of the FP32 tile at ~24 B/clk
+      total += 2000.0 + double(real_split - 1) / real_split * (double(kTileM) * tile_n * 4.0) / 24.0;
+    else total += 6000.0 + 2.0 * real_split * double(g.y_elems) * 4.0 / 1500.0;      // extra launch + partial traffic
   }
   return total;
 }
+
+}  // namespace
+
+namespace gieb {
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("GIEB_DISABLE_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+}  // namespace gieb
+
+namespace {
 
 int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, char* why, size_t why_len) {
   auto no = [&](const char* m) { snprintf(why, why_len, "%s", m); return GIEB_UNSUPPORTED; };
@@ -229,7 +262,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   if (c.tile_m != 0 && c.tile_m != 128 && c.tile_m != 256) return no("tile_m must be 128 or 256");
   // search (tile_m, tile_n, split_k) unless fixed
   double best = 1e300;
-  int best_m = 0, best_n = 0, best_s = 0;
+  int best_m = 0, best_n = 0, best_s = 0, best_mode = 0;
   const int n_opts[4] = {32, 64, 128, 256};
   for (int tm = 128; tm <= 256; tm += 128) {
     if (c.tile_m && tm != c.tile_m) continue;
@@ -241,13 +274,26 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
       for (int s = 1; s <= 16; ++s) {
         if (c.split_k && s != c.split_k) continue;
         if (s > 1 && r->total_kb < 2 * s) break;  // reduction too short (src/kernels/tensor_core_mma.cu:292 rule)
-        if (s > 1 && size_t(s) * size_t(g.y_elems) * 4 > (size_t(1) << 31)) break;
-        const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s) + (r->variant == 2 && tn < d.out_channels && tn < 256 ? 1e6 : 0.0);
-        if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; }
+        const int kbs = ceil_div(r->total_kb, s);
+        const bool even = ceil_div(r->total_kb, kbs) == s;  // every slice non-empty
+        const int64_t ctas = int64_t(ceil_div(rows, tm)) * ceil_div(d.out_channels, tn) * s;
+        for (int mode = (s > 1 ? 1 : 0); mode <= (s > 1 ? 2 : 0); ++mode) {
+          if (c.reduce && mode && mode != c.reduce) continue;
+          if (mode == 1 && size_t(s) * size_t(g.y_elems) * 4 > (size_t(1) << 31)) continue;
+          if (mode == 2) {
+            const int st = c.stages ? c.stages : pick_stages(tm, tn, r->tile_k, kbs, ctas);
+            if (!even || !cluster_reduce_ok(tm, tn, r->tile_k, st, s)) continue;
+            // unasked, clusters are used only when the whole grid is one wave of one CTA per SM
+            if (c.reduce == 0 && ctas > kNumSms) continue;
+          }
+          const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s, mode) + (r->variant == 2 && tn < d.out_channels && tn < 256 ? 1e6 : 0.0);
+          if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; best_mode = mode; }
+        }
       }
     }
   }
   if (best_n == 0) {
+    if (c.reduce == 2) return no("cluster reduction needs tile_m 128, split_k 2, 4 or 8 dividing tile_n / 32 with no empty slice, and a ring that holds the received slices");
     if (c.split_k > 1) return no("reduction too short for this split-K factor");
     return no("no feasible tile configuration");
   }
@@ -270,7 +316,12 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   // src/kernels/tensor_core_mma.cu:265-278)
   r->ws_x = align256(size_t(d.batch) * d.in_h * d.in_w * r->c_padded * 2);
   r->ws_w = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : align256(size_t(d.out_channels) * d.kernel_h * d.kernel_w * r->c_padded * 2);
-  r->ws_part = r->split_k > 1 ? align256(size_t(r->split_k) * size_t((g.y_elems + 3) & ~int64_t(3)) * 4) : 0;
+  // how the split-K slices are summed
+  if (c.reduce < 0 || c.reduce > 2) return no("reduce must be 0 (auto), 1 (workspace) or 2 (cluster)");
+  r->reduce = r->split_k > 1 ? best_mode : 0;
+  if (r->reduce == 2 && !cluster_reduce_ok(r->tile_m, r->tile_n, r->tile_k, stages, r->split_k))
+    return no("cluster reduction needs tile_m 128, split_k 2, 4 or 8 dividing tile_n / 32, and a ring that holds the received slices");
+  r->ws_part = r->split_k > 1 && r->reduce == 1 ? align256(size_t(r->split_k) * size_t((g.y_elems + 3) & ~int64_t(3)) * 4) : 0;
   r->ws_total = r->ws_x + r->ws_w + r->ws_part;
   if (r->ws_total > (size_t(180) << 30) / 4) return no("workspace exceeds a quarter of device memory");
   return GIEB_OK;
@@ -286,6 +337,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
   out->cfg.stages = r.stages;
   out->cfg.split_k = r.split_k;
   out->cfg.variant = r.variant;
+  out->cfg.reduce = r.reduce;
   out->workspace_bytes = r.ws_total;
   out->persistent_bytes = sizeof(uint32_t);
   out->padded_channels = r.c_padded;
@@ -298,7 +350,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
     out->dynamic_smem_bytes = uint32_t(r.smem);
     out->threads_per_block = kTcThreads;
     out->num_blocks = int64_t(r.tiles_m) * r.tiles_n * r.split_k;
-    out->launches = 2 + (r.split_k > 1 ? 1 : 0);  // repack (activations + weights in one launch), convolution, reduction
+    out->launches = 2 + (r.reduce == 1 ? 1 : 0);  // repack (activations + weights in one launch), convolution, reduction
   }
 }
 
@@ -437,7 +489,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   const void* wk = w;
   if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)) wk = wsb + r.ws_x;
   else if (reinterpret_cast<uintptr_t>(w) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "prepacked weights must be 16-byte aligned");
-  float* part = r.split_k > 1 ? reinterpret_cast<float*>(wsb + r.ws_x + r.ws_w) : nullptr;
+  float* part = r.reduce == 1 ? reinterpret_cast<float*>(wsb + r.ws_x + r.ws_w) : nullptr;
 
   // A direct-NCHW plan needs a 16-byte aligned x (TMA base address rule); otherwise this call takes the repack route.
   int mode = r.variant == 1 ? 0 : (r.variant == 4 ? 1 : 2);
@@ -486,6 +538,8 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.tiles_m = ceil_div(rows, r.tile_m);
   p.tiles_n = r.tiles_n;
   p.num_tiles = p.tiles_m * p.tiles_n * r.split_k;
+  p.cluster_split = r.reduce == 2 ? r.split_k : 1;
+  p.fd_cluster = FastDiv::make(p.cluster_split);
   p.fd_tiles_mn = FastDiv::make(p.tiles_m * p.tiles_n);
   p.fd_tiles_n = FastDiv::make(p.tiles_n);
   p.fd_pq = FastDiv::make(p.pq);
@@ -495,11 +549,12 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.fd_boxes = FastDiv::make(p.boxes_per_image > 0 ? p.boxes_per_image : 1);
   // persistent CTAs: as many as can be resident at once, each walking the tile list
   const int64_t resident = int64_t(kNumSms) * resident_ctas(r.tile_m, r.tile_n, r.smem);
-  dim3 grid(unsigned(p.num_tiles < resident ? p.num_tiles : resident));
+  // cluster mode: one tile per CTA, blockIdx.x = tile * split + slice (the grid is a multiple of the cluster size)
+  dim3 grid(unsigned(p.cluster_split > 1 || p.num_tiles < resident ? p.num_tiles : resident));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[1], st));
   GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, tm_act, tm_wgt, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
-  if (r.split_k > 1)
+  if (r.reduce == 1)
     GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_bf16, y, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[3], st));
   return GIEB_OK;

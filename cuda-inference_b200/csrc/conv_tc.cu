@@ -111,6 +111,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
   const int tiles_mn = p.tiles_m * p.tiles_n;
+  const bool cluster = p.cluster_split > 1;
   ptx::grid_dep_launch();  // the next kernel of the stream may begin its own set-up (it orders itself with grid_dep_wait)
 
   if (threadIdx.x == 0) {
@@ -164,8 +165,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     int skip = warp;     // slabs of the coming tile that belong to other warps before this warp's first one
     bool alive = warp < np;
     for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
-      const int z = p.fd_tiles_mn.div(tile);
-      const int rest = tile - z * tiles_mn;
+      int z, rest;
+      if (cluster) {  // slices of a tile sit side by side in one cluster
+        rest = p.fd_cluster.div(tile);
+        z = tile - rest * p.cluster_split;
+      } else {
+        z = p.fd_tiles_mn.div(tile);
+        rest = tile - z * tiles_mn;
+      }
       const int m_blk = p.fd_tiles_n.div(rest);
       const int n0 = (rest - m_blk * p.tiles_n) * BN;
       const int m0 = m_blk * (kTileM * MH);
@@ -230,6 +237,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       skip = i - num_kb;  // how far this warp's next slab lies into the next tile
     }
     join_setup();  // warps without a slab of their own
+    if (cluster) {  // the two cluster barriers of the epilogue's reduction count every thread
+      ptx::cluster_sync_all();
+      ptx::cluster_sync_all();
+    }
   } else if (warp == kProducerWarps) {
     // ---------------- MMA issuer ----------------
     // The warp stays converged (all lanes wait and compute the descriptors); one elected lane issues the MMAs and
@@ -239,8 +250,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     uint32_t phase = 0;
     bool alive = true;
     for (int tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x, ++tcount) {
-      const int z = p.fd_tiles_mn.div(tile);
-      const int rest = tile - z * tiles_mn;
+      int z, rest;
+      if (cluster) {  // slices of a tile sit side by side in one cluster
+        rest = p.fd_cluster.div(tile);
+        z = tile - rest * p.cluster_split;
+      } else {
+        z = p.fd_tiles_mn.div(tile);
+        rest = tile - z * tiles_mn;
+      }
       const int m0 = p.fd_tiles_n.div(rest) * (kTileM * MH);
       const int halves = (MH == 2 && m0 + kTileM < p.m_total) ? 2 : 1;
       const int kb_begin = z * p.kb_per_split;
@@ -282,16 +299,41 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       if (ptx::elect_one()) ptx::mma_commit(&acc_full[buf]);
       __syncwarp();
     }
+    if (cluster) {
+      ptx::cluster_sync_all();
+      ptx::cluster_sync_all();
+    }
   } else {
     // ---------------- epilogue: 8 warps.  Warp w may read TMEM lanes 32*(w%4)..+31; warps 4..7 take the even
     // 32-column chunks of a tile, warps 8..11 the odd ones (two warps per scheduler hide each other's latencies).
     const int quad = warp & 3;
     const int par = (warp - kProducerWarps - 1) >> 2;  // 0 or 1: which chunks this warp owns
     const int et = threadIdx.x - 32 * (kProducerWarps + 1);  // 0..255 among the epilogue threads
+    // GEMM row -> (image, pixel within the image, row holds an output pixel at all)
+    auto decode_row = [&](int m, bool& m_ok, int& img, int& pix) {
+      m_ok = m < p.m_total;
+      img = pix = 0;
+      if (p.a_mode == 2) {  // rows are numbered in 64-pixel boxes per image
+        const int box = m >> 6;
+        img = p.fd_boxes.div(box);
+        pix = ((box - img * p.boxes_per_image) << 6) + (m & 63);
+        m_ok = m_ok && pix < p.pq;
+        if (!m_ok) img = pix = 0;
+      } else if (m_ok) {
+        img = p.fd_pq.div(m);
+        pix = m - img * p.pq;
+      }
+    };
     int tcount = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++tcount) {
-      const int z = p.fd_tiles_mn.div(tile);
-      const int rest = tile - z * tiles_mn;
+      int z, rest;
+      if (cluster) {  // slices of a tile sit side by side in one cluster
+        rest = p.fd_cluster.div(tile);
+        z = tile - rest * p.cluster_split;
+      } else {
+        z = p.fd_tiles_mn.div(tile);
+        rest = tile - z * tiles_mn;
+      }
       const int m_blk = p.fd_tiles_n.div(rest);
       const int n0 = (rest - m_blk * p.tiles_n) * BN;
       const int m0 = m_blk * (kTileM * MH);
@@ -317,23 +359,85 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const bool ok = ptx::mbar_wait(&acc_full[buf], acc_phase, p.status, kStatusEpilogueTimeout);
       __syncwarp();
       ptx::tc_fence_after_sync();
-      if (!__all_sync(0xffffffffu, ok)) break;
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (cluster) {  // keep the cluster's barriers balanced so that the peers can leave as well
+          ptx::cluster_sync_all();
+          ptx::cluster_sync_all();
+        }
+        break;
+      }
       const uint32_t acc = tmem_base + buf * ACC_COLS;
+      if (cluster) {
+        // Split-K inside a cluster (MH = 1, one tile per CTA).  CTA `rank` holds the partial sums of K-slice `rank`
+        // for the whole tile and owns the 32-column chunks [rank * cpr, (rank + 1) * cpr): every CTA pushes the
+        // chunks it does not own into the owner's (now idle) operand ring through distributed shared memory, then
+        // each owner adds the received slices to its own in a fixed order (results are run-to-run identical), applies
+        // bias + ReLU and stores.  Receive layout: [sender slot][chunk][group of 4 columns][row][16 bytes]: one warp
+        // instruction writes (and later reads) 512 contiguous bytes.
+        const int nsplit = p.cluster_split;
+        const int rank = int(ptx::cluster_ctarank());
+        const int cpr = (BN / 32) / nsplit;  // chunks per owner
+        const int row = quad * 32 + lane;
+        const uint32_t recv = ptx::smem_u32(stage_base);
+        ptx::cluster_sync_all();  // every CTA of the cluster has finished its MMAs: all rings are idle
+        for (int chunk = par; chunk < BN / 32; chunk += 2) {
+          if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform, same in every CTA of the cluster
+          const int owner = chunk / cpr;
+          if (owner == rank) continue;
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(chunk * 32), v);
+          ptx::tmem_ld_wait();
+          const int slot = rank < owner ? rank : rank - 1;
+          const uint32_t dst = ptx::map_to_cta(recv + uint32_t((slot * cpr + (chunk - owner * cpr)) * (kTileM * 128) + row * 16), uint32_t(owner));
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            ptx::st_cluster_v4(dst + uint32_t(g * (kTileM * 16)), v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        }
+        ptx::cluster_sync_all();  // all pushes have landed
+        const int m = m0 + row;
+        bool m_ok;
+        int img, pix;
+        decode_row(m, m_ok, img, pix);
+        const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
+        for (int chunk = par; chunk < BN / 32; chunk += 2) {
+          if (n0 + chunk * 32 >= p.out_channels) break;
+          if (chunk / cpr != rank) continue;
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(chunk * 32), v);
+          ptx::tmem_ld_wait();
+          const uint8_t* src0 = stage_base + size_t(chunk - rank * cpr) * (kTileM * 128) + row * 16;
+          for (int slot = 0; slot < nsplit - 1; ++slot) {  // own slice first, then the others in a fixed order
+            const uint8_t* src = src0 + size_t(slot) * cpr * (kTileM * 128);
+#pragma unroll
+            for (int gh = 0; gh < 2; ++gh) {  // 4 independent 16-byte loads in flight, then their adds
+              float4 q[4];
+#pragma unroll
+              for (int g = 0; g < 4; ++g) q[g] = *reinterpret_cast<const float4*>(src + (gh * 4 + g) * (kTileM * 16));
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const int j = (gh * 4 + g) * 4;
+                v[j] = __float_as_uint(__uint_as_float(v[j]) + q[g].x);
+                v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + q[g].y);
+                v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + q[g].z);
+                v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + q[g].w);
+              }
+            }
+          }
+          if (m_ok) {
+            const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
+            const int64_t off = base + int64_t(chunk * 32) * p.pq;
+            if (p.is_bf16) store_chunk<__nv_bfloat16>(v, bias_t + chunk * 32, static_cast<__nv_bfloat16*>(p.y) + off, p.pq, nvalid, p.relu);
+            else store_chunk<__half>(v, bias_t + chunk * 32, static_cast<__half*>(p.y) + off, p.pq, nvalid, p.relu);
+          }
+        }
+        break;  // one tile per CTA in this mode
+      }
       float* part = p.partial ? p.partial + int64_t(z) * ((p.y_elems + 3) & ~int64_t(3)) : nullptr;
       for (int h = 0; h < halves; ++h) {
         const int m = m0 + h * kTileM + quad * 32 + lane;
-        bool m_ok = m < p.m_total;
-        int img = 0, pix = 0;
-        if (p.a_mode == 2) {  // rows are numbered in 64-pixel boxes per image
-          const int box = m >> 6;
-          img = p.fd_boxes.div(box);
-          pix = ((box - img * p.boxes_per_image) << 6) + (m & 63);
-          m_ok = m_ok && pix < p.pq;
-          if (!m_ok) img = pix = 0;
-        } else if (m_ok) {
-          img = p.fd_pq.div(m);
-          pix = m - img * p.pq;
-        }
+        bool m_ok;
+        int img, pix;
+        decode_row(m, m_ok, img, pix);
         const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
 #pragma unroll 1
         for (int chunk = par; chunk < BN / 32; chunk += 2) {
@@ -381,7 +485,8 @@ cudaError_t prepare_one(size_t smem_bytes) {
 template <int BN, int BK, int MH>
 cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tw, const ConvTcParams& p, dim3 grid, size_t smem,
                        cudaStream_t st) {
-  cudaError_t e = launch_pdl(conv_tc_kernel<BN, BK, MH>, grid, dim3(kTcThreads), smem, st, ta, tw, p);
+  cudaError_t e = launch_pdl_cluster(conv_tc_kernel<BN, BK, MH>, grid, dim3(kTcThreads), smem, st,
+                                     unsigned(p.cluster_split > 1 ? p.cluster_split : 1), ta, tw, p);
   if (e != cudaSuccess) return e;
   return cudaGetLastError();
 }

@@ -57,19 +57,38 @@ struct FastDiv {
 // Launch with programmatic stream serialization: the grid may be scheduled before the previous kernel of the stream
 // has finished; the kernel orders itself with ptx::grid_dep_wait().  Works under stream capture (the edge becomes a
 // programmatic dependency of the graph).
+// GIEB_DISABLE_PDL=1 in the environment launches every kernel fully serialised (a debugging aid).
+bool pdl_enabled();
+
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      unsigned cluster_x, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  return launch_pdl_cluster(kernel, grid, block, smem, stream, 1u, static_cast<Args&&>(args)...);
 }
 #endif
 
@@ -99,6 +118,10 @@ struct ConvTcParams {
   int a_mode;
   int boxes_per_image;  // mode 2: ceil(H*W / 64)
   uint32_t idesc;
+  // > 1: split-K slices of one tile form a thread-block cluster (cluster rank = slice) and are summed through
+  // distributed shared memory; blockIdx.x = tile * cluster_split + slice, one tile per CTA, `partial` unused.
+  int cluster_split;
+  FastDiv fd_cluster;
   FastDiv fd_tiles_mn, fd_tiles_n, fd_pq, fd_out_w, fd_kb_per_tap, fd_kernel_w, fd_boxes;  // reciprocals of the fields above
   const void* bias;
   void* y;            // NCHW output in the storage type (split_k == 1)

@@ -78,7 +78,11 @@ typedef struct gieb_conv_cfg {
                            (1x1, stride 1, pad 0, H*W % 8 == 0; a call whose x is not 16-byte aligned takes route 4);
                        3 = FP32 SIMT                                                                          */
   int32_t tile_m;   /* output pixels per CTA tile: 128 or 256 (two accumulators share each weight tile); 0 = auto */
-  int32_t reserved[2];
+  int32_t reduce;   /* how split-K slices are summed: 0 = auto; 1 = FP32 partials in the workspace + a reduction launch;
+                       2 = inside the convolution kernel: the slices of a tile form a thread-block cluster and are
+                           summed through distributed shared memory (split_k 2, 4 or 8 dividing tile_n / 32,
+                           tile_m 128); no partials in the workspace, no extra launch                       */
+  int32_t reserved;
 } gieb_conv_cfg;
 
 /* What KernelDesc::supports / workspace_bytes / dynamic_smem_bytes / num_blocks answer

@@ -65,6 +65,13 @@ TILE_CASES = [
     ((2, 64, 28, 28, 128, 3, 3, 2, 2, 1, 1), dict(tile_n=128, tile_k=64, stages=4)),
     ((2, 8, 17, 23, 12, 3, 5, 2, 1, 1, 2), dict(tile_n=32, tile_k=16, stages=3, split_k=5)),
     ((4, 96, 27, 27, 192, 5, 5, 1, 1, 2, 2), dict(tile_n=64, tile_k=32, stages=8, split_k=2)),
+    # split-K summed inside the kernel: the slices of a tile form a cluster and exchange partials through distributed shared memory
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_n=64, tile_k=64, stages=3, split_k=2, reduce=2)),
+    ((8, 64, 14, 14, 128, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=32, stages=4, split_k=4, reduce=2)),
+    ((2, 130, 9, 9, 130, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=3, split_k=2, reduce=2)),
+    ((1, 512, 7, 7, 512, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=64, stages=4, split_k=8, reduce=2)),
+    ((32, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=4, split_k=2, reduce=2)),
+    ((3, 200, 10, 20, 255, 1, 1, 1, 1, 0, 0), dict(tile_n=256, tile_k=32, stages=3, split_k=2, reduce=2, variant=4)),
     # 256-pixel tiles: two accumulators per CTA share each weight tile
     ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=64, tile_k=64, stages=3)),
     ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=256, tile_k=64, stages=3, split_k=2)),
@@ -103,6 +110,12 @@ DIRECT_CASES = [
     ((2, 64, 16, 16, 48, 1, 1, 1, 1, 0, 0), dict(variant=2), 1),                                         # x off by 2 bytes: repack route
     ((2, 64, 16, 16, 48, 1, 1, 1, 1, 0, 0), dict(variant=4), 0),
     ((2, 64, 16, 16, 48, 1, 1, 1, 1, 0, 0), dict(variant=1), 0),
+    ((2, 512, 8, 8, 256, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=256, tile_k=64, stages=4), 0),       # one image per 64-pixel box
+    ((2, 512, 8, 8, 256, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=128, tile_k=64, stages=4), 0),
+    ((4, 512, 8, 8, 256, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=256, tile_k=64, stages=3), 0),
+    # cluster reduction on the direct route: rows are numbered in 64-pixel boxes, 16 or 24 of them real pixels
+    ((2, 1024, 4, 4, 256, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=256, tile_k=64, stages=4, split_k=4, reduce=2), 0),
+    ((3, 256, 4, 6, 200, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=128, tile_k=64, stages=2, split_k=2, reduce=2), 0),
 ]
 
 
