@@ -28,7 +28,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (None where no capture exists yet).
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"c2": 4466688}  # profiles/conv_tc_kernel_c2_fp16.md
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -309,15 +309,39 @@ def time_conv_e2e(torch, pkg, shape, plan, steps):
 
 
 def cpu_reference_runner():
-    """Returns (callable(problem_args, x, w, b) -> y, kind, threads) for the CPU baseline: the reference's own CPU code
-    when oracle/_ref exists, else the C restatement."""
+    """Returns (orc, oracle, conv(problem, x, w, b) -> y, kind, threads) for the CPU baseline: the reference's own CPU
+    code when oracle/_ref exists, else the C restatement.  Both use every host core the process may run on, whatever
+    OMP_NUM_THREADS a launcher exported: the reference's convolution is a scalar function, so whole images are dealt
+    to a pool of threads (ctypes calls release the GIL); the restatement is OpenMP code."""
+    import numpy as np
+    from concurrent.futures import ThreadPoolExecutor
     orc = entry.load_oracle()
     o = orc.Oracle()
-    threads = o.num_threads()
+    try:
+        threads = len(os.sched_getaffinity(0))
+    except AttributeError:
+        threads = os.cpu_count() or 1
     if orc.Reference.available():
         r = orc.Reference()
-        return orc, o, (lambda p, x, w, b: r.conv2d(p, x, w, b)[0]), "reference", threads
-    return orc, o, (lambda p, x, w, b: o.conv2d(p, x, w, b, want_scale=False)[0]), "port", threads
+        pool = ThreadPoolExecutor(max_workers=threads)
+
+        def conv(p, x, w, b):
+            parts = min(threads, p.batch)
+            if parts <= 1:
+                return r.conv2d(p, x, w, b)[0]
+            bounds = [p.batch * i // parts for i in range(parts + 1)]
+
+            def one(i):
+                lo, hi = bounds[i], bounds[i + 1]
+                sub = orc.Problem.P(hi - lo, p.in_channels, p.in_h, p.in_w, p.out_channels, p.kernel_h, p.kernel_w, p.stride_h,
+                                    p.stride_w, p.pad_h, p.pad_w, p.precision, p.has_bias, p.relu)
+                return r.conv2d(sub, np.ascontiguousarray(x[lo:hi]), w, b)[0]
+
+            return np.concatenate(list(pool.map(one, range(parts))), axis=0)
+
+        return orc, o, conv, "reference", threads
+    o.set_num_threads(threads)
+    return orc, o, (lambda p, x, w, b: o.conv2d(p, x, w, b, want_scale=False)[0]), "port", o.num_threads()
 
 
 def cpu_baseline_leg(torch, shape, host_inputs, gpu_y, budget_s=12.0):
