@@ -22,6 +22,7 @@ STATUS_NAMES = {0: "ok", 1: "invalid_argument", 2: "unsupported", 3: "workspace_
 # gie::Precision order
 FP32, FP16, BF16, TF32 = 0, 1, 2, 3
 FLAG_BIAS_FP32, FLAG_WEIGHTS_PREPACKED = 1, 2
+FLAG_INPUT_NHWC, FLAG_OUTPUT_NHWC, FLAG_RESIDUAL = 4, 8, 16
 
 
 class GieError(RuntimeError):
@@ -74,6 +75,7 @@ def lib() -> C.CDLL:
         L.gieb_conv_plan_destroy.restype = None
         L.gieb_conv_plan_info.argtypes = [vp, C.POINTER(ConvInfo)]
         L.gieb_conv_launch.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp]
+        L.gieb_conv_launch_fused.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.gieb_conv_time_stages.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp, i32, C.POINTER(C.c_float)]
         L.gieb_conv_forward_static.argtypes = [C.POINTER(ConvDesc), C.POINTER(ConvCfg), vp, vp, vp, vp, vp]
         L.gieb_conv_plan_device_status.argtypes = [vp, C.POINTER(C.c_uint32)]
@@ -82,6 +84,7 @@ def lib() -> C.CDLL:
         L.gieb_rmsnorm_launch.argtypes = [C.POINTER(RmsNormDesc), vp, vp, vp, vp, vp, vp]
         L.gieb_bias_act_launch.argtypes = [i32, i32, i32, i32, vp, i32, vp, vp]
         L.gieb_maxpool2d_launch.argtypes = [i32] * 8 + [vp, vp, vp]
+        L.gieb_maxpool2d_nhwc_launch.argtypes = [i32] * 8 + [vp, vp, vp]
         L.gieb_add_relu_launch.argtypes = [i32, i32, vp, vp, vp, i64, vp]
         _lib = L
     return _lib
@@ -171,6 +174,12 @@ class ConvPlan:
         """execute_unchecked: raw device pointers, asynchronous on `stream`."""
         check(lib().gieb_conv_launch(self._h, x, w, bias, y, workspace, workspace_bytes, stream))
 
+    def launch_fused(self, x: int, w: int, bias: int | None, residual: int, y: int, workspace: int | None, workspace_bytes: int,
+                     stream: int = 0) -> None:
+        """launch() with a residual tensor (shape, layout and type of y) added before the activation; for plans whose
+        problem carries FLAG_RESIDUAL."""
+        check(lib().gieb_conv_launch_fused(self._h, x, w, bias, residual, y, workspace, workspace_bytes, stream))
+
     def time_stages(self, x, w, bias, y, workspace, workspace_bytes, stream=0, iters=100):
         """Average milliseconds per call of (repack + prepack, convolution kernel, split-K reduction)."""
         ms = (C.c_float * 3)()
@@ -224,6 +233,12 @@ def bias_act(precision: int, batch: int, channels: int, hw: int, bias: int | Non
 def maxpool2d(precision: int, batch: int, channels: int, h: int, w: int, kernel: int, stride: int, pad: int, x: int, y: int,
               stream: int = 0) -> None:
     check(lib().gieb_maxpool2d_launch(precision, batch, channels, h, w, kernel, stride, pad, x, y, stream))
+
+
+def maxpool2d_nhwc(precision: int, batch: int, channels: int, h: int, w: int, kernel: int, stride: int, pad: int, x: int, y: int,
+                   stream: int = 0) -> None:
+    """maxpool2d on channel-contiguous [B][H][W][C] tensors (fp16 / bf16, C % 8 == 0)."""
+    check(lib().gieb_maxpool2d_nhwc_launch(precision, batch, channels, h, w, kernel, stride, pad, x, y, stream))
 
 
 def add_relu(precision: int, relu: bool, a: int, b: int, y: int, n: int, stream: int = 0) -> None:

@@ -7,8 +7,9 @@ from __future__ import annotations
 
 import math
 
-from . import ConvPlan, ConvProblem, add_relu, maxpool2d
-from .workloads import FP16, BF16, chain_flops, resnet50_chain
+from . import (ConvPlan, ConvProblem, add_relu, maxpool2d, maxpool2d_nhwc, prepack_weights, FLAG_INPUT_NHWC, FLAG_OUTPUT_NHWC,
+               FLAG_RESIDUAL, FLAG_WEIGHTS_PREPACKED)
+from .workloads import FP16, BF16, chain_flops, fuse_residuals, resnet50_chain
 
 
 def _torch():
@@ -35,26 +36,45 @@ def layer_weight_bound(shape, relu: bool) -> float:
 
 
 class ConvChain:
-    def __init__(self, batch: int, precision: int = FP16, image: int = 224, seed: int = 0, weights=None, device=None):
-        """weights: optional list of (w, b) host numpy arrays in storage bit patterns per convolution (tests); when
-        None, weights are generated on the device from `seed` + layer index with the benchmark distributions."""
+    def __init__(self, batch: int, precision: int = FP16, image: int = 224, seed: int = 0, weights=None, device=None,
+                 layout: str = "nchw"):
+        """weights: optional list of (w, b) host numpy arrays in storage bit patterns per convolution, in the order of
+        resnet50_chain (tests); when None, weights are generated on the device from `seed` + layer index with the
+        benchmark distributions.
+        layout "nchw": every tensor NCHW, every layer repacks (the reference API's contract, layer by layer).
+        layout "nhwc": the input image stays NCHW; every later tensor is channel-contiguous, weights are prepacked once
+        at construction, and each block's residual add + ReLU runs inside the epilogue of its last convolution
+        (no repack launches, no add launches)."""
         torch = _torch()
         self.torch = torch
+        if layout not in ("nchw", "nhwc"):
+            raise ValueError("layout must be 'nchw' or 'nhwc'")
+        self.layout = layout
         self.batch, self.precision, self.image = batch, precision, image
         self.dtype = torch.float16 if precision == FP16 else torch.bfloat16
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-        self.ops, self.slot_shapes = resnet50_chain(batch, precision, image)
+        base_ops, self.slot_shapes = resnet50_chain(batch, precision, image)
+        nhwc = layout == "nhwc"
+        base_relu = {op.layer: op.relu for op in base_ops if op.kind == "conv"}
+        self.ops = fuse_residuals(base_ops) if nhwc else base_ops
         self.flops = chain_flops(self.ops)
         self.slots = {i: torch.empty(batch * c * h * w, dtype=self.dtype, device=self.device) for i, (c, h, w) in self.slot_shapes.items()}
-        self.convs = []  # (op, plan, w, b)
+        self.convs = []  # (op, plan, w, b) in launch order; w is prepacked in the nhwc layout
         ws_bytes = 256
-        li = 0
         for op in self.ops:
             if op.kind != "conv":
                 continue
             s = op.shape
+            li = op.layer
+            flags = 0
+            if nhwc:
+                flags = FLAG_OUTPUT_NHWC | FLAG_WEIGHTS_PREPACKED
+                if op.src != 0:
+                    flags |= FLAG_INPUT_NHWC  # the image itself (3 channels) stays NCHW and is repacked by the stem
+                if op.other >= 0:
+                    flags |= FLAG_RESIDUAL
             plan = ConvPlan(ConvProblem(s.batch, s.in_channels, s.in_h, s.in_w, s.out_channels, s.kernel, s.kernel, s.stride, s.stride,
-                                        s.pad, s.pad, 1, 1, 1, precision, True, op.relu))
+                                        s.pad, s.pad, 1, 1, 1, precision, True, op.relu, flags))
             if weights is not None:
                 import numpy as np
                 w = torch.from_numpy(weights[li][0].view(np.int16)).to(self.device).view(self.dtype)
@@ -62,12 +82,19 @@ class ConvChain:
             else:
                 g = torch.Generator(device=self.device)
                 g.manual_seed(seed + li)
-                bound = layer_weight_bound(s, op.relu)
+                # a layer followed by ReLU (directly, or through the block's residual add) draws with gain sqrt(2)
+                bound = layer_weight_bound(s, base_relu[li])
                 w = ((torch.rand(s.w_elems, device=self.device, generator=g) * 2 - 1) * bound).to(self.dtype)
                 b = ((torch.rand(s.out_channels, device=self.device, generator=g) * 2 - 1) * 0.1).to(self.dtype)
+            if nhwc:  # static weights: [O][C][RS] -> [O][RS][Cp] once, here
+                cp = plan.info.padded_channels
+                wp = torch.empty(s.out_channels * s.kernel * s.kernel * cp, dtype=self.dtype, device=self.device)
+                prepack_weights(w.data_ptr(), wp.data_ptr(), s.out_channels, s.in_channels, s.kernel * s.kernel, cp,
+                                torch.cuda.current_stream().cuda_stream)
+                w = wp
             self.convs.append((op, plan, w, b))
             ws_bytes = max(ws_bytes, plan.workspace_bytes)
-            li += 1
+        torch.cuda.current_stream().synchronize()
         self._ws = torch.empty(ws_bytes + 256, dtype=torch.uint8, device=self.device)
         self.ws_ptr = (self._ws.data_ptr() + 255) // 256 * 256
         self.ws_bytes = ws_bytes
@@ -89,11 +116,16 @@ class ConvChain:
             if op.kind == "conv":
                 _, plan, w, b = self.convs[ci]
                 ci += 1
-                plan.launch(self.slots[op.src].data_ptr(), w.data_ptr(), b.data_ptr(), self.slots[op.dst].data_ptr(), self.ws_ptr,
-                            self.ws_bytes, stream)
+                if op.other >= 0 and self.layout == "nhwc":
+                    plan.launch_fused(self.slots[op.src].data_ptr(), w.data_ptr(), b.data_ptr(), self.slots[op.other].data_ptr(),
+                                      self.slots[op.dst].data_ptr(), self.ws_ptr, self.ws_bytes, stream)
+                else:
+                    plan.launch(self.slots[op.src].data_ptr(), w.data_ptr(), b.data_ptr(), self.slots[op.dst].data_ptr(), self.ws_ptr,
+                                self.ws_bytes, stream)
             elif op.kind == "maxpool":
                 c, h, w, k, s, p = op.pool
-                maxpool2d(self.precision, self.batch, c, h, w, k, s, p, self.slots[op.src].data_ptr(), self.slots[op.dst].data_ptr(), stream)
+                pool = maxpool2d_nhwc if self.layout == "nhwc" else maxpool2d
+                pool(self.precision, self.batch, c, h, w, k, s, p, self.slots[op.src].data_ptr(), self.slots[op.dst].data_ptr(), stream)
             else:
                 n = self.slots[op.dst].numel()
                 add_relu(self.precision, op.relu, self.slots[op.src].data_ptr(), self.slots[op.other].data_ptr(),

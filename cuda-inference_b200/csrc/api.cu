@@ -102,6 +102,7 @@ struct Resolved {
   int variant;
   int boxes_per_image;  // variant 2: ceil(H*W / 64)
   int tile_m, tile_n, tile_k, stages, split_k;
+  int tma_epilogue;  // channel-contiguous output staged in shared memory and written by TMA stores
   int reduce;  // 1 workspace partials + reduction launch, 2 cluster (distributed shared memory); 0 when split_k == 1
   int c_padded, kb_per_tap, total_kb, kb_per_split;
   int tiles_m, tiles_n;
@@ -139,7 +140,7 @@ int resident_ctas(int tile_m, int tile_n, size_t smem) {
 
 // Ring depth: deep enough to cover L2 latency, shallow enough that two CTAs share an SM when more than one wave of
 // CTAs exists (their epilogues then overlap with another CTA's main loop).
-int pick_stages(int tile_m, int tile_n, int tile_k, int kb_per_split, int64_t ctas) {
+int pick_stages(int tile_m, int tile_n, int tile_k, int kb_per_split, int64_t ctas, size_t extra_smem = 0) {
   const size_t sb = stage_bytes_of(tile_m, tile_n, tile_k);
   const int by_tmem = 512 / tmem_cols_of(tile_m, tile_n);
   // measured: with >= 2.5 tiles per SM three shallow CTAs per SM beat two deeper ones; between 1 and 2.5 two CTAs win
@@ -147,7 +148,7 @@ int pick_stages(int tile_m, int tile_n, int tile_k, int kb_per_split, int64_t ct
   if (ctas > kNumSms) want = 2;  // two CTAs per SM (the register file holds no more)
   if (want > by_tmem) want = by_tmem;
   const size_t budget = want == 1 ? kSmemBudget : (kMaxDynamicSmem / want - 2048);
-  int stages = int((budget - 3072) / sb);
+  int stages = budget > 3072 + extra_smem + sb ? int((budget - 3072 - extra_smem) / sb) : 1;
   if (stages > 6) stages = 6;
   if (stages > kb_per_split) stages = kb_per_split;
   if (stages < 2) stages = 2;
@@ -176,7 +177,7 @@ double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, i
   const int real_split = ceil_div(total_kb, kb_per_split);
   const int64_t ctas = int64_t(ceil_div(g.pixels, tile_m)) * ceil_div(d.out_channels, tile_n) * real_split;
   const int stages = pick_stages(tile_m, tile_n, tile_k, kb_per_split, ctas);
-  const size_t smem = conv_tc_smem_bytes(tile_m, tile_n, tile_k, stages);
+  const size_t smem = conv_tc_smem_bytes(tile_m, tile_n, tile_k, stages, false);
   if (smem > kMaxDynamicSmem) return 1e300;
   const int mh = tile_m / kTileM;
   const int resident = resident_ctas(tile_m, tile_n, smem);
@@ -224,7 +225,8 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   if (d.precision == GIEB_TF32) return no("TF32 is not offered: the only TF32 route of the reference is its cuBLAS im2col backend");
   if (d.precision == GIEB_FP32) {
     if (c.variant != 0 && c.variant != 3) return no("FP32 runs on the SIMT kernel only (variant 3)");
-    if (d.flags & (GIEB_FLAG_WEIGHTS_PREPACKED)) return no("prepacked weights apply to the 16-bit tensor path only");
+    if (d.flags & (GIEB_FLAG_WEIGHTS_PREPACKED | GIEB_FLAG_INPUT_NHWC | GIEB_FLAG_OUTPUT_NHWC | GIEB_FLAG_RESIDUAL))
+      return no("prepacked weights, channel-contiguous tensors and the fused residual apply to the 16-bit tensor path only");
     r->variant = 3;
     r->tile_m = r->tile_n = conv_fp32_tile(g.pixels, d.out_channels);
     r->tile_k = 16;
@@ -239,7 +241,12 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
     return no("unknown kernel variant for 16-bit precision (1 = im2col-mode TMA, 2 = direct NCHW 1x1, 4 = tiled TMA for 1x1)");
   if (c.variant == 4 && !pointwise) return no("variant 4 (tiled activation loads) needs a 1x1 kernel with stride 1 and no padding");
   if (c.variant == 2 && !direct_ok) return no("variant 2 (direct NCHW loads) needs a 1x1 kernel, stride 1, no padding and H*W % 8 == 0");
-  r->variant = c.variant ? c.variant : (direct_ok ? 2 : (pointwise ? 4 : 1));
+  const bool in_nhwc = (d.flags & GIEB_FLAG_INPUT_NHWC) != 0;
+  if (in_nhwc) {
+    if (d.in_channels % 16 != 0) return no("channel-contiguous input needs a channel count that is a multiple of 16");
+    if (c.variant == 2) return no("variant 2 reads NCHW activations; a channel-contiguous input takes variant 1 or 4");
+  }
+  r->variant = c.variant ? c.variant : (in_nhwc ? (pointwise ? 4 : 1) : (direct_ok ? 2 : (pointwise ? 4 : 1)));
   r->boxes_per_image = ceil_div(int64_t(d.in_h) * d.in_w, 64);
   // GEMM rows: output pixels, or (variant 2) 64-pixel boxes that never straddle an image
   const int64_t rows = r->variant == 2 ? int64_t(d.batch) * r->boxes_per_image * 64 : g.pixels;
@@ -248,8 +255,9 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   if (d.stride_h > 8 || d.stride_w > 8) return no("stride > 8 cannot be expressed by the TMA im2col traversal stride");
   if (d.pad_h > 127 || d.pad_w > 127 || d.kernel_h > 128 || d.kernel_w > 128) return no("padding/kernel extent exceeds the TMA im2col corner range");
 
-  r->tile_k = c.tile_k ? c.tile_k : pick_tile_k(d.in_channels);
+  r->tile_k = c.tile_k ? c.tile_k : (in_nhwc ? (d.in_channels % 64 == 0 ? 64 : (d.in_channels % 32 == 0 ? 32 : 16)) : pick_tile_k(d.in_channels));
   if (r->tile_k != 16 && r->tile_k != 32 && r->tile_k != 64) return no("tile_k must be 16, 32 or 64");
+  if (in_nhwc && d.in_channels % r->tile_k != 0) return no("tile_k must divide the channel count of a channel-contiguous input (it is read in place)");
   r->c_padded = round_up(d.in_channels, r->tile_k);
   r->kb_per_tap = r->c_padded / r->tile_k;
   r->total_kb = d.kernel_h * d.kernel_w * r->kb_per_tap;
@@ -305,16 +313,20 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   r->tiles_n = ceil_div(d.out_channels, r->tile_n);
   if (int64_t(r->tiles_m) * r->tiles_n * r->split_k > 2147483647LL) return no("tile count exceeds 32-bit indexing");
 
+  // Channel-contiguous output goes through shared-memory boxes and TMA stores when the rows of the [pixels][O] matrix
+  // are 16-byte multiples, rows are numbered by pixel (not the direct-NCHW route) and each CTA finishes its tiles alone.
+  r->tma_epilogue = (d.flags & GIEB_FLAG_OUTPUT_NHWC) && d.out_channels % 8 == 0 && r->variant != 2 && r->split_k == 1;
+  const size_t epi_smem = r->tma_epilogue ? conv_tc_epilogue_staging_bytes(r->tile_n) : 0;
   const int stages = c.stages ? c.stages
-                              : pick_stages(r->tile_m, r->tile_n, r->tile_k, r->kb_per_split, int64_t(r->tiles_m) * r->tiles_n * r->split_k);
+                              : pick_stages(r->tile_m, r->tile_n, r->tile_k, r->kb_per_split, int64_t(r->tiles_m) * r->tiles_n * r->split_k, epi_smem);
   if (stages < 2 || stages > kMaxStages) return no("stages must be in [2, 8]");
   r->stages = stages;
-  r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages);
+  r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, r->tma_epilogue != 0);
   if (r->smem > kMaxDynamicSmem) return no("configuration needs more shared memory than one CTA may have (227 KiB)");
 
   // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
   // src/kernels/tensor_core_mma.cu:265-278)
-  r->ws_x = align256(size_t(d.batch) * d.in_h * d.in_w * r->c_padded * 2);
+  r->ws_x = in_nhwc ? 0 : align256(size_t(d.batch) * d.in_h * d.in_w * r->c_padded * 2);
   r->ws_w = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : align256(size_t(d.out_channels) * d.kernel_h * d.kernel_w * r->c_padded * 2);
   // how the split-K slices are summed
   if (c.reduce < 0 || c.reduce > 2) return no("reduce must be 0 (auto), 1 (workspace) or 2 (cluster)");
@@ -350,7 +362,10 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
     out->dynamic_smem_bytes = uint32_t(r.smem);
     out->threads_per_block = kTcThreads;
     out->num_blocks = int64_t(r.tiles_m) * r.tiles_n * r.split_k;
-    out->launches = 2 + (r.reduce == 1 ? 1 : 0);  // repack (activations + weights in one launch), convolution, reduction
+    // repack (activations and weights in one launch; none when both are consumed in place), convolution, reduction
+    const bool x_in_place = r.variant == 2 || (d.flags & GIEB_FLAG_INPUT_NHWC);
+    const bool w_in_place = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) != 0;
+    out->launches = (x_in_place && w_in_place ? 0 : 1) + 1 + (r.reduce == 1 ? 1 : 0);
   }
 }
 
@@ -454,16 +469,36 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
   return GIEB_OK;
 }
 
+// The output (or the residual) of a channel-contiguous plan as the 2-D tensor {O channels, B*P*Q pixels}: boxes of
+// 32 channels x 32 pixels with 64-byte swizzle, the unit one epilogue warp stages per TMA store / load.
+int encode_epilogue_map(const gieb_conv_plan* pl, const void* ptr, CUtensorMap* tm) {
+  const gieb_conv_desc& d = pl->desc;
+  const CUtensorMapDataType dt = d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint64_t dims[2] = {cuuint64_t(d.out_channels), cuuint64_t(pl->g.pixels)};
+  const cuuint64_t strides[1] = {cuuint64_t(d.out_channels) * 2};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult res = g_encode_tiled(tm, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (epilogue tensor) failed with CUresult %d", int(res));
+  small_tensor_fixup(tm, size_t(pl->g.pixels) * d.out_channels * 2);
+  return GIEB_OK;
+}
+
 // `ev`, when given, receives four stage marks: before the repack, before the convolution kernel, after it, and
 // after the split-K reduction (LaunchArgs::stage_events analogue, include/gpu_inference/kernel_registry.h:38-40).
 int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
-                cudaStream_t st, cudaEvent_t* ev = nullptr) {
+                cudaStream_t st, cudaEvent_t* ev = nullptr, const void* residual = nullptr) {
   if (pl == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null plan");
   const gieb_conv_desc& d = pl->desc;
   const Resolved& r = pl->r;
   if (x == nullptr || w == nullptr || y == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
   if (d.has_bias && bias == nullptr) return fail(GIEB_INVALID_ARGUMENT, "problem has a bias but no bias pointer was given");
   if (!d.has_bias) bias = nullptr;
+  if ((d.flags & GIEB_FLAG_RESIDUAL) && residual == nullptr)
+    return fail(GIEB_INVALID_ARGUMENT, "plan has a fused residual: launch it with gieb_conv_launch_fused and a residual pointer");
+  if (!(d.flags & GIEB_FLAG_RESIDUAL) && residual != nullptr)
+    return fail(GIEB_INVALID_ARGUMENT, "a residual was given but the plan was created without GIEB_FLAG_RESIDUAL");
   if (r.ws_total > 0) {
     if (reinterpret_cast<uintptr_t>(ws) % 256 != 0) return fail(GIEB_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
     if (ws == nullptr || ws_bytes < r.ws_total)
@@ -494,6 +529,11 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   // A direct-NCHW plan needs a 16-byte aligned x (TMA base address rule); otherwise this call takes the repack route.
   int mode = r.variant == 1 ? 0 : (r.variant == 4 ? 1 : 2);
   if (mode == 2 && reinterpret_cast<uintptr_t>(x) % 16 != 0) mode = 1;
+  const bool in_nhwc = (d.flags & GIEB_FLAG_INPUT_NHWC) != 0;
+  if (in_nhwc) {  // read in place
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "a channel-contiguous input must be 16-byte aligned");
+    xn = const_cast<void*>(x);
+  }
   const int64_t rows = mode == 2 ? int64_t(d.batch) * r.boxes_per_image * 64 : pl->g.pixels;
 
   CUtensorMap tm_act, tm_wgt;
@@ -501,9 +541,9 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   if (st_maps != GIEB_OK) return st_maps;
 
   if (ev) GIEB_CUDA(cudaEventRecord(ev[0], st));
-  if (mode == 2) {
+  if (mode == 2 || in_nhwc) {
     if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED))
-      GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, 1, r.c_padded, st));
+      GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
   } else if (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)
     GIEB_CUDA(repack_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, st));
   else
@@ -532,6 +572,8 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.a_mode = mode;
   p.idesc = ptx::make_idesc_f16(kTileM, r.tile_n, p.is_bf16, mode == 2, false);
   p.bias = bias;
+  p.residual = residual;
+  p.out_nhwc = (d.flags & GIEB_FLAG_OUTPUT_NHWC) ? 1 : 0;
   p.y = y;
   p.partial = part;
   p.status = pl->d_status;
@@ -552,10 +594,25 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   // cluster mode: one tile per CTA, blockIdx.x = tile * split + slice (the grid is a multiple of the cluster size)
   dim3 grid(unsigned(p.cluster_split > 1 || p.num_tiles < resident ? p.num_tiles : resident));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[1], st));
-  GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, tm_act, tm_wgt, p, grid, r.smem, st));
+  // TMA epilogue: needs 16-byte aligned tensors; a call that is not takes the direct stores (the staging stays unused)
+  CUtensorMap tm_out, tm_res;
+  memset(&tm_out, 0, sizeof(tm_out));
+  memset(&tm_res, 0, sizeof(tm_res));
+  if (r.tma_epilogue && mode != 2 && reinterpret_cast<uintptr_t>(y) % 16 == 0 && reinterpret_cast<uintptr_t>(residual) % 16 == 0) {
+    const int so = encode_epilogue_map(pl, y, &tm_out);
+    if (so != GIEB_OK) return so;
+    p.out_tma = 1;
+    if (residual != nullptr) {
+      const int sr = encode_epilogue_map(pl, residual, &tm_res);
+      if (sr != GIEB_OK) return sr;
+      p.res_tma = 1;
+    }
+  }
+  GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
   if (r.reduce == 1)
-    GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_bf16, y, st));
+    GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_bf16, residual,
+                                   p.out_nhwc, y, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[3], st));
   return GIEB_OK;
 }
@@ -653,6 +710,11 @@ int gieb_conv_plan_info(const gieb_conv_plan* plan, gieb_conv_info* out) {
 int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y, void* workspace,
                      size_t workspace_bytes, void* stream) {
   return launch_impl(plan, x, w, bias, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int gieb_conv_launch_fused(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, const void* residual, void* y,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+  return launch_impl(plan, x, w, bias, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), nullptr, residual);
 }
 
 int gieb_conv_time_stages(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y, void* workspace,
@@ -794,6 +856,19 @@ int gieb_maxpool2d_launch(int precision, int batch, int channels, int h, int w, 
   if (h + 2 * pad < kernel || w + 2 * pad < kernel) return fail(GIEB_INVALID_ARGUMENT, "window larger than padded input");
   if (precision < 0 || precision > 2) return fail(GIEB_INVALID_ARGUMENT, "precision must be fp32, fp16 or bf16");
   GIEB_CUDA(maxpool2d_launch(precision, batch, channels, h, w, kernel, stride, pad, x, y, static_cast<cudaStream_t>(stream)));
+  return GIEB_OK;
+}
+
+int gieb_maxpool2d_nhwc_launch(int precision, int batch, int channels, int h, int w, int kernel, int stride, int pad, const void* x,
+                               void* y, void* stream) {
+  if (x == nullptr || y == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
+  if (batch <= 0 || channels <= 0 || h <= 0 || w <= 0 || kernel <= 0 || stride <= 0 || pad < 0 || pad >= kernel)
+    return fail(GIEB_INVALID_ARGUMENT, "bad pooling geometry");
+  if (h + 2 * pad < kernel || w + 2 * pad < kernel) return fail(GIEB_INVALID_ARGUMENT, "window larger than padded input");
+  if (precision != GIEB_FP16 && precision != GIEB_BF16) return fail(GIEB_INVALID_ARGUMENT, "channel-contiguous pooling handles fp16 and bf16");
+  if (channels % 8 != 0) return fail(GIEB_INVALID_ARGUMENT, "channel-contiguous pooling needs a channel count that is a multiple of 8");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "tensors must be 16-byte aligned");
+  GIEB_CUDA(maxpool2d_nhwc_launch(precision, batch, channels, h, w, kernel, stride, pad, x, y, static_cast<cudaStream_t>(stream)));
   return GIEB_OK;
 }
 

@@ -52,28 +52,123 @@ __device__ __forceinline__ void store_chunk_full(const uint32_t (&v)[32], const 
   }
 }
 
+template <typename T>
+__device__ __forceinline__ float load_as_float(const T* p) {
+  if constexpr (std::is_same<T, __half>::value) return __half2float(*p);
+  else return __bfloat162float(*p);
+}
+
+// General form: any element stride, partial chunks, optional residual (same layout as the output).
 template <typename T, bool RELU>
-__device__ __forceinline__ void store_chunk_tail(const uint32_t (&v)[32], const float* __restrict__ bias, T* __restrict__ dst,
+__device__ __forceinline__ void store_chunk_tail(const uint32_t (&v)[32], const float* __restrict__ bias, T* dst, const T* res,
                                                  int64_t stride, int nvalid) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
-    float a = __uint_as_float(v[j]) + bias[j];
-    if (RELU) a = fmaxf(a, 0.f);
     if (j < nvalid) {
+      float a = __uint_as_float(v[j]) + bias[j];
+      if (res != nullptr) a += load_as_float(res + int64_t(j) * stride);
+      if (RELU) a = fmaxf(a, 0.f);
       if constexpr (std::is_same<T, __half>::value) dst[int64_t(j) * stride] = __float2half_rn(a);
       else dst[int64_t(j) * stride] = __float2bfloat16_rn(a);
     }
   }
 }
 
+// Eight consecutive channels of one accumulator row: + bias (+ residual) -> ReLU -> one rounding, packed as 16 bytes.
+template <typename T, bool RELU, bool RES>
+__device__ __forceinline__ uint4 finish8(const uint32_t (&v)[32], int q, const float* __restrict__ bias, uint4 r) {
+  const float4* b4 = reinterpret_cast<const float4*>(bias);
+  const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float4 b = b4[q * 2 + h];
+    const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      float a0 = __uint_as_float(v[q * 8 + h * 4 + t * 2]) + bb[t * 2];
+      float a1 = __uint_as_float(v[q * 8 + h * 4 + t * 2 + 1]) + bb[t * 2 + 1];
+      if (RES) {
+        const uint32_t w = rw[h * 2 + t];
+        if constexpr (std::is_same<T, __half>::value) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+          a0 += f.x; a1 += f.y;
+        } else {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+          a0 += f.x; a1 += f.y;
+        }
+      }
+      if (RELU) { a0 = fmaxf(a0, 0.f); a1 = fmaxf(a1, 0.f); }
+      if constexpr (std::is_same<T, __half>::value) {
+        const __half2 o = __floats2half2_rn(a0, a1);
+        ow[h * 2 + t] = *reinterpret_cast<const uint32_t*>(&o);
+      } else {
+        const __nv_bfloat162 o = __floats2bfloat162_rn(a0, a1);
+        ow[h * 2 + t] = *reinterpret_cast<const uint32_t*>(&o);
+      }
+    }
+  }
+  return make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
+// Channel-contiguous output: the 32 channels of a chunk are 64 contiguous, 16-byte aligned bytes of one pixel.
+// Four 16-byte stores per lane (and four 16-byte residual loads) instead of 32 two-byte ones.
+template <typename T, bool RELU, bool RES>
+__device__ __forceinline__ void store_chunk_contiguous(const uint32_t (&v)[32], const float* __restrict__ bias, T* dst, const T* res) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4 r = make_uint4(0, 0, 0, 0);
+    if (RES) r = reinterpret_cast<const uint4*>(res)[q];
+    reinterpret_cast<uint4*>(dst)[q] = finish8<T, RELU, RES>(v, q, bias, r);
+  }
+}
+
+// The same chunk into a staging box for a TMA store: 32 rows (lanes) of 64 bytes in the 64-byte-swizzled layout the
+// tensor map describes (16-byte cell q of row r sits at cell q ^ ((r >> 1) & 3)); bank-conflict free.  With RES the
+// box already holds the residual values (a TMA load put them there) and is overwritten in place.
+template <typename T, bool RELU, bool RES>
+__device__ __forceinline__ void chunk_to_staging(const uint32_t (&v)[32], const float* __restrict__ bias, uint8_t* box, int lane) {
+  uint8_t* row = box + lane * 64;
+  const int sw = (lane >> 1) & 3;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4* cell = reinterpret_cast<uint4*>(row + ((q ^ sw) << 4));
+    uint4 r = make_uint4(0, 0, 0, 0);
+    if (RES) r = *cell;
+    *cell = finish8<T, RELU, RES>(v, q, bias, r);
+  }
+}
+
 template <typename T>
-__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const float* bias, T* dst, int64_t stride, int nvalid, int relu) {
-  if (nvalid == 32) {
+__device__ __forceinline__ void chunk_to_staging(const uint32_t (&v)[32], const float* bias, uint8_t* box, int lane, int relu, bool res) {
+  if (res) {
+    if (relu) chunk_to_staging<T, true, true>(v, bias, box, lane);
+    else chunk_to_staging<T, false, true>(v, bias, box, lane);
+  } else {
+    if (relu) chunk_to_staging<T, true, false>(v, bias, box, lane);
+    else chunk_to_staging<T, false, false>(v, bias, box, lane);
+  }
+}
+
+// dst / res point at the first element of the chunk for this row; consecutive channels are `stride` elements apart
+// (P*Q for NCHW, 1 for channel-contiguous output).
+template <typename T>
+__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const float* bias, T* dst, const T* res, int64_t stride,
+                                            int nvalid, int relu) {
+  if (nvalid == 32 && stride == 1 && ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(res)) & 15u) == 0) {
+    if (res != nullptr) {
+      if (relu) store_chunk_contiguous<T, true, true>(v, bias, dst, res);
+      else store_chunk_contiguous<T, false, true>(v, bias, dst, res);
+    } else {
+      if (relu) store_chunk_contiguous<T, true, false>(v, bias, dst, res);
+      else store_chunk_contiguous<T, false, false>(v, bias, dst, res);
+    }
+  } else if (nvalid == 32 && res == nullptr) {
     if (relu) store_chunk_full<T, true>(v, bias, dst, stride);
     else store_chunk_full<T, false>(v, bias, dst, stride);
   } else {
-    if (relu) store_chunk_tail<T, true>(v, bias, dst, stride, nvalid);
-    else store_chunk_tail<T, false>(v, bias, dst, stride, nvalid);
+    if (relu) store_chunk_tail<T, true>(v, bias, dst, res, stride, nvalid);
+    else store_chunk_tail<T, false>(v, bias, dst, res, stride, nvalid);
   }
 }
 
@@ -86,7 +181,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const float
 template <int BN, int BK, int MH>
 __global__ void __launch_bounds__(kTcThreads, 2)  // at most 80 registers: two CTAs of 12 warps fit the register file
 conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_wgt,
-               const ConvTcParams p) {
+               const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res, const ConvTcParams p) {
   constexpr int ROW_BYTES = BK * 2;
   constexpr uint32_t A_HALF_BYTES = kTileM * ROW_BYTES;
   constexpr uint32_t A_BYTES = MH * A_HALF_BYTES;
@@ -105,8 +200,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;     // [2] MMA -> epilogue: accumulator complete
   uint64_t* acc_empty = acc_full + 2;              // [2] epilogue -> MMA: accumulator drained
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  constexpr int kEpiBufs = BN >= 64 ? BN / 64 : 1;  // 32-column chunks one epilogue warp owns per 128-pixel half
+  uint64_t* res_bar = acc_empty + 2;               // [8 epilogue warps][kEpiBufs] residual tile landed (TMA epilogue only)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + 8 * kEpiBufs);
   uint8_t* stage_base = smem + kCtrlBytes;
+  // TMA epilogue staging: per epilogue warp kEpiBufs boxes of 32 pixels x 32 channels (2 KiB, 64-byte swizzle)
+  uint8_t* epi_base = stage_base + size_t(p.stages) * STAGE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
@@ -117,6 +216,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tm_act);
     ptx::prefetch_tensormap(&tm_wgt);
+    if (p.out_tma) ptx::prefetch_tensormap(&tm_out);
+    if (p.res_tma) ptx::prefetch_tensormap(&tm_res);
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(&full_bar[s], 1);
       ptx::mbar_init(&empty_bar[s], 1);
@@ -125,6 +226,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       ptx::mbar_init(&acc_full[b], 1);
       ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
+    for (int b = 0; b < 8 * kEpiBufs; ++b) ptx::mbar_init(&res_bar[b], 1);
     ptx::fence_mbar_init();
   }
   if (warp == kProducerWarps) {
@@ -309,6 +411,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     const int quad = warp & 3;
     const int par = (warp - kProducerWarps - 1) >> 2;  // 0 or 1: which chunks this warp owns
     const int et = threadIdx.x - 32 * (kProducerWarps + 1);  // 0..255 among the epilogue threads
+    const int we = warp - kProducerWarps - 1;                // 0..7 among the epilogue warps
+    uint32_t res_phase = 0;                                  // bit k: parity of this warp's residual barrier k (TMA epilogue)
     // GEMM row -> (image, pixel within the image, row holds an output pixel at all)
     auto decode_row = [&](int m, bool& m_ok, int& img, int& pix) {
       m_ok = m < p.m_total;
@@ -356,6 +460,24 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");  // epilogue warps only
 
+      // TMA epilogue (channel-contiguous output): this warp's chunk c of half h is staged in its own 2 KiB box and
+      // leaves as one TMA store; with a residual, TMA first loads the residual box into the same place, issued here
+      // (before the accumulator is even complete) so that the load overlaps the main loop.
+      auto stage_box = [&](int k) { return epi_base + size_t(we * kEpiBufs + k) * 2048; };
+      auto prefetch_residual = [&](int h) {
+        if (lane == 0) ptx::bulk_wait_group_read0();  // earlier stores of this warp have left the boxes
+        __syncwarp();
+        if (p.res_tma && lane == 0) {
+          for (int k = 0; k < kEpiBufs; ++k) {
+            const int chunk = par + 2 * k;
+            if (chunk >= BN / 32 || n0 + chunk * 32 >= p.out_channels) break;
+            ptx::mbar_arrive_expect_tx(&res_bar[we * kEpiBufs + k], 2048);
+            ptx::tma_load_2d(stage_box(k), &tm_res, &res_bar[we * kEpiBufs + k], n0 + chunk * 32, m0 + h * kTileM + quad * 32);
+          }
+        }
+      };
+      if (p.out_tma) prefetch_residual(0);
+
       const bool ok = ptx::mbar_wait(&acc_full[buf], acc_phase, p.status, kStatusEpilogueTimeout);
       __syncwarp();
       ptx::tc_fence_after_sync();
@@ -398,7 +520,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         bool m_ok;
         int img, pix;
         decode_row(m, m_ok, img, pix);
-        const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
+        // element offset of (this row, channel n0) and the distance between consecutive channels
+        const int64_t cstride = p.out_nhwc ? 1 : p.pq;
+        const int64_t base = p.out_nhwc ? (int64_t(img) * p.pq + pix) * p.out_channels + n0
+                                        : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
         for (int chunk = par; chunk < BN / 32; chunk += 2) {
           if (n0 + chunk * 32 >= p.out_channels) break;
           if (chunk / cpr != rank) continue;
@@ -425,9 +550,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           }
           if (m_ok) {
             const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
-            const int64_t off = base + int64_t(chunk * 32) * p.pq;
-            if (p.is_bf16) store_chunk<__nv_bfloat16>(v, bias_t + chunk * 32, static_cast<__nv_bfloat16*>(p.y) + off, p.pq, nvalid, p.relu);
-            else store_chunk<__half>(v, bias_t + chunk * 32, static_cast<__half*>(p.y) + off, p.pq, nvalid, p.relu);
+            const int64_t off = base + int64_t(chunk * 32) * cstride;
+            if (p.is_bf16)
+              store_chunk<__nv_bfloat16>(v, bias_t + chunk * 32, static_cast<__nv_bfloat16*>(p.y) + off,
+                                         p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + off : nullptr, cstride, nvalid, p.relu);
+            else
+              store_chunk<__half>(v, bias_t + chunk * 32, static_cast<__half*>(p.y) + off,
+                                  p.residual ? static_cast<const __half*>(p.residual) + off : nullptr, cstride, nvalid, p.relu);
           }
         }
         break;  // one tile per CTA in this mode
@@ -438,25 +567,56 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         bool m_ok;
         int img, pix;
         decode_row(m, m_ok, img, pix);
-        const int64_t base = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
+        const int64_t cstride = p.out_nhwc ? 1 : p.pq;
+        const int64_t base = p.out_nhwc ? (int64_t(img) * p.pq + pix) * p.out_channels + n0
+                                        : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
+        if (p.out_tma && h > 0) prefetch_residual(h);
 #pragma unroll 1
         for (int chunk = par; chunk < BN / 32; chunk += 2) {
           if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform
           uint32_t v[32];
           ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(h * BN + chunk * 32), v);
           ptx::tmem_ld_wait();
+          if (p.out_tma) {
+            const int k = chunk >> 1;
+            uint8_t* box = stage_box(k);
+            bool landed = true;
+            if (p.res_tma) {
+              landed = ptx::mbar_wait(&res_bar[we * kEpiBufs + k], (res_phase >> k) & 1u, p.status, kStatusEpilogueTimeout);
+              res_phase ^= 1u << k;  // barrier k has been used once more (a tile at the channel edge skips some)
+            }
+            if (__all_sync(0xffffffffu, landed)) {
+              if (p.is_bf16) chunk_to_staging<__nv_bfloat16>(v, bias_t + chunk * 32, box, lane, p.relu, p.res_tma != 0);
+              else chunk_to_staging<__half>(v, bias_t + chunk * 32, box, lane, p.relu, p.res_tma != 0);
+              ptx::fence_proxy_async_smem();  // generic-proxy writes above -> visible to the TMA store below
+              __syncwarp();
+              if (lane == 0) {
+                // rows beyond the last pixel and channels beyond O are clipped by the tensor map
+                ptx::tma_store_2d(&tm_out, box, n0 + chunk * 32, m0 + h * kTileM + quad * 32);
+                ptx::bulk_commit_group();
+              }
+            }
+            continue;
+          }
           if (m_ok) {
             const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
-            const int64_t off = base + int64_t(chunk * 32) * p.pq;
-            if (part) {
+            const int64_t off = base + int64_t(chunk * 32) * cstride;
+            if (part) {  // FP32 partials in the output's own element order
               float* dst = part + off;
+              if (cstride == 1 && nvalid == 32 && (off & 3) == 0) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < nvalid) dst[int64_t(j) * p.pq] = __uint_as_float(v[j]);
+                for (int g = 0; g < 8; ++g) reinterpret_cast<uint4*>(dst)[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < nvalid) dst[int64_t(j) * cstride] = __uint_as_float(v[j]);
+              }
             } else if (p.is_bf16) {
-              store_chunk<__nv_bfloat16>(v, bias_t + chunk * 32, static_cast<__nv_bfloat16*>(p.y) + off, p.pq, nvalid, p.relu);
+              store_chunk<__nv_bfloat16>(v, bias_t + chunk * 32, static_cast<__nv_bfloat16*>(p.y) + off,
+                                         p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + off : nullptr, cstride, nvalid, p.relu);
             } else {
-              store_chunk<__half>(v, bias_t + chunk * 32, static_cast<__half*>(p.y) + off, p.pq, nvalid, p.relu);
+              store_chunk<__half>(v, bias_t + chunk * 32, static_cast<__half*>(p.y) + off,
+                                  p.residual ? static_cast<const __half*>(p.residual) + off : nullptr, cstride, nvalid, p.relu);
             }
           }
         }
@@ -468,6 +628,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     }
   }
 
+  if (p.out_tma && warp > kProducerWarps && lane == 0) ptx::bulk_wait_group0();  // this warp's TMA stores are complete
   join_setup();  // no-op for every warp that had a tile (all of them: the grid never exceeds the tile count)
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -483,10 +644,10 @@ cudaError_t prepare_one(size_t smem_bytes) {
 }
 
 template <int BN, int BK, int MH>
-cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tw, const ConvTcParams& p, dim3 grid, size_t smem,
-                       cudaStream_t st) {
+cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const CUtensorMap& tr, const ConvTcParams& p,
+                       dim3 grid, size_t smem, cudaStream_t st) {
   cudaError_t e = launch_pdl_cluster(conv_tc_kernel<BN, BK, MH>, grid, dim3(kTcThreads), smem, st,
-                                     unsigned(p.cluster_split > 1 ? p.cluster_split : 1), ta, tw, p);
+                                     unsigned(p.cluster_split > 1 ? p.cluster_split : 1), ta, tw, to, tr, p);
   if (e != cudaSuccess) return e;
   return cudaGetLastError();
 }
@@ -536,20 +697,26 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t total, int64_t slice_stride, int out_channels,
                      int pq, FastDiv fd_pq, FastDiv fd_oc, const void* __restrict__ bias, int bias_fp32, int relu,
-                     T* __restrict__ y) {
+                     const T* residual, int out_nhwc, T* y) {
   ptx::grid_dep_wait();  // launched with programmatic stream serialization right behind the convolution kernel
   const int64_t step = int64_t(gridDim.x) * blockDim.x;
   const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  // bias of the channel of element i plus, when given, the residual element (same layout as the output)
   auto bias_of = [&](int64_t i) -> float {
-    if (bias == nullptr) return 0.f;
+    float extra = residual != nullptr ? to_f32(residual[i]) : 0.f;
+    if (bias == nullptr) return extra;
     int oc;
-    if (total < (int64_t(1) << 31)) {  // the usual case: two multiply-high divisions
-      const int plane = fd_pq.div(int(i));
-      oc = plane - fd_oc.div(plane) * out_channels;
+    if (total < (int64_t(1) << 31)) {  // the usual case: multiply-high divisions
+      if (out_nhwc) {
+        oc = int(i) - fd_oc.div(int(i)) * out_channels;
+      } else {
+        const int plane = fd_pq.div(int(i));
+        oc = plane - fd_oc.div(plane) * out_channels;
+      }
     } else {
-      oc = int((i / pq) % out_channels);
+      oc = out_nhwc ? int(i % out_channels) : int((i / pq) % out_channels);
     }
-    return bias_fp32 ? static_cast<const float*>(bias)[oc] : to_f32(static_cast<const T*>(bias)[oc]);
+    return extra + (bias_fp32 ? static_cast<const float*>(bias)[oc] : to_f32(static_cast<const T*>(bias)[oc]));
   };
   if (VEC) {
     const int64_t nvec = total >> 2;
@@ -588,8 +755,10 @@ splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t tota
 
 }  // namespace
 
-size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages) {
-  return 1024 + kCtrlBytes + size_t(stages) * (size_t(tile_m) + tile_n) * tile_k * 2;
+size_t conv_tc_epilogue_staging_bytes(int tile_n) { return size_t(8) * (tile_n >= 64 ? tile_n / 64 : 1) * 2048; }
+
+size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, bool tma_epilogue) {
+  return 1024 + kCtrlBytes + size_t(stages) * (size_t(tile_m) + tile_n) * tile_k * 2 + (tma_epilogue ? conv_tc_epilogue_staging_bytes(tile_n) : 0);
 }
 
 cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, size_t smem_bytes) {
@@ -597,12 +766,14 @@ cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, size_t smem_byte
 }
 
 cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
-                           const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream) {
-  GIEB_TC_DISPATCH(launch_one, tm_act, tm_wgt, p, grid, smem_bytes, stream)
+                           const CUtensorMap& tm_out, const CUtensorMap& tm_res, const ConvTcParams& p, dim3 grid, size_t smem_bytes,
+                           cudaStream_t stream) {
+  GIEB_TC_DISPATCH(launch_one, tm_act, tm_wgt, tm_out, tm_res, p, grid, smem_bytes, stream)
 }
 
 cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total, int out_channels, int pq, const void* bias,
-                                 int bias_fp32, int relu, int is_bf16, void* y, cudaStream_t stream) {
+                                 int bias_fp32, int relu, int is_bf16, const void* residual, int out_nhwc, void* y,
+                                 cudaStream_t stream) {
   const int64_t slice_stride = (total + 3) & ~int64_t(3);
   const bool vec = (reinterpret_cast<uintptr_t>(y) & 7u) == 0;
   const int64_t work = vec ? (total + 3) / 4 : total;
@@ -613,12 +784,14 @@ cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total
   cudaError_t e;
   if (is_bf16) {
     auto* yy = static_cast<__nv_bfloat16*>(y);
-    if (vec) e = launch_pdl(splitk_reduce_kernel<__nv_bfloat16, true>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, yy);
-    else e = launch_pdl(splitk_reduce_kernel<__nv_bfloat16, false>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, yy);
+    auto* rr = static_cast<const __nv_bfloat16*>(residual);
+    if (vec) e = launch_pdl(splitk_reduce_kernel<__nv_bfloat16, true>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, rr, out_nhwc, yy);
+    else e = launch_pdl(splitk_reduce_kernel<__nv_bfloat16, false>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, rr, out_nhwc, yy);
   } else {
     auto* yy = static_cast<__half*>(y);
-    if (vec) e = launch_pdl(splitk_reduce_kernel<__half, true>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, yy);
-    else e = launch_pdl(splitk_reduce_kernel<__half, false>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, yy);
+    auto* rr = static_cast<const __half*>(residual);
+    if (vec) e = launch_pdl(splitk_reduce_kernel<__half, true>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, rr, out_nhwc, yy);
+    else e = launch_pdl(splitk_reduce_kernel<__half, false>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, rr, out_nhwc, yy);
   }
   return e != cudaSuccess ? e : cudaGetLastError();
 }

@@ -85,6 +85,42 @@ maxpool2d_kernel(const T* __restrict__ x, T* __restrict__ y, int planes, int h, 
   }
 }
 
+// Channel-contiguous variant ([B][H][W][C], C % 8 == 0, 16-bit types): one thread per (output pixel, group of 8
+// channels); consecutive threads take consecutive groups, so every window tap is a coalesced 16-byte load.
+template <typename T2>
+__global__ void __launch_bounds__(256)
+maxpool2d_nhwc_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_t total, int c8, int h, int w, int oh, int ow, int k,
+                      int stride, int pad) {
+  const int64_t step = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int g = int(i % c8);
+    int64_t px = i / c8;
+    const int ox = int(px % ow);
+    px /= ow;
+    const int oy = int(px % oh);
+    const int b = int(px / oh);
+    const int iy0 = oy * stride - pad, ix0 = ox * stride - pad;
+    const int r0 = iy0 < 0 ? -iy0 : 0, r1 = min(k, h - iy0);
+    const int s0 = ix0 < 0 ? -ix0 : 0, s1 = min(k, w - ix0);
+    bool first = true;
+    uint4 best = make_uint4(0, 0, 0, 0);
+    for (int r = r0; r < r1; ++r)
+      for (int s = s0; s < s1; ++s) {
+        const uint4 v = x[((int64_t(b) * h + iy0 + r) * w + ix0 + s) * c8 + g];
+        if (first) {
+          best = v;
+          first = false;
+        } else {
+          T2* bp = reinterpret_cast<T2*>(&best);
+          const T2* vp = reinterpret_cast<const T2*>(&v);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) bp[q] = __hmax2(bp[q], vp[q]);
+        }
+      }
+    y[i] = best;
+  }
+}
+
 unsigned grid_for(int64_t work) {
   int64_t b = (work + 255) / 256;
   if (b > 148 * 32) b = 148 * 32;
@@ -136,6 +172,20 @@ cudaError_t maxpool2d_launch(int precision, int batch, int channels, int h, int 
     case 2: maxpool2d_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), planes, h, w, oh, ow, k, stride, pad); break;
     default: return cudaErrorInvalidValue;
   }
+  return cudaGetLastError();
+}
+
+cudaError_t maxpool2d_nhwc_launch(int precision, int batch, int channels, int h, int w, int k, int stride, int pad, const void* x,
+                                  void* y, cudaStream_t st) {
+  const int oh = (h + 2 * pad - k) / stride + 1, ow = (w + 2 * pad - k) / stride + 1;
+  if (channels % 8 != 0 || (precision != 1 && precision != 2)) return cudaErrorInvalidValue;
+  const int c8 = channels / 8;
+  const int64_t total = int64_t(batch) * oh * ow * c8;
+  const unsigned g = grid_for(total);
+  if (precision == 1)
+    maxpool2d_nhwc_kernel<__half2><<<g, 256, 0, st>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y), total, c8, h, w, oh, ow, k, stride, pad);
+  else
+    maxpool2d_nhwc_kernel<__nv_bfloat162><<<g, 256, 0, st>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y), total, c8, h, w, oh, ow, k, stride, pad);
   return cudaGetLastError();
 }
 

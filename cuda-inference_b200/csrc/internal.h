@@ -124,20 +124,29 @@ struct ConvTcParams {
   FastDiv fd_cluster;
   FastDiv fd_tiles_mn, fd_tiles_n, fd_pq, fd_out_w, fd_kb_per_tap, fd_kernel_w, fd_boxes;  // reciprocals of the fields above
   const void* bias;
-  void* y;            // NCHW output in the storage type (split_k == 1)
-  float* partial;     // [splits][B*O*P*Q] FP32 partial sums in NCHW order (split_k > 1), else null
+  const void* residual;  // optional tensor of the output's shape, layout and type, added before the activation
+  int out_nhwc;          // 0: y (and residual, partials) are NCHW; 1: channel-contiguous [B][P][Q][O]
+  int out_tma, res_tma;  // channel-contiguous output leaves through TMA stores / the residual arrives through TMA loads
+  void* y;            // output in the storage type (split_k == 1 or cluster reduction)
+  float* partial;     // [splits][B*O*P*Q] FP32 partial sums in the output's element order (workspace reduction), else null
   uint32_t* status;
 };
 
 // tile_m is 128 or 256 output pixels per CTA (one or two TMEM accumulators sharing each weight tile).
-size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages);
+// tma_epilogue: add the staging boxes of the TMA-store epilogue (channel-contiguous output).
+size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, bool tma_epilogue);
+size_t conv_tc_epilogue_staging_bytes(int tile_n);
 cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, size_t smem_bytes);  // opt in to large dynamic shared memory
+// tm_out / tm_res: the output and the residual as 2-D tensors {channels, pixels} with a 32 x 32 box and 64-byte swizzle;
+// read only when p.out_tma / p.res_tma are set.
 cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
-                           const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream);
+                           const CUtensorMap& tm_out, const CUtensorMap& tm_res, const ConvTcParams& p, dim3 grid, size_t smem_bytes,
+                           cudaStream_t stream);
 
-// Sum of split-K partials + bias + ReLU + one rounding; `total` = B*O*P*Q elements in NCHW order.
+// Sum of split-K partials + bias (+ residual) + ReLU + one rounding; `total` = B*O*P*Q elements in the output's order.
 cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total, int out_channels, int pq,
-                                 const void* bias, int bias_fp32, int relu, int is_bf16, void* y, cudaStream_t stream);
+                                 const void* bias, int bias_fp32, int relu, int is_bf16, const void* residual, int out_nhwc,
+                                 void* y, cudaStream_t stream);
 
 // 16-bit [B][C][HW] -> [B][HW][Cp] (zero-filled channel padding).
 cudaError_t repack_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream);
@@ -159,6 +168,9 @@ cudaError_t bias_act_launch(int precision, int64_t total, int channels, int hw, 
                             cudaStream_t stream);
 cudaError_t maxpool2d_launch(int precision, int batch, int channels, int h, int w, int k, int stride, int pad, const void* x,
                              void* y, cudaStream_t stream);
+// [B][H][W][C] tensors, C % 8 == 0, 16-bit types.
+cudaError_t maxpool2d_nhwc_launch(int precision, int batch, int channels, int h, int w, int k, int stride, int pad, const void* x,
+                                  void* y, cudaStream_t stream);
 cudaError_t add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, cudaStream_t stream);
 
 }  // namespace gieb

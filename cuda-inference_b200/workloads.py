@@ -74,8 +74,9 @@ class ChainOp:
     dst: int
     shape: ConvShape | None = None
     relu: bool = True
-    other: int = -1          # second operand of 'add'
+    other: int = -1          # second operand of 'add'; residual slot of a fused 'conv' (-1: none)
     pool: tuple = ()         # (channels, h, w, kernel, stride, pad) of 'maxpool'
+    layer: int = -1          # 'conv': index in the order resnet50_chain emits convolutions (names its weights and seed)
 
 
 def resnet50_chain(batch: int, precision: int = FP16, image: int = 224):
@@ -122,7 +123,27 @@ def resnet50_chain(batch: int, precision: int = FP16, image: int = 224):
             so = new_slot(c_out, h2, h2)
             ops.append(ChainOp("add", sc, so, relu=True, other=short))
             cur, c_in, h = so, c_out, h2
+    n = 0
+    for i, op in enumerate(ops):
+        if op.kind == "conv":
+            ops[i] = ChainOp(op.kind, op.src, op.dst, op.shape, op.relu, op.other, op.pool, n)
+            n += 1
     return ops, slots
+
+
+def fuse_residuals(ops):
+    """The same chain with every 'add' folded into the convolution that produces its first operand: that convolution
+    moves behind whatever computes the other operand (the projection shortcut of a stage's first block), takes it as
+    its residual, applies the add's ReLU and writes the add's destination slot."""
+    out = []
+    for op in ops:
+        if op.kind != "add":
+            out.append(op)
+            continue
+        idx = next(i for i in range(len(out) - 1, -1, -1) if out[i].kind == "conv" and out[i].dst == op.src)
+        conv = out.pop(idx)
+        out.append(ChainOp("conv", conv.src, op.dst, conv.shape, op.relu, other=op.other, layer=conv.layer))
+    return out
 
 
 def chain_flops(ops) -> int:

@@ -50,7 +50,14 @@ typedef enum gieb_precision { GIEB_FP32 = 0, GIEB_FP16 = 1, GIEB_BF16 = 2, GIEB_
 /* Optional behaviour beyond the reference API (all off by default = exact drop-in behaviour). */
 enum {
   GIEB_FLAG_BIAS_FP32 = 1u << 0,        /* bias is float[O] even for 16-bit storage                              */
-  GIEB_FLAG_WEIGHTS_PREPACKED = 1u << 1 /* `w` already holds gieb_prepack_weights output (static weights)       */
+  GIEB_FLAG_WEIGHTS_PREPACKED = 1u << 1, /* `w` already holds gieb_prepack_weights output (static weights)      */
+  /* Channel-contiguous tensors and a fused residual for chains of convolutions (16-bit tensor path only).  The
+   * reference keeps every tensor NCHW (include/gpu_inference/conv2d.h:66-69) and has no residual operand; its
+   * epilogue hook is src/kernels/fused_epilogue.cuh:11-16.  A chain that stays channel-contiguous needs no layout
+   * repack between layers, and the residual add + ReLU of a bottleneck block disappears into the epilogue. */
+  GIEB_FLAG_INPUT_NHWC = 1u << 2,   /* x is [B][H][W][C], 16-byte aligned, C a multiple of 16: read in place, no repack */
+  GIEB_FLAG_OUTPUT_NHWC = 1u << 3,  /* y (and the residual) are [B][P][Q][O]                                             */
+  GIEB_FLAG_RESIDUAL = 1u << 4      /* y = act(conv + bias + residual); launch with gieb_conv_launch_fused               */
 };
 
 /* Conv2DParams + ConvProblem (include/gpu_inference/conv2d.h:47-85) as fixed-width fields. */
@@ -131,6 +138,13 @@ GIEB_API int gieb_conv_plan_info(const gieb_conv_plan* plan, gieb_conv_info* out
 GIEB_API int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y,
                               void* workspace, size_t workspace_bytes, void* stream);
 
+/* gieb_conv_launch with one more operand (no reference counterpart): `residual` has the shape, layout and storage
+ * type of y and is added in FP32 before the activation and the single rounding.  Required (non-null) for plans
+ * created with GIEB_FLAG_RESIDUAL, refused for others.  `residual` may be the same buffer as y (each element is read
+ * by the thread that writes it) but must not overlap x or w. */
+GIEB_API int gieb_conv_launch_fused(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias,
+                                    const void* residual, void* y, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Measurement helper standing in for the stage_events hook of ExecutionPlan::execute
  * (include/gpu_inference/execution_plan.h:25-31, kernel_registry.h:38-40) and time_stream_work
  * (src/runtime/timing.cpp:21-83): runs `iters` forward calls on `stream` with CUDA events between the stages,
@@ -197,6 +211,9 @@ GIEB_API int gieb_bias_act_launch(int precision, int batch, int channels, int hw
  * benchmarks/graph_bench.cpp:84-91).  16-bit NCHW tensors. */
 GIEB_API int gieb_maxpool2d_launch(int precision, int batch, int channels, int h, int w, int kernel, int stride, int pad,
                                    const void* x, void* y, void* stream);
+/* The same pooling on channel-contiguous [B][H][W][C] tensors (fp16 / bf16, C % 8 == 0, 16-byte aligned). */
+GIEB_API int gieb_maxpool2d_nhwc_launch(int precision, int batch, int channels, int h, int w, int kernel, int stride, int pad,
+                                        const void* x, void* y, void* stream);
 GIEB_API int gieb_add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, void* stream);
 
 #ifdef __cplusplus

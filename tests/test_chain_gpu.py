@@ -25,13 +25,14 @@ def _host_weights(orc, oracle, ops, precision, seed):
     return out
 
 
-def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed):
+def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed, layout="nchw"):
     import torch
     from cuda_inference_b200.chain import ConvChain
     from cuda_inference_b200 import workloads as wl
     ops, _ = wl.resnet50_chain(batch, precision, image)
     hw = _host_weights(orc, oracle, ops, precision, seed)
-    chain = ConvChain(batch, precision, image, weights=[(oracle.to_bits16(precision, w), oracle.to_bits16(precision, b)) for w, b in hw])
+    chain = ConvChain(batch, precision, image, weights=[(oracle.to_bits16(precision, w), oracle.to_bits16(precision, b)) for w, b in hw],
+                      layout=layout)
     x = oracle.quantize(precision, oracle.rng(seed + 1000).draw(orc.DIST_NORMAL, batch * 3 * image * image))
     chain.input.view(torch.int16).copy_(torch.from_numpy(oracle.to_bits16(precision, x).view(np.int16)).cuda())
     for t in list(chain.slots.values())[1:]:
@@ -45,7 +46,10 @@ def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed):
     def slot(i):
         c, h, w = chain.slot_shapes[i]
         raw = chain.slots[i].view(torch.int16).cpu().numpy().view(np.uint16)
-        return oracle.from_bits16(precision, raw).reshape(batch, c, h, w)
+        vals = oracle.from_bits16(precision, raw)
+        if layout == "nhwc" and i != 0:  # every tensor but the input image is channel-contiguous
+            return np.ascontiguousarray(vals.reshape(batch, h, w, c).transpose(0, 3, 1, 2))
+        return vals.reshape(batch, c, h, w)
 
     ci = 0
     worst = 0.0
@@ -54,11 +58,19 @@ def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed):
         assert np.all(np.isfinite(got)), f"non-finite output at {op.kind} -> slot {op.dst}"
         if op.kind == "conv":
             s = op.shape
+            fused = layout == "nhwc" and op.other >= 0
             p = orc.Problem.P(s.batch, s.in_channels, s.in_h, s.in_w, s.out_channels, s.kernel, s.kernel, s.stride, s.stride, s.pad, s.pad,
-                              precision, True, op.relu)
-            w, b = hw[ci]
+                              precision, True, op.relu and not fused)
+            w, b = hw[op.layer]
             ci += 1
             ref, scale = oracle.conv2d(p, slot(op.src), w.reshape(p.w_shape), b)
+            if fused:  # y = act(conv + bias + residual), one rounding
+                res = slot(op.other).astype(np.float64)
+                ref = ref.astype(np.float64) + res
+                if op.relu:
+                    ref = np.maximum(ref, 0.0)
+                ref = ref.astype(np.float32)
+                scale = (scale.astype(np.float64) + np.abs(res)).astype(np.float32)
             m = oracle.compare(p, got, ref, scale)
             assert m.passed(), f"conv {ci} {s}: {m.summary()}"
             worst = max(worst, m.worst_tol_ratio)
@@ -83,6 +95,21 @@ def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed):
 def test_chain_small_images_batch2_fp16(pkg, orc, oracle):
     worst, nodes = _run_chain_case(pkg, orc, oracle, batch=2, image=64, precision=orc.FP16, seed=0)
     assert nodes >= 53 * 2 + 17
+
+
+def test_chain_channel_contiguous_fused_residual_fp16(pkg, orc, oracle):
+    """Channel-contiguous chain: prepacked weights, no repack between layers, residual add + ReLU inside the epilogue
+    of each block's last convolution.  One launch per convolution except the stem (which repacks the NCHW image)."""
+    worst, nodes = _run_chain_case(pkg, orc, oracle, batch=2, image=64, precision=orc.FP16, seed=0, layout="nhwc")
+    assert 53 + 2 <= nodes <= 53 + 2 + 20  # convolutions + stem repack + max-pool (+ workspace reductions of tiny layers)
+
+
+def test_chain_channel_contiguous_bf16(pkg, orc, oracle):
+    _run_chain_case(pkg, orc, oracle, batch=3, image=32, precision=orc.BF16, seed=5, layout="nhwc")
+
+
+def test_chain_channel_contiguous_full_size_image(pkg, orc, oracle):
+    _run_chain_case(pkg, orc, oracle, batch=1, image=224, precision=orc.FP16, seed=3, layout="nhwc")
 
 
 def test_chain_full_size_image_batch1_fp16(pkg, orc, oracle):
