@@ -75,6 +75,8 @@ def lib() -> C.CDLL:
         L.gieb_conv_plan_destroy.restype = None
         L.gieb_conv_plan_info.argtypes = [vp, C.POINTER(ConvInfo)]
         L.gieb_conv_launch.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp]
+        L.gieb_conv_plan_prepacked_weight_bytes.argtypes = [vp, C.POINTER(C.c_uint64)]
+        L.gieb_conv_plan_prepack_weights.argtypes = [vp, vp, vp, vp]
         L.gieb_conv_launch_fused.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.gieb_conv_time_stages.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp, i32, C.POINTER(C.c_float)]
         L.gieb_conv_forward_static.argtypes = [C.POINTER(ConvDesc), C.POINTER(ConvCfg), vp, vp, vp, vp, vp]
@@ -173,6 +175,16 @@ class ConvPlan:
     def launch(self, x: int, w: int, bias: int | None, y: int, workspace: int | None, workspace_bytes: int, stream: int = 0) -> None:
         """execute_unchecked: raw device pointers, asynchronous on `stream`."""
         check(lib().gieb_conv_launch(self._h, x, w, bias, y, workspace, workspace_bytes, stream))
+
+    @property
+    def prepacked_weight_bytes(self) -> int:
+        v = C.c_uint64()
+        check(lib().gieb_conv_plan_prepacked_weight_bytes(self._h, C.byref(v)))
+        return int(v.value)
+
+    def prepack_weights(self, w: int, dst: int, stream: int = 0) -> None:
+        """OIHW weights -> the layout this plan's kernel reads (for problems with FLAG_WEIGHTS_PREPACKED)."""
+        check(lib().gieb_conv_plan_prepack_weights(self._h, w, dst, stream))
 
     def launch_fused(self, x: int, w: int, bias: int | None, residual: int, y: int, workspace: int | None, workspace_bytes: int,
                      stream: int = 0) -> None:

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import math
 
-from . import (ConvPlan, ConvProblem, add_relu, maxpool2d, maxpool2d_nhwc, prepack_weights, FLAG_INPUT_NHWC, FLAG_OUTPUT_NHWC,
+from . import (ConvPlan, ConvProblem, add_relu, maxpool2d, maxpool2d_nhwc, FLAG_INPUT_NHWC, FLAG_OUTPUT_NHWC,
                FLAG_RESIDUAL, FLAG_WEIGHTS_PREPACKED)
 from .workloads import FP16, BF16, chain_flops, fuse_residuals, resnet50_chain
 
@@ -86,11 +86,9 @@ class ConvChain:
                 bound = layer_weight_bound(s, base_relu[li])
                 w = ((torch.rand(s.w_elems, device=self.device, generator=g) * 2 - 1) * bound).to(self.dtype)
                 b = ((torch.rand(s.out_channels, device=self.device, generator=g) * 2 - 1) * 0.1).to(self.dtype)
-            if nhwc:  # static weights: [O][C][RS] -> [O][RS][Cp] once, here
-                cp = plan.info.padded_channels
-                wp = torch.empty(s.out_channels * s.kernel * s.kernel * cp, dtype=self.dtype, device=self.device)
-                prepack_weights(w.data_ptr(), wp.data_ptr(), s.out_channels, s.in_channels, s.kernel * s.kernel, cp,
-                                torch.cuda.current_stream().cuda_stream)
+            if nhwc:  # static weights: converted once, here, to the layout the plan's kernel reads
+                wp = torch.empty(plan.prepacked_weight_bytes // 2, dtype=self.dtype, device=self.device)
+                plan.prepack_weights(w.data_ptr(), wp.data_ptr(), torch.cuda.current_stream().cuda_stream)
                 w = wp
             self.convs.append((op, plan, w, b))
             ws_bytes = max(ws_bytes, plan.workspace_bytes)

@@ -98,10 +98,14 @@ int validate(const gieb_conv_desc* d) {
 // cost, plus (for split-K) writing and re-reading FP32 partials and the extra launch.
 struct Resolved {
   // 1 tensor path with im2col-mode TMA; 4 tensor path with tiled TMA over the NHWC copy (1x1, stride 1, pad 0);
-  // 2 tensor path reading the caller's NCHW activations directly (1x1, stride 1, pad 0, H*W % 8 == 0); 3 FP32 SIMT
+  // 2 tensor path reading the caller's NCHW activations directly (1x1, stride 1, pad 0, H*W % 8 == 0); 3 FP32 SIMT;
+  // 5 tensor path over row-gathered activations (few input channels: S*C <= 64)
   int variant;
   int boxes_per_image;  // variant 2: ceil(H*W / 64)
   int tile_m, tile_n, tile_k, stages, split_k;
+  // Width geometry the kernel and its tensor maps see: the problem's own, except on the row-gather route (variant 5),
+  // where the S taps of a filter row have become channels of a tensor of width Q (kernel width 1, stride 1, no padding).
+  int eff_in_w, eff_kernel_w, eff_stride_w, eff_pad_w;
   int tma_epilogue;  // channel-contiguous output staged in shared memory and written by TMA stores
   int reduce;  // 1 workspace partials + reduction launch, 2 cluster (distributed shared memory); 0 when split_k == 1
   int c_padded, kb_per_tap, total_kb, kb_per_split;
@@ -170,9 +174,7 @@ bool cluster_reduce_ok(int tile_m, int tile_n, int tile_k, int stages, int split
 //  * ~4500 cycles from launch to the first MMA, ~500 + 16 per accumulator column for an epilogue, which is hidden
 //    behind the next tile's main loop when the accumulator is double-buffered or a second CTA shares the SM.
 // reduce: 0 none, 1 FP32 partials in the workspace + reduction launch, 2 cluster.
-double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, int tile_n, int tile_k, int split, int reduce) {
-  const int c_padded = round_up(d.in_channels, tile_k);
-  const int total_kb = d.kernel_h * d.kernel_w * (c_padded / tile_k);
+double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, int tile_n, int tile_k, int split, int reduce, int total_kb) {
   const int kb_per_split = ceil_div(total_kb, split);
   const int real_split = ceil_div(total_kb, kb_per_split);
   const int64_t ctas = int64_t(ceil_div(g.pixels, tile_m)) * ceil_div(d.out_channels, tile_n) * real_split;
@@ -237,8 +239,14 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   }
   const bool pointwise = d.kernel_h == 1 && d.kernel_w == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_h == 0 && d.pad_w == 0;
   const bool direct_ok = pointwise && (d.in_h * d.in_w) % 8 == 0;
-  if (c.variant != 0 && c.variant != 1 && c.variant != 2 && c.variant != 4)
-    return no("unknown kernel variant for 16-bit precision (1 = im2col-mode TMA, 2 = direct NCHW 1x1, 4 = tiled TMA for 1x1)");
+  if (c.variant != 0 && c.variant != 1 && c.variant != 2 && c.variant != 4 && c.variant != 5)
+    return no("unknown kernel variant for 16-bit precision (1 = im2col-mode TMA, 2 = direct NCHW 1x1, 4 = tiled TMA for 1x1, 5 = row gather)");
+  // Row gather: the S taps of a filter row become channels (c2 = padded S*C <= 64, one slab or less per filter row).
+  // Worth it when it at least halves the padded reduction length (a 7x7 stem over 3 channels: 7*32 instead of 49*16).
+  const int gather_c2 = round_up(d.kernel_w * d.in_channels, 16);
+  const bool gather_ok = !(d.flags & GIEB_FLAG_INPUT_NHWC) && d.kernel_w > 1 && gather_c2 <= 64;
+  const bool gather_pays = gather_ok && 2 * gather_c2 <= d.kernel_w * round_up(d.in_channels, 16);
+  if (c.variant == 5 && !gather_ok) return no("variant 5 (row gather) needs an NCHW input, a kernel wider than 1 and kernel_w * channels <= 64");
   if (c.variant == 4 && !pointwise) return no("variant 4 (tiled activation loads) needs a 1x1 kernel with stride 1 and no padding");
   if (c.variant == 2 && !direct_ok) return no("variant 2 (direct NCHW loads) needs a 1x1 kernel, stride 1, no padding and H*W % 8 == 0");
   const bool in_nhwc = (d.flags & GIEB_FLAG_INPUT_NHWC) != 0;
@@ -246,7 +254,12 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
     if (d.in_channels % 16 != 0) return no("channel-contiguous input needs a channel count that is a multiple of 16");
     if (c.variant == 2) return no("variant 2 reads NCHW activations; a channel-contiguous input takes variant 1 or 4");
   }
-  r->variant = c.variant ? c.variant : (in_nhwc ? (pointwise ? 4 : 1) : (direct_ok ? 2 : (pointwise ? 4 : 1)));
+  r->variant = c.variant ? c.variant : (in_nhwc ? (pointwise ? 4 : 1) : (direct_ok ? 2 : (pointwise ? 4 : (gather_pays ? 5 : 1))));
+  const bool gather = r->variant == 5;
+  r->eff_in_w = gather ? g.out_w : d.in_w;
+  r->eff_kernel_w = gather ? 1 : d.kernel_w;
+  r->eff_stride_w = gather ? 1 : d.stride_w;
+  r->eff_pad_w = gather ? 0 : d.pad_w;
   r->boxes_per_image = ceil_div(int64_t(d.in_h) * d.in_w, 64);
   // GEMM rows: output pixels, or (variant 2) 64-pixel boxes that never straddle an image
   const int64_t rows = r->variant == 2 ? int64_t(d.batch) * r->boxes_per_image * 64 : g.pixels;
@@ -258,9 +271,15 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   r->tile_k = c.tile_k ? c.tile_k : (in_nhwc ? (d.in_channels % 64 == 0 ? 64 : (d.in_channels % 32 == 0 ? 32 : 16)) : pick_tile_k(d.in_channels));
   if (r->tile_k != 16 && r->tile_k != 32 && r->tile_k != 64) return no("tile_k must be 16, 32 or 64");
   if (in_nhwc && d.in_channels % r->tile_k != 0) return no("tile_k must divide the channel count of a channel-contiguous input (it is read in place)");
-  r->c_padded = round_up(d.in_channels, r->tile_k);
+  if (gather) {
+    if (!c.tile_k) r->tile_k = gather_c2 % 64 == 0 ? 64 : (gather_c2 % 32 == 0 ? 32 : 16);
+    if (gather_c2 % r->tile_k != 0) return no("tile_k must divide the gathered row length (padded kernel_w * channels)");
+    r->c_padded = gather_c2;
+  } else {
+    r->c_padded = round_up(d.in_channels, r->tile_k);
+  }
   r->kb_per_tap = r->c_padded / r->tile_k;
-  r->total_kb = d.kernel_h * d.kernel_w * r->kb_per_tap;
+  r->total_kb = d.kernel_h * r->eff_kernel_w * r->kb_per_tap;
 
   if (c.tile_n) {
     if (c.tile_n != 32 && c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256) return no("tile_n must be 32, 64, 128 or 256");
@@ -294,7 +313,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
             // unasked, clusters are used only when the whole grid is one wave of one CTA per SM
             if (c.reduce == 0 && ctas > kNumSms) continue;
           }
-          const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s, mode) + (r->variant == 2 && tn < d.out_channels && tn < 256 ? 1e6 : 0.0);
+          const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s, mode, r->total_kb) + (r->variant == 2 && tn < d.out_channels && tn < 256 ? 1e6 : 0.0);
           if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; best_mode = mode; }
         }
       }
@@ -326,8 +345,8 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
 
   // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
   // src/kernels/tensor_core_mma.cu:265-278)
-  r->ws_x = in_nhwc ? 0 : align256(size_t(d.batch) * d.in_h * d.in_w * r->c_padded * 2);
-  r->ws_w = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : align256(size_t(d.out_channels) * d.kernel_h * d.kernel_w * r->c_padded * 2);
+  r->ws_x = in_nhwc ? 0 : align256(size_t(d.batch) * d.in_h * r->eff_in_w * r->c_padded * 2);
+  r->ws_w = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : align256(size_t(d.out_channels) * d.kernel_h * r->eff_kernel_w * r->c_padded * 2);
   // how the split-K slices are summed
   if (c.reduce < 0 || c.reduce > 2) return no("reduce must be 0 (auto), 1 (workspace) or 2 (cluster)");
   r->reduce = r->split_k > 1 ? best_mode : 0;
@@ -443,20 +462,20 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (activations) failed with CUresult %d", int(res));
     small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * d.in_w * r.c_padded * 2);
   } else {
-    const cuuint64_t dims[4] = {cuuint64_t(r.c_padded), cuuint64_t(d.in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
-    const cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(d.in_w) * r.c_padded * 2,
-                                   cuuint64_t(d.in_h) * d.in_w * r.c_padded * 2};
-    const int lower[2] = {-d.pad_w, -d.pad_h};
-    const int upper[2] = {d.pad_w - (d.kernel_w - 1), d.pad_h - (d.kernel_h - 1)};
-    const cuuint32_t trav[4] = {1, cuuint32_t(d.stride_w), cuuint32_t(d.stride_h), 1};
+    const cuuint64_t dims[4] = {cuuint64_t(r.c_padded), cuuint64_t(r.eff_in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
+    const cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(r.eff_in_w) * r.c_padded * 2,
+                                   cuuint64_t(d.in_h) * r.eff_in_w * r.c_padded * 2};
+    const int lower[2] = {-r.eff_pad_w, -d.pad_h};
+    const int upper[2] = {r.eff_pad_w - (r.eff_kernel_w - 1), d.pad_h - (d.kernel_h - 1)};
+    const cuuint32_t trav[4] = {1, cuuint32_t(r.eff_stride_w), cuuint32_t(d.stride_h), 1};
     const CUresult res = g_encode_im2col(tm_act, dt, 4, const_cast<void*>(xn), dims, strides, lower, upper, cuuint32_t(r.tile_k),
                                          cuuint32_t(kTileM), trav, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeIm2col failed with CUresult %d", int(res));
-    small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * d.in_w * r.c_padded * 2);
+    small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * r.eff_in_w * r.c_padded * 2);
   }
   {
-    const cuuint64_t kp = cuuint64_t(d.kernel_h) * d.kernel_w * r.c_padded;
+    const cuuint64_t kp = cuuint64_t(d.kernel_h) * r.eff_kernel_w * r.c_padded;
     const cuuint64_t dims[2] = {kp, cuuint64_t(d.out_channels)};
     const cuuint64_t strides[1] = {kp * 2};
     const cuuint32_t box[2] = {cuuint32_t(r.tile_k), cuuint32_t(r.tile_n)};
@@ -527,7 +546,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   float* part = r.reduce == 1 ? reinterpret_cast<float*>(wsb + r.ws_x + r.ws_w) : nullptr;
 
   // A direct-NCHW plan needs a 16-byte aligned x (TMA base address rule); otherwise this call takes the repack route.
-  int mode = r.variant == 1 ? 0 : (r.variant == 4 ? 1 : 2);
+  int mode = (r.variant == 1 || r.variant == 5) ? 0 : (r.variant == 4 ? 1 : 2);
   if (mode == 2 && reinterpret_cast<uintptr_t>(x) % 16 != 0) mode = 1;
   const bool in_nhwc = (d.flags & GIEB_FLAG_INPUT_NHWC) != 0;
   if (in_nhwc) {  // read in place
@@ -541,7 +560,10 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   if (st_maps != GIEB_OK) return st_maps;
 
   if (ev) GIEB_CUDA(cudaEventRecord(ev[0], st));
-  if (mode == 2 || in_nhwc) {
+  if (r.variant == 5) {  // row gather of the activations (and of the weights unless they come gathered)
+    GIEB_CUDA(gather_rows_launch(x, xn, d.batch, d.in_channels, d.in_h, d.in_w, pl->g.out_w, d.kernel_w, d.stride_w, d.pad_w, r.c_padded,
+                                 (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? nullptr : w, const_cast<void*>(wk), d.out_channels, d.kernel_h, st));
+  } else if (mode == 2 || in_nhwc) {
     if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED))
       GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
   } else if (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)
@@ -559,12 +581,12 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.out_h = pl->g.out_h;
   p.out_w = pl->g.out_w;
   p.pq = pl->g.pq;
-  p.kernel_w = d.kernel_w;
+  p.kernel_w = r.eff_kernel_w;
   p.c_padded = r.c_padded;
   p.kb_per_tap = r.kb_per_tap;
   p.total_kb = r.total_kb;
   p.kb_per_split = r.kb_per_split;
-  p.stride_h = d.stride_h; p.stride_w = d.stride_w; p.pad_h = d.pad_h; p.pad_w = d.pad_w;
+  p.stride_h = d.stride_h; p.stride_w = r.eff_stride_w; p.pad_h = d.pad_h; p.pad_w = r.eff_pad_w;
   p.stages = r.stages;
   p.relu = d.relu; p.has_bias = d.has_bias;
   p.is_bf16 = d.precision == GIEB_BF16;
@@ -710,6 +732,28 @@ int gieb_conv_plan_info(const gieb_conv_plan* plan, gieb_conv_info* out) {
 int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y, void* workspace,
                      size_t workspace_bytes, void* stream) {
   return launch_impl(plan, x, w, bias, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int gieb_conv_plan_prepacked_weight_bytes(const gieb_conv_plan* plan, uint64_t* bytes) {
+  if (plan == nullptr || bytes == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null argument");
+  if (plan->r.variant == 3) return fail(GIEB_UNSUPPORTED, "the FP32 path reads OIHW weights directly");
+  *bytes = uint64_t(plan->desc.out_channels) * plan->desc.kernel_h * plan->r.eff_kernel_w * plan->r.c_padded * 2;
+  return GIEB_OK;
+}
+
+int gieb_conv_plan_prepack_weights(const gieb_conv_plan* plan, const void* w, void* dst, void* stream) {
+  if (plan == nullptr || w == nullptr || dst == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null argument");
+  const gieb_conv_desc& d = plan->desc;
+  const Resolved& r = plan->r;
+  if (r.variant == 3) return fail(GIEB_UNSUPPORTED, "the FP32 path reads OIHW weights directly");
+  if (reinterpret_cast<uintptr_t>(dst) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "prepacked weights must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (r.variant == 5)
+    GIEB_CUDA(gather_rows_launch(nullptr, nullptr, d.batch, d.in_channels, d.in_h, d.in_w, plan->g.out_w, d.kernel_w, d.stride_w, d.pad_w,
+                                 r.c_padded, w, dst, d.out_channels, d.kernel_h, st));
+  else
+    GIEB_CUDA(repack_launch(w, dst, d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
+  return GIEB_OK;
 }
 
 int gieb_conv_launch_fused(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, const void* residual, void* y,

@@ -154,6 +154,13 @@ cudaError_t repack_launch(const void* src, void* dst, int batch, int channels, i
 cudaError_t repack_pair_launch(const void* src_a, void* dst_a, int batch_a, int ch_a, int hw_a, int cp_a, const void* src_b,
                                void* dst_b, int batch_b, int ch_b, int hw_b, int cp_b, cudaStream_t stream);
 
+// Row gather for convolutions with few input channels (16-bit types, bit-exact):
+//   x2[n][h][q][s*C + c] = x[n][c][h][q*stride_w - pad_w + s]   (c2 = padded S*C elements per position, zero-filled)
+//   w2[o][r][s*C + c]    = w[o][c][r][s]
+// x == nullptr gathers only the weights, wsrc == nullptr only the activations.  x2 needs 16-byte alignment.
+cudaError_t gather_rows_launch(const void* x, void* x2, int batch, int channels, int h, int w, int q, int kernel_w, int stride_w,
+                               int pad_w, int c2, const void* wsrc, void* w2, int out_channels, int kernel_h, cudaStream_t stream);
+
 // FP32 SIMT implicit GEMM straight from NCHW.
 cudaError_t conv_fp32_launch(const void* x, const void* w, const void* bias, void* y, int batch, int c, int h, int wd,
                              int o, int r, int s, int stride_h, int stride_w, int pad_h, int pad_w, int out_h, int out_w,

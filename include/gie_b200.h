@@ -83,7 +83,10 @@ typedef struct gieb_conv_cfg {
                        4 = tensor path, tiled TMA over that copy (1x1, stride 1, pad 0);
                        2 = tensor path reading the caller's NCHW activations directly, no activation repack
                            (1x1, stride 1, pad 0, H*W % 8 == 0; a call whose x is not 16-byte aligned takes route 4);
-                       3 = FP32 SIMT                                                                          */
+                       3 = FP32 SIMT;
+                       5 = tensor path over row-gathered activations for inputs with few channels (NCHW input,
+                           kernel_w > 1, kernel_w * C <= 64): the S taps of a filter row become channels, so a 7x7
+                           stem over 3 channels reduces over 7 x 32 values instead of 49 x 16 padded ones      */
   int32_t tile_m;   /* output pixels per CTA tile: 128 or 256 (two accumulators share each weight tile); 0 = auto */
   int32_t reduce;   /* how split-K slices are summed: 0 = auto; 1 = FP32 partials in the workspace + a reduction launch;
                        2 = inside the convolution kernel: the slices of a tile form a thread-block cluster and are
@@ -137,6 +140,13 @@ GIEB_API int gieb_conv_plan_info(const gieb_conv_plan* plan, gieb_conv_info* out
  * alignment (src/runtime/execution_plan.cpp:103-108), current device == plan device (:113-117). */
 GIEB_API int gieb_conv_launch(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y,
                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* Static weights (GIEB_FLAG_WEIGHTS_PREPACKED): the layout a plan's kernel reads depends on its route ([O][R*S][Cp]
+ * on the repack routes -- what gieb_prepack_weights writes -- and [O][R][padded S*C] on the row-gather route), so the
+ * plan itself converts OIHW weights once: size of the converted tensor, and the conversion on `stream` (dst 16-byte
+ * aligned).  Stands in for the per-call weight transpose of the reference (src/kernels/tensor_core_mma.cu:310). */
+GIEB_API int gieb_conv_plan_prepacked_weight_bytes(const gieb_conv_plan* plan, uint64_t* bytes);
+GIEB_API int gieb_conv_plan_prepack_weights(const gieb_conv_plan* plan, const void* w, void* dst, void* stream);
 
 /* gieb_conv_launch with one more operand (no reference counterpart): `residual` has the shape, layout and storage
  * type of y and is added in FP32 before the activation and the single rounding.  Required (non-null) for plans

@@ -107,7 +107,11 @@ def test_workspace_layout_and_padding(pkg):
     assert i.launches == 3
     pre = P(pkg, 2, 130, 9, 9, 130, 3, 3, 1, 1, 1, 1, precision=pkg.FP16, flags=pkg.FLAG_WEIGHTS_PREPACKED)
     assert pkg.query(pre, pkg.make_cfg(tile_k=32, split_k=1)).workspace_bytes == a256(2 * 81 * 160 * 2)
-    assert pkg.query(P(pkg, 1, 3, 224, 224, 64, 7, 7, 2, 2, 3, 3, precision=pkg.FP16)).padded_channels == 16
+    stem = P(pkg, 1, 3, 224, 224, 64, 7, 7, 2, 2, 3, 3, precision=pkg.FP16)
+    assert pkg.query(stem, pkg.make_cfg(variant=1)).padded_channels == 16
+    auto = pkg.query(stem)  # few channels: the 7 taps of a filter row become 7 * 3 -> 32 channels of a 7 x 1 convolution
+    assert auto.variant == 5 and auto.padded_channels == 32
+    assert auto.workspace_bytes == a256(1 * 224 * 112 * 32 * 2) + a256(64 * 7 * 32 * 2)
     assert pkg.query(P(pkg, 1, 96, 27, 27, 192, 5, 5, 1, 1, 2, 2, precision=pkg.FP16)).padded_channels == 96
 
 

@@ -119,6 +119,30 @@ DIRECT_CASES = [
 ]
 
 
+GATHER_CASES = [
+    # few input channels: the S taps of a filter row become channels (variant 5)
+    ((2, 3, 32, 32, 64, 7, 7, 2, 2, 3, 3), dict()),                      # the stem geometry: picked automatically
+    ((2, 3, 37, 29, 64, 7, 7, 2, 2, 3, 3), dict(variant=5)),             # odd extents: partial last tile, padded columns
+    ((3, 1, 20, 24, 40, 3, 3, 1, 1, 1, 1), dict(variant=5)),             # one channel, 3 taps -> 16 gathered channels
+    ((2, 4, 18, 18, 48, 5, 5, 1, 1, 2, 2), dict(variant=5, tile_n=64)),  # 5 x 4 = 20 -> 32
+    ((2, 8, 16, 20, 96, 3, 5, 2, 1, 1, 2), dict(variant=5, tile_k=16, split_k=2)),   # 5 x 8 = 40 -> 48: three 16-channel slabs per row
+    ((1, 3, 64, 64, 32, 7, 7, 2, 2, 3, 3), dict(variant=5, tile_m=256, tile_n=32)),
+]
+
+
+@pytest.mark.parametrize("case", range(len(GATHER_CASES)))
+@pytest.mark.parametrize("prec_name", ["fp16", "bf16"])
+def test_row_gather_route(pkg, orc, oracle, case, prec_name):
+    args, kw = GATHER_CASES[case]
+    prec = orc.FP16 if prec_name == "fp16" else orc.BF16
+    p = orc.Problem.P(*args, precision=prec, bias=True, relu=(case % 2 == 0))
+    x, w, b = oracle.make_conv_data(p, 5000 + case, case % 4)
+    ref, scale = oracle.conv2d(p, x, w, b)
+    got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b, cfg=pkg.make_cfg(**kw))
+    assert plan.info.variant == 5
+    _check(oracle, p, got, ref, scale, f"gather case {case} {kw} {prec_name}")
+
+
 @pytest.mark.parametrize("case", range(len(DIRECT_CASES)))
 @pytest.mark.parametrize("prec_name", ["fp16", "bf16"])
 def test_pointwise_routes(pkg, orc, oracle, case, prec_name):
