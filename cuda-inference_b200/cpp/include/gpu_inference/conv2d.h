@@ -88,9 +88,9 @@ void validate_problem(const ConvProblem& prob);
 struct Conv2DOptions {
   Backend backend = Backend::kAuto;
   std::string kernel;         // name of one registered configuration to force (optional)
-  bool autotune = false;      // accepted; selection here is by the built-in cost model
-  bool force_retune = false;  // accepted, see above
-  std::string cache_path;     // accepted, unused
+  bool autotune = false;      // search the registered configurations now when the tuning cache has no entry
+  bool force_retune = false;  // ignore the cached winner and search again (with autotune)
+  std::string cache_path;     // tuning cache file; empty -> TuneCache::default_path()
 };
 
 class Conv2D {

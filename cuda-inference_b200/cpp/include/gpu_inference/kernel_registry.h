@@ -59,6 +59,9 @@ struct KernelDesc {
   std::shared_ptr<void> (*create_state)(const ConvProblem&) = nullptr;
   size_t (*persistent_bytes)(const ConvProblem&) = nullptr;
   void (*launch)(const LaunchArgs&) = nullptr;
+  // Not in the reference's table: the family's own time estimate for this configuration in microseconds (stands in
+  // for estimate_kernel of src/runtime/perf_model.cpp:130-174); null = unknown, such entries rank last.
+  double (*estimate_us)(const ConvProblem&) = nullptr;
 
   std::string describe() const;
 };

@@ -29,10 +29,11 @@ struct PlanHandle {
 [[noreturn]] void rethrow(int status) { throw Error(static_cast<StatusCode>(status), gieb_last_error()); }
 
 // One family point; all-zero = let the library choose.
-template <int PREC, int TM, int TN, int TK, int ST, int SK>
+// RD: how split-K slices are summed (0 auto, 1 workspace + reduction launch, 2 cluster / distributed shared memory).
+template <int PREC, int TM, int TN, int TK, int ST, int SK, int RD = 0>
 struct Point {
   static const gieb_conv_cfg* cfg() {
-    static const gieb_conv_cfg c = {TN, TK, ST, SK, 0, TM, 0, 0};
+    static const gieb_conv_cfg c = {TN, TK, ST, SK, 0, TM, RD, 0};
     return (TM | TN | TK | ST | SK) ? &c : nullptr;
   }
   static gieb_conv_info query(const ConvProblem& pr, int device = -1) {
@@ -65,6 +66,11 @@ struct Point {
     if (rc != GIEB_OK) rethrow(rc);
     return st;
   }
+  static double estimate_us(const ConvProblem& pr) {
+    const gieb_conv_desc d = to_c_desc(pr);
+    double us = 0;
+    return gieb_conv_estimate_us(&d, cfg(), &us) == GIEB_OK ? us : 1e30;
+  }
   static void launch(const LaunchArgs& la) {
     auto* st = static_cast<PlanHandle*>(la.plan_state);
     if (st == nullptr || st->h == nullptr) throw Error(StatusCode::kInternal, "kernel launched without plan state");
@@ -77,17 +83,17 @@ struct Point {
     std::ostringstream nm;
     if (PREC == int(Precision::kFp32)) nm << "b200_simt_fp32";
     else if (cfg() == nullptr) nm << "b200_tc_" << to_string(prec) << "_auto";
-    else nm << "b200_tc_" << to_string(prec) << "_" << TM << "x" << TN << "x" << TK << "_s" << ST << "_sk" << SK;
+    else nm << "b200_tc_" << to_string(prec) << "_" << TM << "x" << TN << "x" << TK << "_s" << ST << "_sk" << SK << (RD == 2 ? "c" : "");
     k.name = nm.str();
     k.backend = PREC == int(Precision::kFp32) ? Backend::kImplicitGemm : Backend::kTensorCore;
     k.version = kLibraryVersion;
-    k.params = {{"tile_pixels", TM}, {"tile_channels", TN}, {"tile_k", TK}, {"stages", ST}, {"split_k", SK}};
+    k.params = {{"tile_pixels", TM}, {"tile_channels", TN}, {"tile_k", TK}, {"stages", ST}, {"split_k", SK}, {"reduce", RD}};
     k.threads_per_block = PREC == int(Precision::kFp32) ? 256 : 384;
     k.tile_m = TN ? TN : 128;   // reference orientation: M = output channels
     k.tile_n = TM ? TM : 128;   //                        N = output pixels
     k.tile_k = TK ? TK : 64;
     k.uses_tensor_cores = PREC != int(Precision::kFp32);
-    k.launches = PREC == int(Precision::kFp32) ? 1 : (SK > 1 ? 3 : 2);
+    k.launches = PREC == int(Precision::kFp32) ? 1 : (SK > 1 && RD != 2 ? 3 : 2);
     k.efficiency_prior = 0.5;
     k.extra_traffic_bytes = &extra_traffic;
     k.supports = &supports;
@@ -97,6 +103,7 @@ struct Point {
     k.create_state = &create_state;
     k.persistent_bytes = &persistent_bytes;
     k.launch = &launch;
+    k.estimate_us = &estimate_us;
     out.push_back(std::move(k));
   }
 };
@@ -118,6 +125,13 @@ void add_family(std::vector<KernelDesc>& out) {
   Point<PREC, 128, 64, 64, 4, 4>::add(out);
   Point<PREC, 128, 128, 64, 4, 8>::add(out);
   Point<PREC, 128, 256, 64, 4, 3>::add(out);
+  Point<PREC, 128, 128, 64, 4, 2>::add(out);
+  Point<PREC, 128, 128, 64, 3, 2, 2>::add(out);  // the same slices summed inside a cluster
+  Point<PREC, 128, 128, 64, 4, 4, 2>::add(out);
+  Point<PREC, 128, 256, 64, 4, 2, 2>::add(out);
+  Point<PREC, 128, 256, 64, 3, 4, 2>::add(out);
+  Point<PREC, 256, 64, 64, 2, 1>::add(out);
+  Point<PREC, 256, 128, 64, 3, 1>::add(out);
 }
 
 std::vector<KernelDesc>& storage() {

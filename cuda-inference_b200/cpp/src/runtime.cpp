@@ -7,6 +7,7 @@
 #include <tuple>
 
 #include "gie_b200.h"
+#include "gpu_inference/autotuner.h"
 #include "gpu_inference/cuda_graph.h"
 #include "gpu_inference/dispatcher.h"
 #include "gpu_inference/execution_plan.h"
@@ -67,6 +68,34 @@ Selection Dispatcher::select(const ConvProblem& prob, const DeviceInfo& dev, con
     if (rejected.empty()) os << ": this library has no kernels for that backend (single sm_100a family: tensor_core, implicit_gemm)";
     for (size_t i = 0; i < rejected.size() && i < 4; ++i) os << "\n  - " << rejected[i].kernel << ": " << rejected[i].reason;
     throw Error(StatusCode::kUnsupported, os.str());
+  }
+  // measured winners first: the persisted tuning cache, then (when asked for) a search now
+  {
+    TuneCache cache(opt.cache_path);
+    std::string name;
+    double us = 0;
+    if (!opt.force_retune && cache.lookup(prob, dev, &name, &us, nullptr, opt.backend)) {
+      if (const KernelDesc* k = find_kernel(name)) {
+        sel.kernel = k;
+        sel.source = SelectionSource::kTuningCache;
+        sel.predicted_us = us;
+        sel.reason = "winner recorded in " + cache.path();
+        return sel;
+      }
+    }
+    if (opt.autotune) {
+      TuneOptions to;
+      to.only_backend = opt.backend;
+      to.cache_path = opt.cache_path;
+      to.force_retune = opt.force_retune;
+      to.timing.samples = 10;
+      const TuneResult tr = Autotuner::tune(prob, dev, to);
+      sel.kernel = find_kernel(tr.best_kernel);
+      sel.source = tr.from_cache ? SelectionSource::kTuningCache : SelectionSource::kTuned;
+      sel.predicted_us = tr.best_us;
+      sel.reason = "measured fastest of " + std::to_string(tr.candidates_measured) + " candidates";
+      if (sel.kernel != nullptr) return sel;
+    }
   }
   sel.kernel = cands.front();  // the family's "auto" entry: tile, stages and split-K come from the built-in cost model
   sel.source = opt.backend == Backend::kAuto ? SelectionSource::kCostModel : SelectionSource::kForcedBackend;

@@ -7,6 +7,11 @@
 #include <cmath>
 #include <thread>
 
+#include <unistd.h>
+
+#include <fstream>
+
+#include "gpu_inference/autotuner.h"
 #include "gpu_inference/cuda_graph.h"
 #include "gpu_inference/fused_ops.h"
 #include "gpu_inference/rmsnorm.h"
@@ -498,4 +503,233 @@ CASE(rmsnorm_rejects_bad_arguments) {
   EXPECT_THROWS(rmsnorm_forward(p, a.data(), b.data(), c.data(), nullptr, nullptr, nullptr), StatusCode::kInvalidArgument);
 }
 
-int main(int argc, char** argv) { return chk::run(argc, argv); }
+// ---------------------------------------------------------------------------------------------------------------
+// autotuner and tuning cache (tests/test_autotuner.cu:64-203), with faults injected on the host: a registry entry whose
+// launch writes zeros, and one whose launch raises
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+std::string temp_cache_path(const char* tag) {
+  return std::string("/tmp/gie_b200_tune_") + tag + "_" + std::to_string(long(getpid())) + ".json";
+}
+
+ConvProblem tune_problem() { return ts::problem(ts::geom(2, 32, 12, 12, 64, 3, 3, 1, 1, 1, 1), Precision::kFp16, true, true); }
+
+void launch_zeros(const LaunchArgs& la) {  // fast, wrong: the output is all zeros
+  const size_t bytes = size_t(la.problem->p.output_shape().numel()) * dtype_size(la.problem->dtype());
+  GIE_CUDA_CHECK(cudaMemsetAsync(la.y, 0, bytes, la.stream));
+}
+void launch_throws(const LaunchArgs&) { throw Error(StatusCode::kCudaError, "injected launch failure"); }
+bool fp16_only(const ConvProblem& pr, const DeviceInfo&, std::string* why) {
+  if (pr.precision == Precision::kFp16) return true;
+  if (why) *why = "test entry is fp16 only";
+  return false;
+}
+size_t no_bytes(const ConvProblem&) { return 0; }
+int64_t one_block(const ConvProblem&) { return 1; }
+double instant(const ConvProblem&) { return 0.01; }  // ranks first
+std::shared_ptr<void> no_state(const ConvProblem&) { return nullptr; }
+
+void inject_faulty_entries() {
+  if (find_kernel("test_fast_but_wrong_fp16") != nullptr) return;
+  for (int which = 0; which < 2; ++which) {
+    KernelDesc k;
+    k.name = which == 0 ? "test_fast_but_wrong_fp16" : "test_throwing_fp16";
+    k.backend = Backend::kTensorCore;
+    k.version = kLibraryVersion;
+    k.threads_per_block = 32;
+    k.supports = &fp16_only;
+    k.workspace_bytes = &no_bytes;
+    k.dynamic_smem_bytes = &no_bytes;
+    k.num_blocks = &one_block;
+    k.persistent_bytes = &no_bytes;
+    k.create_state = &no_state;
+    k.estimate_us = &instant;
+    k.launch = which == 0 ? &launch_zeros : &launch_throws;
+    kernel_registry_for_testing().push_back(k);
+  }
+}
+
+TuneOptions quick_tune(const std::string& cache) {
+  TuneOptions o;
+  o.timing.samples = 5;
+  o.timing.warmup_iters = 2;
+  o.timing.min_sample_ms = 0.2;
+  o.cache_path = cache;
+  return o;
+}
+
+}  // namespace
+
+CASE(tuner_never_selects_incorrect_or_failing_candidates) {
+  inject_faulty_entries();
+  const ConvProblem prob = tune_problem();
+  TuneOptions o = quick_tune(temp_cache_path("faults"));
+  o.use_cache = false;
+  const TuneResult r = Autotuner::tune(prob, DeviceInfo::current(), o);
+  EXPECT(r.best_kernel != "test_fast_but_wrong_fp16");
+  EXPECT(r.best_kernel != "test_throwing_fp16");
+  bool saw_wrong = false, saw_throw = false;
+  for (const CandidateResult& c : r.candidates) {
+    if (c.kernel == "test_fast_but_wrong_fp16") { saw_wrong = true; EXPECT(!c.measured); EXPECT(c.status.find("failed validation") == 0); }
+    if (c.kernel == "test_throwing_fp16") { saw_throw = true; EXPECT(!c.measured); EXPECT(c.status.find("error:") == 0); }
+  }
+  EXPECT(saw_wrong && saw_throw);
+  // the winner is right according to the independent CPU reference as well
+  ts::Bundle b = ts::make_bundle(prob, 77);
+  bool ran = false;
+  const KernelDesc* best = find_kernel(r.best_kernel);
+  EXPECT(best != nullptr);
+  const ErrorMetrics m = ts::run_kernel(*best, b, &ran, nullptr);
+  EXPECT_MSG(ran && m.passed(), r.best_kernel + " " + m.summary());
+  EXPECT(r.best_us > 0);
+}
+
+CASE(tuner_reports_search_space_and_cost) {
+  const ConvProblem prob = tune_problem();
+  TuneOptions o = quick_tune(temp_cache_path("space"));
+  o.use_cache = false;
+  const TuneResult r = Autotuner::tune(prob, DeviceInfo::current(), o);
+  EXPECT(r.candidates_total >= 10);
+  EXPECT(r.candidates_measured == r.candidates_total);
+  EXPECT(r.search_seconds > 0);
+  int measured = 0;
+  for (const CandidateResult& c : r.candidates)
+    if (c.measured) { ++measured; EXPECT(c.timing.median_us > 0); EXPECT(c.timing.samples == 5); EXPECT(c.frac_over_tol == 0); }
+  EXPECT(measured >= 5);
+}
+
+CASE(tuning_cache_hit_skips_the_search_and_persists) {
+  const std::string path = temp_cache_path("persist");
+  std::remove(path.c_str());
+  const ConvProblem prob = tune_problem();
+  const DeviceInfo& dev = DeviceInfo::current();
+  TuneOptions o = quick_tune(path);
+  o.model_keep = 4;
+  const TuneResult cold = Autotuner::tune(prob, dev, o);
+  EXPECT(!cold.from_cache);
+  const TuneResult warm = Autotuner::tune(prob, dev, o);
+  EXPECT(warm.from_cache);
+  EXPECT(warm.best_kernel == cold.best_kernel);
+  EXPECT(warm.candidates.empty());
+  TuneCache fresh(path);
+  std::string name;
+  double us = 0;
+  EXPECT(fresh.lookup(prob, dev, &name, &us));
+  EXPECT(name == cold.best_kernel);
+  EXPECT(us > 0);
+  o.force_retune = true;
+  EXPECT(!Autotuner::tune(prob, dev, o).from_cache);
+  EXPECT(fresh.lookup(prob, dev, &name, &us));  // the new search may have crowned another configuration
+  // selection honours the cache, and Conv2DOptions::autotune fills it
+  Conv2DOptions co;
+  co.cache_path = path;
+  const Selection from_cache = Dispatcher::select(prob, dev, co);
+  EXPECT(from_cache.source == SelectionSource::kTuningCache);
+  EXPECT(from_cache.kernel != nullptr && from_cache.kernel->name == name);
+  fresh.clear();
+  EXPECT(fresh.size() == size_t(0));
+  EXPECT(!fresh.lookup(prob, dev, &name, &us));
+  EXPECT(Dispatcher::select(prob, dev, co).source == SelectionSource::kCostModel);
+  co.autotune = true;
+  EXPECT(Dispatcher::select(prob, dev, co).source == SelectionSource::kTuned);
+  EXPECT(Dispatcher::select(prob, dev, co).source == SelectionSource::kTuningCache);
+  std::remove(path.c_str());
+}
+
+CASE(tuning_cache_key_separates_problems_precisions_and_fusion) {
+  const DeviceInfo& dev = DeviceInfo::current();
+  const ConvProblem a = tune_problem();
+  ConvProblem b = a, c = a, d = a;
+  b.p.batch += 1;
+  c.precision = Precision::kBf16;
+  d.activation = Activation::kNone;
+  const std::string ka = TuneCache::make_key(a, dev);
+  EXPECT(ka != TuneCache::make_key(b, dev));
+  EXPECT(ka != TuneCache::make_key(c, dev));
+  EXPECT(ka != TuneCache::make_key(d, dev));
+  EXPECT(ka != TuneCache::make_key(a, dev, Backend::kTensorCore));
+  EXPECT(ka.find(dev.name) != std::string::npos);
+  EXPECT(ka.find("cudart") != std::string::npos);
+}
+
+CASE(tuning_cache_rejects_stale_and_corrupt_entries) {
+  const std::string path = temp_cache_path("stale");
+  const ConvProblem prob = tune_problem();
+  const DeviceInfo& dev = DeviceInfo::current();
+  const std::string key = TuneCache::make_key(prob, dev);
+  std::string name;
+  double us = 0;
+  auto write = [&](const std::string& text) { std::ofstream f(path, std::ios::trunc); f << text; };
+  write("{ this is not json");
+  EXPECT(!TuneCache(path).lookup(prob, dev, &name, &us));
+  EXPECT(TuneCache(path).size() == size_t(0));
+  write("{\"schema\": 1, \"entries\": {\"" + key + "\": {\"kernel\": \"b200_tc_fp16_auto\", \"kernel_version\": " +
+        std::to_string(kLibraryVersion + 1) + ", \"us\": 5.0}}}");
+  EXPECT(!TuneCache(path).lookup(prob, dev, &name, &us));  // recorded for another version of the kernel
+  write("{\"schema\": 1, \"entries\": {\"" + key + "\": {\"kernel\": \"no_such_kernel\", \"kernel_version\": " +
+        std::to_string(kLibraryVersion) + ", \"us\": 5.0}}}");
+  EXPECT(!TuneCache(path).lookup(prob, dev, &name, &us));
+  write("{\"schema\": 2, \"entries\": {\"" + key + "\": {\"kernel\": \"b200_tc_fp16_auto\", \"kernel_version\": " +
+        std::to_string(kLibraryVersion) + ", \"us\": 5.0}}}");
+  EXPECT(!TuneCache(path).lookup(prob, dev, &name, &us));  // unknown schema
+  write("{\"schema\": 1, \"entries\": {\"" + key + "\": {\"kernel\": \"b200_tc_fp16_auto\", \"kernel_version\": " +
+        std::to_string(kLibraryVersion) + ", \"us\": 5.0, \"extra\": {\"nested\": 1}}}}");
+  EXPECT(TuneCache(path).lookup(prob, dev, &name, &us));   // well-formed: accepted, unknown fields skipped
+  EXPECT(name == "b200_tc_fp16_auto" && us == 5.0);
+  write("garbage");
+  TuneOptions o = quick_tune(path);
+  o.model_keep = 3;
+  const TuneResult again = Autotuner::tune(prob, dev, o);
+  EXPECT(!again.from_cache);
+  EXPECT(TuneCache(path).lookup(prob, dev, &name, &us));   // the corrupt file was rewritten
+  std::remove(path.c_str());
+}
+
+CASE(tuner_pruning_limits_the_search_and_runs_are_reproducible) {
+  const ConvProblem prob = tune_problem();
+  TuneOptions o = quick_tune(temp_cache_path("prune"));
+  o.use_cache = false;
+  o.model_keep = 4;
+  const TuneResult a = Autotuner::tune(prob, DeviceInfo::current(), o);
+  EXPECT(a.candidates_measured == 4);
+  int attempted = 0;
+  for (const CandidateResult& c : a.candidates)
+    if (c.status.find("rejected") != 0) ++attempted;
+  EXPECT(attempted == 4);
+  const TuneResult b = Autotuner::tune(prob, DeviceInfo::current(), o);
+  EXPECT(a.candidates.size() == b.candidates.size());
+  for (size_t i = 0; i < a.candidates.size() && i < b.candidates.size(); ++i) {
+    EXPECT(a.candidates[i].kernel == b.candidates[i].kernel);
+    EXPECT(a.candidates[i].measured == b.candidates[i].measured);
+    EXPECT(a.candidates[i].max_abs_err == b.candidates[i].max_abs_err);  // same seed, same data, same kernels
+  }
+  o.only_backend = Backend::kImplicitGemm;  // no FP16 kernel in that backend
+  EXPECT_THROWS(Autotuner::tune(prob, DeviceInfo::current(), o), StatusCode::kUnsupported);
+}
+
+CASE(timing_protocol_batches_short_kernels_and_summarises) {
+  const TimingStats s = summarize({5.0, 1.0, 3.0, 2.0, 4.0}, 7);
+  EXPECT(s.samples == 5 && s.inner_iters == 7);
+  EXPECT(s.median_us == 3.0 && s.min_us == 1.0 && s.max_us == 5.0 && s.mean_us == 3.0);
+  EXPECT(s.p10_us > 1.0 && s.p10_us < 2.0 && s.p90_us > 4.0 && s.p90_us < 5.0);
+  EXPECT(std::fabs(s.iqr_us - 2.0) < 1e-12);
+  DeviceBuffer buf(1 << 20);
+  TimingOptions t;
+  t.samples = 4;
+  t.min_sample_ms = 0.5;
+  const TimingStats m = time_stream_work([&](cudaStream_t st) { GIE_CUDA_CHECK(cudaMemsetAsync(buf.data(), 1, buf.size(), st)); }, nullptr, t);
+  EXPECT(m.samples == 4 && m.inner_iters > 1 && m.median_us > 0);
+  DeviceBuffer flush(64 << 20);
+  t.flush_buffer = flush.data();
+  t.flush_bytes = flush.size();
+  const TimingStats c = time_stream_work([&](cudaStream_t st) { GIE_CUDA_CHECK(cudaMemsetAsync(buf.data(), 1, buf.size(), st)); }, nullptr, t);
+  EXPECT(c.inner_iters == 1 && c.samples == 4);
+}
+
+int main(int argc, char** argv) {
+  // selection must not depend on a tuning cache left in the home directory
+  setenv("GIE_TUNE_CACHE", temp_cache_path("default").c_str(), 1);
+  std::remove(temp_cache_path("default").c_str());
+  return chk::run(argc, argv);
+}

@@ -106,6 +106,7 @@ struct Resolved {
   // Width geometry the kernel and its tensor maps see: the problem's own, except on the row-gather route (variant 5),
   // where the S taps of a filter row have become channels of a tensor of width Q (kernel width 1, stride 1, no padding).
   int eff_in_w, eff_kernel_w, eff_stride_w, eff_pad_w;
+  double est_cycles;  // the cost model's estimate for the chosen configuration (SM cycles; 0 on the FP32 path)
   int tma_epilogue;  // channel-contiguous output staged in shared memory and written by TMA stores
   int reduce;  // 1 workspace partials + reduction launch, 2 cluster (distributed shared memory); 0 when split_k == 1
   int c_padded, kb_per_tap, total_kb, kb_per_split;
@@ -326,6 +327,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   }
   r->tile_m = best_m;
   r->tile_n = best_n;
+  r->est_cycles = best;
   r->kb_per_split = ceil_div(r->total_kb, best_s);
   r->split_k = ceil_div(r->total_kb, r->kb_per_split);  // every slice non-empty
   r->tiles_m = ceil_div(rows, r->tile_m);
@@ -913,6 +915,68 @@ int gieb_maxpool2d_nhwc_launch(int precision, int batch, int channels, int h, in
   if (channels % 8 != 0) return fail(GIEB_INVALID_ARGUMENT, "channel-contiguous pooling needs a channel count that is a multiple of 8");
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "tensors must be 16-byte aligned");
   GIEB_CUDA(maxpool2d_nhwc_launch(precision, batch, channels, h, w, kernel, stride, pad, x, y, static_cast<cudaStream_t>(stream)));
+  return GIEB_OK;
+}
+
+int gieb_conv_estimate_us(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, double* microseconds) {
+  if (desc == nullptr || microseconds == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null argument");
+  const int st = gieb_conv_validate(desc);
+  if (st != GIEB_OK) return st;
+  Resolved r;
+  char why[256];
+  const int rs = resolve(*desc, cfg, &r, why, sizeof(why));
+  if (rs != GIEB_OK) return fail(rs, "%s", why);
+  // SM cycles at the 1.9 GHz these parts sustain; the FP32 path has no model: FLOPs at 20 TFLOP/s plus a launch
+  if (r.variant == 3) *microseconds = 3.0 + 2.0 * double(geometry(*desc).y_elems) * desc->in_channels * desc->kernel_h * desc->kernel_w / 20e6;
+  else *microseconds = r.est_cycles / 1900.0 + 3.0;
+  return GIEB_OK;
+}
+
+int gieb_conv_reference_launch(const gieb_conv_desc* desc, const void* x, const void* w, const void* bias, float* ref, float* scale,
+                               void* stream) {
+  const int st = gieb_conv_validate(desc);
+  if (st != GIEB_OK) return st;
+  if (x == nullptr || w == nullptr || ref == nullptr || scale == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
+  if (desc->has_bias && bias == nullptr) return fail(GIEB_INVALID_ARGUMENT, "problem has a bias but no bias pointer was given");
+  if (desc->precision == GIEB_TF32) return fail(GIEB_UNSUPPORTED, "TF32 is not offered");
+  const Geometry g = geometry(*desc);
+  GIEB_CUDA(reference_conv_launch(desc->precision, x, w, desc->has_bias ? bias : nullptr, ref, scale, desc->batch, desc->in_channels,
+                                  desc->in_h, desc->in_w, desc->out_channels, desc->kernel_h, desc->kernel_w, desc->stride_h,
+                                  desc->stride_w, desc->pad_h, desc->pad_w, g.out_h, g.out_w, desc->relu, static_cast<cudaStream_t>(stream)));
+  return GIEB_OK;
+}
+
+int gieb_conv_check_output(const gieb_conv_desc* desc, const void* y, const float* ref, const float* scale, double* max_abs_err,
+                           double* frac_over_tol, int64_t* nonfinite, void* stream) {
+  const int st = gieb_conv_validate(desc);
+  if (st != GIEB_OK) return st;
+  if (y == nullptr || ref == nullptr || scale == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
+  if (desc->precision == GIEB_TF32) return fail(GIEB_UNSUPPORTED, "TF32 is not offered");
+  const Geometry g = geometry(*desc);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned long long* d_out = nullptr;
+  GIEB_CUDA(cudaMalloc(&d_out, 3 * sizeof(unsigned long long)));
+  unsigned long long h[3] = {0, 0, 0};
+  cudaError_t e = cudaMemsetAsync(d_out, 0, sizeof(h), s);
+  if (e == cudaSuccess) e = check_output_launch(desc->precision, y, ref, scale, g.y_elems, int64_t(desc->in_channels) * desc->kernel_h * desc->kernel_w, d_out, s);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(h, d_out, sizeof(h), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  cudaFree(d_out);
+  if (e != cudaSuccess) return fail_cuda(e, "checking a convolution output");
+  float worst;
+  const unsigned int bits = static_cast<unsigned int>(h[2] & 0xffffffffu);
+  memcpy(&worst, &bits, sizeof(worst));
+  if (max_abs_err) *max_abs_err = double(worst);
+  if (frac_over_tol) *frac_over_tol = g.y_elems ? double(h[0]) / double(g.y_elems) : 0.0;
+  if (nonfinite) *nonfinite = int64_t(h[1]);
+  return GIEB_OK;
+}
+
+int gieb_fill_uniform(int precision, void* data, int64_t count, uint64_t seed, float lo, float hi, void* stream) {
+  if (data == nullptr || count < 0) return fail(GIEB_INVALID_ARGUMENT, "null pointer or negative count");
+  if (precision < 0 || precision > 2) return fail(GIEB_INVALID_ARGUMENT, "precision must be fp32, fp16 or bf16");
+  if (count == 0) return GIEB_OK;
+  GIEB_CUDA(fill_uniform_launch(precision, data, count, seed, lo, hi, static_cast<cudaStream_t>(stream)));
   return GIEB_OK;
 }
 
