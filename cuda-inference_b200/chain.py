@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import math
 
-from . import (ConvPlan, ConvProblem, add_relu, maxpool2d, maxpool2d_nhwc, FLAG_INPUT_NHWC, FLAG_OUTPUT_NHWC,
+from . import (ConvPlan, ConvProblem, GieError, add_relu, make_cfg, maxpool2d, maxpool2d_nhwc, FLAG_INPUT_NHWC, FLAG_OUTPUT_NHWC,
                FLAG_RESIDUAL, FLAG_WEIGHTS_PREPACKED)
 from .workloads import FP16, BF16, chain_flops, fuse_residuals, resnet50_chain
 
@@ -35,16 +35,34 @@ def layer_weight_bound(shape, relu: bool) -> float:
     return math.sqrt(6.0 / fan_in) if relu else 0.5 * math.sqrt(3.0 / fan_in)
 
 
+def candidate_cfgs(out_channels: int):
+    """Configuration points tried per layer when a chain is built with tune=True: the heuristic's own pick (None) plus
+    tile shapes and ring depths around it.  Unsupported points are skipped by plan creation."""
+    cfgs = [None]
+    for tile_m in (128, 256):
+        for tile_n in (64, 128, 256):
+            if tile_n > 64 and tile_n // 2 >= out_channels:
+                continue
+            for stages in (2, 3, 4):
+                cfgs.append(dict(tile_m=tile_m, tile_n=tile_n, stages=stages))
+    return cfgs
+
+
+_TUNED: dict = {}  # (problem fields, flags) -> best cfg kwargs (or None), per process
+
+
 class ConvChain:
     def __init__(self, batch: int, precision: int = FP16, image: int = 224, seed: int = 0, weights=None, device=None,
-                 layout: str = "nchw"):
+                 layout: str = "nchw", tune: bool = False):
         """weights: optional list of (w, b) host numpy arrays in storage bit patterns per convolution, in the order of
         resnet50_chain (tests); when None, weights are generated on the device from `seed` + layer index with the
         benchmark distributions.
         layout "nchw": every tensor NCHW, every layer repacks (the reference API's contract, layer by layer).
         layout "nhwc": the input image stays NCHW; every later tensor is channel-contiguous, weights are prepacked once
         at construction, and each block's residual add + ReLU runs inside the epilogue of its last convolution
-        (no repack launches, no add launches)."""
+        (no repack launches, no add launches).
+        tune: time candidate_cfgs() for every distinct layer on this GPU (a few launches each, on scratch buffers of the
+        chain) and build each plan with the fastest; the choice is remembered per process."""
         torch = _torch()
         self.torch = torch
         if layout not in ("nchw", "nhwc"):
@@ -73,8 +91,9 @@ class ConvChain:
                     flags |= FLAG_INPUT_NHWC  # the image itself (3 channels) stays NCHW and is repacked by the stem
                 if op.other >= 0:
                     flags |= FLAG_RESIDUAL
-            plan = ConvPlan(ConvProblem(s.batch, s.in_channels, s.in_h, s.in_w, s.out_channels, s.kernel, s.kernel, s.stride, s.stride,
-                                        s.pad, s.pad, 1, 1, 1, precision, True, op.relu, flags))
+            problem = ConvProblem(s.batch, s.in_channels, s.in_h, s.in_w, s.out_channels, s.kernel, s.kernel, s.stride, s.stride,
+                                  s.pad, s.pad, 1, 1, 1, precision, True, op.relu, flags)
+            plan = self._tuned_plan(problem, op) if tune else ConvPlan(problem)
             if weights is not None:
                 import numpy as np
                 w = torch.from_numpy(weights[li][0].view(np.int16)).to(self.device).view(self.dtype)
@@ -98,6 +117,51 @@ class ConvChain:
         self.ws_bytes = ws_bytes
         self.launches = sum(p.info.launches for _, p, _, _ in self.convs) + sum(1 for op in self.ops if op.kind != "conv")
         self.graph = None
+
+    def _tuned_plan(self, problem: ConvProblem, op) -> ConvPlan:
+        """The fastest of candidate_cfgs() for this layer, measured with CUDA events on the chain's own buffers."""
+        torch = self.torch
+        key = (problem.batch, problem.in_channels, problem.in_h, problem.in_w, problem.out_channels, problem.kernel_h, problem.stride_h,
+               problem.precision, problem.relu, problem.flags)
+        if key in _TUNED:
+            kw = _TUNED[key]
+            return ConvPlan(problem, make_cfg(**kw) if kw else None)
+        s = op.shape
+        x, y = self.slots[op.src], self.slots[op.dst]
+        res = self.slots[op.other] if op.other >= 0 else y
+        w = torch.zeros(s.w_elems * 4 + 4096, dtype=self.dtype, device=self.device)  # room for any padded layout
+        b = torch.zeros(s.out_channels, dtype=self.dtype, device=self.device)
+        stream = torch.cuda.current_stream().cuda_stream
+        best, best_kw, best_ms = None, None, float("inf")
+        for kw in candidate_cfgs(s.out_channels):
+            try:
+                plan = ConvPlan(problem, make_cfg(**kw) if kw else None)
+            except GieError:
+                continue
+            ws = torch.empty(plan.workspace_bytes + 256, dtype=torch.uint8, device=self.device)
+            wsp = (ws.data_ptr() + 255) // 256 * 256
+
+            def go():
+                if problem.flags & FLAG_RESIDUAL:
+                    plan.launch_fused(x.data_ptr(), w.data_ptr(), b.data_ptr(), res.data_ptr(), y.data_ptr(), wsp, plan.workspace_bytes, stream)
+                else:
+                    plan.launch(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), wsp, plan.workspace_bytes, stream)
+
+            go()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                go()
+            e1.record()
+            e1.synchronize()
+            ms = e0.elapsed_time(e1)
+            if plan.device_status() == 0 and ms < best_ms:
+                best, best_kw, best_ms = plan, kw, ms
+            del ws
+        if best is None:
+            raise RuntimeError("no configuration could run this layer")
+        _TUNED[key] = best_kw
+        return best
 
     @property
     def input(self):

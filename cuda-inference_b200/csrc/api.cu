@@ -42,7 +42,6 @@ int fail_cuda(cudaError_t e, const char* what) {
 // ---- hardware constants of the one supported target (B200, sm_100a) -------------------------------------------------
 constexpr int kNumSms = 148;
 constexpr size_t kMaxDynamicSmem = 232448;  // 227 KiB opt-in limit per CTA
-constexpr size_t kSmemBudget = 200 * 1024;  // ring + control; leaves headroom below the opt-in limit
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 int ceil_div(int64_t a, int64_t b) { return int((a + b - 1) / b); }
@@ -152,7 +151,7 @@ int pick_stages(int tile_m, int tile_n, int tile_k, int kb_per_split, int64_t ct
   int want = 1;
   if (ctas > kNumSms) want = 2;  // two CTAs per SM (the register file holds no more)
   if (want > by_tmem) want = by_tmem;
-  const size_t budget = want == 1 ? kSmemBudget : (kMaxDynamicSmem / want - 2048);
+  const size_t budget = want == 1 ? kMaxDynamicSmem - 1024 : (kMaxDynamicSmem / want - 2048);
   int stages = budget > 3072 + extra_smem + sb ? int((budget - 3072 - extra_smem) / sb) : 1;
   if (stages > 6) stages = 6;
   if (stages > kb_per_split) stages = kb_per_split;

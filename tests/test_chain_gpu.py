@@ -25,14 +25,14 @@ def _host_weights(orc, oracle, ops, precision, seed):
     return out
 
 
-def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed, layout="nchw"):
+def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed, layout="nchw", tune=False):
     import torch
     from cuda_inference_b200.chain import ConvChain
     from cuda_inference_b200 import workloads as wl
     ops, _ = wl.resnet50_chain(batch, precision, image)
     hw = _host_weights(orc, oracle, ops, precision, seed)
     chain = ConvChain(batch, precision, image, weights=[(oracle.to_bits16(precision, w), oracle.to_bits16(precision, b)) for w, b in hw],
-                      layout=layout)
+                      layout=layout, tune=tune)
     x = oracle.quantize(precision, oracle.rng(seed + 1000).draw(orc.DIST_NORMAL, batch * 3 * image * image))
     chain.input.view(torch.int16).copy_(torch.from_numpy(oracle.to_bits16(precision, x).view(np.int16)).cuda())
     for t in list(chain.slots.values())[1:]:
@@ -102,6 +102,13 @@ def test_chain_channel_contiguous_fused_residual_fp16(pkg, orc, oracle):
     of each block's last convolution.  One launch per convolution except the stem (which repacks the NCHW image)."""
     worst, nodes = _run_chain_case(pkg, orc, oracle, batch=2, image=64, precision=orc.FP16, seed=0, layout="nhwc")
     assert 53 + 2 <= nodes <= 53 + 2 + 20  # convolutions + stem repack + max-pool (+ workspace reductions of tiny layers)
+
+
+def test_chain_with_measured_configurations(pkg, orc, oracle):
+    """tune=True times candidate configurations per layer and keeps the fastest: whatever wins must still match the
+    oracle layer by layer."""
+    _run_chain_case(pkg, orc, oracle, batch=2, image=64, precision=orc.FP16, seed=9, layout="nhwc", tune=True)
+    _run_chain_case(pkg, orc, oracle, batch=2, image=64, precision=orc.FP16, seed=9, layout="nchw", tune=True)
 
 
 def test_chain_channel_contiguous_bf16(pkg, orc, oracle):
