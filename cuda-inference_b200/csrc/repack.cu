@@ -146,8 +146,11 @@ struct GatherJob {
   int64_t rows;       // B * H * Q
 };
 
-constexpr int kGatherRows = 128;  // (n, h, q) positions per block (= half the threads: two threads share a row)
+constexpr int kGatherRows = 128;  // output positions (consecutive q of one image row) per block
 
+// Block = one (image, input row, chunk of kGatherRows output columns).  The C input-row segments the chunk touches are
+// staged in shared memory with coalesced loads; each thread then assembles 16-byte output vectors from them through
+// a small table (element e of a gathered row -> offset of its (channel, tap) in the staged strip).
 __global__ void __launch_bounds__(256) gather_rows_kernel(const GatherJob j) {
   extern __shared__ __align__(16) uint8_t gsm[];
   ptx::grid_dep_wait();
@@ -167,54 +170,45 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const GatherJob j) {
     }
     return;
   }
-  // Tile [kGatherRows][c2 + 8] of 16-bit values (16-byte aligned rows for the vector copy-out; the padding spreads
-  // the 2-byte column writes of neighbouring rows over the banks).  Thread t owns row t % 128 and half of the filter taps: neighbouring threads read neighbouring columns of
-  // the same image row, so the global loads coalesce; index arithmetic is done once per thread, not per element.
-  uint16_t* tile = reinterpret_cast<uint16_t*>(gsm);
-  const int ld = j.c2 + 8;
-  const int64_t row0 = int64_t(blockIdx.x) * kGatherRows;
-  const int rl = threadIdx.x & (kGatherRows - 1), part = threadIdx.x >> 7;
-  const int64_t row = row0 + rl;
-  if (row < j.rows) {
-    const int q = int(row % j.Q);
-    const int64_t nh = row / j.Q;
-    const int h = int(nh % j.H), n = int(nh / j.H);
-    const int half = (j.S + 1) >> 1;
-    const int s_begin = part == 0 ? 0 : half, s_end = part == 0 ? half : j.S;
-    const uint16_t* xrow = j.x + (int64_t(n) * j.C * j.H + h) * j.W;  // channel 0 of this image row
-    const int64_t plane = int64_t(j.H) * j.W;
-    uint16_t* out = tile + rl * ld;
-    if (part == 1)  // zero padding behind the S*C gathered values
-      for (int e = j.S * j.C; e < j.c2; ++e) out[e] = 0;
-    // up to 4 taps x 4 channels per batch: all loads are issued before the first store, so their latencies overlap
-    for (int sb = s_begin; sb < s_end; sb += 4) {
-      for (int cb = 0; cb < j.C; cb += 4) {
-        uint16_t v[4][4];
-#pragma unroll
-        for (int a = 0; a < 4; ++a) {
-          const int s = sb + a;
-          const int wc = q * j.stride_w - j.pad_w + s;
-          const bool in = s < s_end && wc >= 0 && wc < j.W;
-#pragma unroll
-          for (int b = 0; b < 4; ++b) v[a][b] = (in && cb + b < j.C) ? __ldg(xrow + (cb + b) * plane + wc) : uint16_t(0);
-        }
-#pragma unroll
-        for (int a = 0; a < 4; ++a) {
-#pragma unroll
-          for (int b = 0; b < 4; ++b)
-            if (sb + a < s_end && cb + b < j.C) out[(sb + a) * j.C + cb + b] = v[a][b];
-        }
-      }
-    }
+  const int chunks = (j.Q + kGatherRows - 1) / kGatherRows;
+  const int chunk = int(blockIdx.x % unsigned(chunks));
+  const unsigned nh = blockIdx.x / unsigned(chunks);
+  const int h = int(nh % unsigned(j.H)), n = int(nh / unsigned(j.H));
+  const int q0 = chunk * kGatherRows;
+  const int nq = min(kGatherRows, j.Q - q0);
+  const int strip_w = (kGatherRows - 1) * j.stride_w + j.S;  // input columns one chunk can touch
+  const int w0 = q0 * j.stride_w - j.pad_w;                  // first of them (may be negative: zero padding)
+  uint16_t* strip = reinterpret_cast<uint16_t*>(gsm);        // [C][strip_w]
+  int* table = reinterpret_cast<int*>(gsm + ((size_t(j.C) * strip_w * 2 + 15) & ~size_t(15)));  // [c2], -1 = padding
+  const uint16_t* xrow = j.x + (int64_t(n) * j.C * j.H + h) * j.W;
+  const int64_t plane = int64_t(j.H) * j.W;
+  for (int i = threadIdx.x; i < j.C * strip_w; i += 256) {
+    const int c = i / strip_w, col = i - c * strip_w;
+    const int wc = w0 + col;
+    strip[i] = (wc >= 0 && wc < j.W) ? __ldg(xrow + c * plane + wc) : uint16_t(0);
+  }
+  for (int e = threadIdx.x; e < j.c2; e += 256) {
+    const int s = e / j.C, c = e - s * j.C;
+    table[e] = e < j.S * j.C ? c * strip_w + s : -1;
   }
   __syncthreads();
-  // the block's rows are contiguous in X2: 16-byte vectors, consecutive threads -> consecutive vectors
-  const int vpr = j.c2 >> 3;  // vectors per row
-  const int nrows = int(j.rows - row0 < kGatherRows ? j.rows - row0 : kGatherRows);
-  uint4* dst = reinterpret_cast<uint4*>(j.x2 + row0 * j.c2);
-  for (int i = threadIdx.x; i < nrows * vpr; i += 256) {
-    const int r = i / vpr, k = i - r * vpr;
-    dst[i] = *reinterpret_cast<const uint4*>(tile + r * ld + 8 * k);
+  const int vpr = j.c2 >> 3;  // 16-byte vectors per output position
+  uint4* dst = reinterpret_cast<uint4*>(j.x2 + ((int64_t(n) * j.H + h) * j.Q + q0) * j.c2);
+  for (int i = threadIdx.x; i < nq * vpr; i += 256) {
+    const int rl = i / vpr, k = i - rl * vpr;
+    const int base = rl * j.stride_w;
+    uint16_t o[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      const int off = table[k * 8 + t];
+      o[t] = off >= 0 ? strip[off + base] : uint16_t(0);
+    }
+    uint4 v;
+    v.x = uint32_t(o[0]) | (uint32_t(o[1]) << 16);
+    v.y = uint32_t(o[2]) | (uint32_t(o[3]) << 16);
+    v.z = uint32_t(o[4]) | (uint32_t(o[5]) << 16);
+    v.w = uint32_t(o[6]) | (uint32_t(o[7]) << 16);
+    dst[i] = v;
   }
 }
 
@@ -265,7 +259,8 @@ cudaError_t gather_rows_launch(const void* x, void* x2, int batch, int channels,
   j.B = batch; j.C = channels; j.H = h; j.W = w; j.Q = q; j.S = kernel_w; j.R = kernel_h; j.O = out_channels;
   j.stride_w = stride_w; j.pad_w = pad_w; j.c2 = c2;
   j.rows = int64_t(batch) * h * q;
-  const int64_t xb = x != nullptr ? (j.rows + kGatherRows - 1) / kGatherRows : 0;
+  const int chunks = (q + kGatherRows - 1) / kGatherRows;
+  const int64_t xb = x != nullptr ? int64_t(batch) * h * chunks : 0;
   int64_t wb = 0;
   if (wsrc != nullptr) {
     wb = (int64_t(out_channels) * kernel_h * c2 + 255) / 256;
@@ -273,7 +268,9 @@ cudaError_t gather_rows_launch(const void* x, void* x2, int batch, int channels,
   }
   if (xb + wb > 2147483647LL || xb + wb == 0) return cudaErrorInvalidValue;
   j.x_blocks = unsigned(xb);
-  const size_t smem = size_t(kGatherRows) * (c2 + 8) * 2;
+  const int strip_w = (kGatherRows - 1) * stride_w + kernel_w;
+  const size_t smem = ((size_t(channels) * strip_w * 2 + 15) & ~size_t(15)) + size_t(c2) * 4;
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;  // channels * (127 * stride + S) * 2 bytes: far below for S*C <= 64, stride <= 8
   const cudaError_t e = launch_pdl(gather_rows_kernel, dim3(unsigned(xb + wb)), dim3(256), smem, stream, j);
   if (e != cudaSuccess) return e;
   return cudaGetLastError();
