@@ -20,7 +20,7 @@ namespace gie {
 //   kFp32  FP32 storage, plain FP32 FMA arithmetic (never TF32)
 //   kFp16  FP16 storage, tensor cores, FP32 accumulate
 //   kBf16  BF16 storage, tensor cores, FP32 accumulate
-//   kTf32  accepted by the descriptor, answered with kUnsupported by this library
+//   kTf32  FP32 storage, inputs rounded to TF32 (ties away), tensor-core contraction (kind::tf32), FP32 accumulate / output
 enum class Precision { kFp32, kFp16, kBf16, kTf32 };
 
 DataType tensor_dtype(Precision p);

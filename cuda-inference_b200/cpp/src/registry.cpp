@@ -140,6 +140,15 @@ std::vector<KernelDesc>& storage() {
     r.reserve(256);  // element addresses stay valid when a test appends entries
     add_family<int(Precision::kFp16)>(r);
     add_family<int(Precision::kBf16)>(r);
+    // FP32 storage on the tensor cores (kind::tf32): slab rows of 32 / 16 FP32 values
+    Point<int(Precision::kTf32), 0, 0, 0, 0, 0>::add(r);
+    Point<int(Precision::kTf32), 128, 64, 32, 4, 1>::add(r);
+    Point<int(Precision::kTf32), 128, 128, 32, 3, 1>::add(r);
+    Point<int(Precision::kTf32), 128, 256, 32, 3, 1>::add(r);
+    Point<int(Precision::kTf32), 256, 128, 32, 2, 1>::add(r);
+    Point<int(Precision::kTf32), 128, 128, 32, 4, 2>::add(r);
+    Point<int(Precision::kTf32), 128, 128, 32, 3, 2, 2>::add(r);
+    Point<int(Precision::kTf32), 128, 64, 16, 4, 1>::add(r);
     Point<int(Precision::kFp32), 0, 0, 0, 0, 0>::add(r);
     std::set<std::string> names;
     for (const KernelDesc& k : r)

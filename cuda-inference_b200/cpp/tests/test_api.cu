@@ -190,7 +190,7 @@ CASE(suite_every_shape_every_precision_has_a_passing_kernel) {
   const Distribution dists[4] = {Distribution::kUniform, Distribution::kNormal, Distribution::kSparseSigned, Distribution::kPositive};
   int cell = 0, runs = 0;
   for (const ts::NamedShape& sh : ts::shapes()) {
-    for (Precision prec : {Precision::kFp32, Precision::kFp16, Precision::kBf16}) {
+    for (Precision prec : {Precision::kFp32, Precision::kFp16, Precision::kBf16, Precision::kTf32}) {
       const int mode = cell % 3;
       ++cell;
       const ConvProblem prob = ts::problem(sh.p, prec, mode >= 1, mode == 2);

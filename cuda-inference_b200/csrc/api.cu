@@ -224,7 +224,9 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   memset(&c, 0, sizeof(c));
   if (user) c = *user;
 
-  if (d.precision == GIEB_TF32) return no("TF32 is not offered: the only TF32 route of the reference is its cuBLAS im2col backend");
+  const bool tf32 = d.precision == GIEB_TF32;
+  if (tf32 && (d.flags & (GIEB_FLAG_WEIGHTS_PREPACKED | GIEB_FLAG_INPUT_NHWC | GIEB_FLAG_OUTPUT_NHWC | GIEB_FLAG_RESIDUAL)))
+    return no("prepacked weights, channel-contiguous tensors and the fused residual are offered for FP16 / BF16 only");
   if (d.precision == GIEB_FP32) {
     if (c.variant != 0 && c.variant != 3) return no("FP32 runs on the SIMT kernel only (variant 3)");
     if (d.flags & (GIEB_FLAG_WEIGHTS_PREPACKED | GIEB_FLAG_INPUT_NHWC | GIEB_FLAG_OUTPUT_NHWC | GIEB_FLAG_RESIDUAL))
@@ -238,13 +240,13 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
     return GIEB_OK;
   }
   const bool pointwise = d.kernel_h == 1 && d.kernel_w == 1 && d.stride_h == 1 && d.stride_w == 1 && d.pad_h == 0 && d.pad_w == 0;
-  const bool direct_ok = pointwise && (d.in_h * d.in_w) % 8 == 0;
+  const bool direct_ok = !tf32 && pointwise && (d.in_h * d.in_w) % 8 == 0;
   if (c.variant != 0 && c.variant != 1 && c.variant != 2 && c.variant != 4 && c.variant != 5)
     return no("unknown kernel variant for 16-bit precision (1 = im2col-mode TMA, 2 = direct NCHW 1x1, 4 = tiled TMA for 1x1, 5 = row gather)");
   // Row gather: the S taps of a filter row become channels (c2 = padded S*C <= 64, one slab or less per filter row).
   // Worth it when it at least halves the padded reduction length (a 7x7 stem over 3 channels: 7*32 instead of 49*16).
   const int gather_c2 = round_up(d.kernel_w * d.in_channels, 16);
-  const bool gather_ok = !(d.flags & GIEB_FLAG_INPUT_NHWC) && d.kernel_w > 1 && gather_c2 <= 64;
+  const bool gather_ok = !tf32 && !(d.flags & GIEB_FLAG_INPUT_NHWC) && d.kernel_w > 1 && gather_c2 <= 64;
   const bool gather_pays = gather_ok && 2 * gather_c2 <= d.kernel_w * round_up(d.in_channels, 16);
   if (c.variant == 5 && !gather_ok) return no("variant 5 (row gather) needs an NCHW input, a kernel wider than 1 and kernel_w * channels <= 64");
   if (c.variant == 4 && !pointwise) return no("variant 4 (tiled activation loads) needs a 1x1 kernel with stride 1 and no padding");
@@ -268,13 +270,28 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   if (d.stride_h > 8 || d.stride_w > 8) return no("stride > 8 cannot be expressed by the TMA im2col traversal stride");
   if (d.pad_h > 127 || d.pad_w > 127 || d.kernel_h > 128 || d.kernel_w > 128) return no("padding/kernel extent exceeds the TMA im2col corner range");
 
-  r->tile_k = c.tile_k ? c.tile_k : (in_nhwc ? (d.in_channels % 64 == 0 ? 64 : (d.in_channels % 32 == 0 ? 32 : 16)) : pick_tile_k(d.in_channels));
+  if (tf32) {
+    // FP32 storage: a 128/64/32-byte slab row holds 32/16/8 values.  cfg.tile_k counts FP32 values; internally every
+    // tile and padding quantity is kept in 2-byte units (twice the FP32 counts) so that the byte layouts coincide.
+    if (c.variant == 2 || c.variant == 5) return no("TF32 runs on the im2col (1) and tiled (4) routes");
+    int tk = c.tile_k;
+    if (tk == 0) {
+      const int base = round_up(d.in_channels, 8);
+      tk = double(round_up(d.in_channels, 32)) <= 1.15 * base ? 32 : (double(round_up(d.in_channels, 16)) <= 1.15 * base ? 16 : 8);
+    }
+    if (tk != 8 && tk != 16 && tk != 32) return no("tile_k must be 8, 16 or 32 for TF32 (FP32 values per slab row)");
+    r->tile_k = 2 * tk;
+  } else {
+    r->tile_k = c.tile_k ? c.tile_k : (in_nhwc ? (d.in_channels % 64 == 0 ? 64 : (d.in_channels % 32 == 0 ? 32 : 16)) : pick_tile_k(d.in_channels));
+  }
   if (r->tile_k != 16 && r->tile_k != 32 && r->tile_k != 64) return no("tile_k must be 16, 32 or 64");
   if (in_nhwc && d.in_channels % r->tile_k != 0) return no("tile_k must divide the channel count of a channel-contiguous input (it is read in place)");
   if (gather) {
     if (!c.tile_k) r->tile_k = gather_c2 % 64 == 0 ? 64 : (gather_c2 % 32 == 0 ? 32 : 16);
     if (gather_c2 % r->tile_k != 0) return no("tile_k must divide the gathered row length (padded kernel_w * channels)");
     r->c_padded = gather_c2;
+  } else if (tf32) {
+    r->c_padded = 2 * round_up(d.in_channels, r->tile_k / 2);
   } else {
     r->c_padded = round_up(d.in_channels, r->tile_k);
   }
@@ -365,14 +382,14 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
   out->variant = r.variant;
   out->cfg.tile_m = r.tile_m;
   out->cfg.tile_n = r.tile_n;
-  out->cfg.tile_k = r.tile_k;
+  out->cfg.tile_k = d.precision == GIEB_TF32 ? r.tile_k / 2 : r.tile_k;  // in elements of the storage type
   out->cfg.stages = r.stages;
   out->cfg.split_k = r.split_k;
   out->cfg.variant = r.variant;
   out->cfg.reduce = r.reduce;
   out->workspace_bytes = r.ws_total;
   out->persistent_bytes = sizeof(uint32_t);
-  out->padded_channels = r.c_padded;
+  out->padded_channels = d.precision == GIEB_TF32 ? r.c_padded / 2 : r.c_padded;
   if (r.variant == 3) {
     out->dynamic_smem_bytes = 0;
     out->threads_per_block = r.tile_n == 64 ? 256 : 64;
@@ -385,7 +402,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
     // repack (activations and weights in one launch; none when both are consumed in place), convolution, reduction
     const bool x_in_place = r.variant == 2 || (d.flags & GIEB_FLAG_INPUT_NHWC);
     const bool w_in_place = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) != 0;
-    out->launches = (x_in_place && w_in_place ? 0 : 1) + 1 + (r.reduce == 1 ? 1 : 0);
+    out->launches = (x_in_place && w_in_place ? 0 : 1) + 1 + (r.reduce == 1 ? 1 : 0) + (d.precision == GIEB_TF32 ? 1 : 0);  // TF32: X and W repacked by two launches
   }
 }
 
@@ -441,8 +458,11 @@ namespace {
 int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* wk, CUtensorMap* tm_act, CUtensorMap* tm_wgt) {
   const gieb_conv_desc& d = pl->desc;
   const Resolved& r = pl->r;
-  const CUtensorMapDataType dt = d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const bool tf32 = d.precision == GIEB_TF32;
+  const CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                      : (d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   const CUtensorMapSwizzle sw = swizzle_for(r.tile_k);
+  const int esh = tf32 ? 1 : 0;  // element counts along channels: 2-byte units >> esh
   if (mode == 2) {  // NCHW seen as {HW, C, N}: one box = 64 pixels (128 bytes, the swizzle span) x tile_k channels
     const cuuint64_t hw = cuuint64_t(d.in_h) * d.in_w;
     const cuuint64_t dims[3] = {hw, cuuint64_t(d.in_channels), cuuint64_t(d.batch)};
@@ -454,32 +474,32 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (NCHW activations) failed with CUresult %d", int(res));
     small_tensor_fixup(tm_act, size_t(hw) * d.in_channels * d.batch * 2);
   } else if (mode == 1) {  // 1x1 / stride 1 / pad 0: the NHWC copy is the GEMM operand [pixels][Cp] itself
-    const cuuint64_t dims[2] = {cuuint64_t(r.c_padded), cuuint64_t(d.batch) * d.in_h * d.in_w};
+    const cuuint64_t dims[2] = {cuuint64_t(r.c_padded >> esh), cuuint64_t(d.batch) * d.in_h * d.in_w};
     const cuuint64_t strides[1] = {cuuint64_t(r.c_padded) * 2};
-    const cuuint32_t box[2] = {cuuint32_t(r.tile_k), cuuint32_t(kTileM)};
+    const cuuint32_t box[2] = {cuuint32_t(r.tile_k >> esh), cuuint32_t(kTileM)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult res = g_encode_tiled(tm_act, dt, 2, const_cast<void*>(xn), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (activations) failed with CUresult %d", int(res));
     small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * d.in_w * r.c_padded * 2);
   } else {
-    const cuuint64_t dims[4] = {cuuint64_t(r.c_padded), cuuint64_t(r.eff_in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
+    const cuuint64_t dims[4] = {cuuint64_t(r.c_padded >> esh), cuuint64_t(r.eff_in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
     const cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(r.eff_in_w) * r.c_padded * 2,
                                    cuuint64_t(d.in_h) * r.eff_in_w * r.c_padded * 2};
     const int lower[2] = {-r.eff_pad_w, -d.pad_h};
     const int upper[2] = {r.eff_pad_w - (r.eff_kernel_w - 1), d.pad_h - (d.kernel_h - 1)};
     const cuuint32_t trav[4] = {1, cuuint32_t(r.eff_stride_w), cuuint32_t(d.stride_h), 1};
-    const CUresult res = g_encode_im2col(tm_act, dt, 4, const_cast<void*>(xn), dims, strides, lower, upper, cuuint32_t(r.tile_k),
+    const CUresult res = g_encode_im2col(tm_act, dt, 4, const_cast<void*>(xn), dims, strides, lower, upper, cuuint32_t(r.tile_k >> esh),
                                          cuuint32_t(kTileM), trav, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeIm2col failed with CUresult %d", int(res));
     small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * r.eff_in_w * r.c_padded * 2);
   }
   {
-    const cuuint64_t kp = cuuint64_t(d.kernel_h) * r.eff_kernel_w * r.c_padded;
-    const cuuint64_t dims[2] = {kp, cuuint64_t(d.out_channels)};
+    const cuuint64_t kp = cuuint64_t(d.kernel_h) * r.eff_kernel_w * r.c_padded;  // in 2-byte units
+    const cuuint64_t dims[2] = {kp >> esh, cuuint64_t(d.out_channels)};
     const cuuint64_t strides[1] = {kp * 2};
-    const cuuint32_t box[2] = {cuuint32_t(r.tile_k), cuuint32_t(r.tile_n)};
+    const cuuint32_t box[2] = {cuuint32_t(r.tile_k >> esh), cuuint32_t(r.tile_n)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult res = g_encode_tiled(tm_wgt, dt, 2, const_cast<void*>(wk), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -561,7 +581,10 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   if (st_maps != GIEB_OK) return st_maps;
 
   if (ev) GIEB_CUDA(cudaEventRecord(ev[0], st));
-  if (r.variant == 5) {  // row gather of the activations (and of the weights unless they come gathered)
+  if (d.precision == GIEB_TF32) {  // FP32 tensors rounded to TF32 while they are repacked (two launches)
+    GIEB_CUDA(repack_tf32_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded / 2, st));
+    GIEB_CUDA(repack_tf32_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded / 2, st));
+  } else if (r.variant == 5) {  // row gather of the activations (and of the weights unless they come gathered)
     GIEB_CUDA(gather_rows_launch(x, xn, d.batch, d.in_channels, d.in_h, d.in_w, pl->g.out_w, d.kernel_w, d.stride_w, d.pad_w, r.c_padded,
                                  (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? nullptr : w, const_cast<void*>(wk), d.out_channels, d.kernel_h, st));
   } else if (mode == 2 || in_nhwc) {
@@ -591,9 +614,10 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.stages = r.stages;
   p.relu = d.relu; p.has_bias = d.has_bias;
   p.is_bf16 = d.precision == GIEB_BF16;
-  p.bias_fp32 = (d.flags & GIEB_FLAG_BIAS_FP32) ? 1 : 0;
+  p.is_tf32 = d.precision == GIEB_TF32;
+  p.bias_fp32 = (p.is_tf32 || (d.flags & GIEB_FLAG_BIAS_FP32)) ? 1 : 0;
   p.a_mode = mode;
-  p.idesc = ptx::make_idesc_f16(kTileM, r.tile_n, p.is_bf16, mode == 2, false);
+  p.idesc = p.is_tf32 ? ptx::make_idesc_tf32(kTileM, r.tile_n, false, false) : ptx::make_idesc_f16(kTileM, r.tile_n, p.is_bf16, mode == 2, false);
   p.bias = bias;
   p.residual = residual;
   p.out_nhwc = (d.flags & GIEB_FLAG_OUTPUT_NHWC) ? 1 : 0;
@@ -634,7 +658,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
   if (r.reduce == 1)
-    GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_bf16, residual,
+    GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_tf32 ? 2 : p.is_bf16, residual,
                                    p.out_nhwc, y, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[3], st));
   return GIEB_OK;

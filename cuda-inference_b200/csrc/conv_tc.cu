@@ -30,6 +30,20 @@ namespace {
 
 constexpr uint32_t kCtrlBytes = 3072;  // [0,2048): two bias tiles as float; [2048,3072): mbarriers + TMEM address slot
 
+template <typename T>
+__device__ __forceinline__ float load_as_float(const T* p) {
+  if constexpr (std::is_same<T, __half>::value) return __half2float(*p);
+  else if constexpr (std::is_same<T, float>::value) return *p;
+  else return __bfloat162float(*p);
+}
+
+template <typename T>
+__device__ __forceinline__ T round_to(float a) {
+  if constexpr (std::is_same<T, __half>::value) return __float2half_rn(a);
+  else if constexpr (std::is_same<T, float>::value) return a;
+  else return __float2bfloat16_rn(a);
+}
+
 // Epilogue of one 32-column chunk for one accumulator row (= one output pixel): + bias, optional ReLU, one rounding,
 // 32 stores that are `stride` elements apart (consecutive output channels of an NCHW tensor).  Branch-free body:
 // the ReLU / storage-type / full-chunk decisions are made once per chunk by the caller.
@@ -45,17 +59,10 @@ __device__ __forceinline__ void store_chunk_full(const uint32_t (&v)[32], const 
     for (int t = 0; t < 4; ++t) {
       float a = __uint_as_float(v[q * 4 + t]) + bb[t];
       if (RELU) a = fmaxf(a, 0.f);
-      if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) *dst = __float2half_rn(a);
-      else *dst = __float2bfloat16_rn(a);
+      *dst = round_to<T>(a);
       dst += stride;
     }
   }
-}
-
-template <typename T>
-__device__ __forceinline__ float load_as_float(const T* p) {
-  if constexpr (std::is_same<T, __half>::value) return __half2float(*p);
-  else return __bfloat162float(*p);
 }
 
 // General form: any element stride, partial chunks, optional residual (same layout as the output).
@@ -68,8 +75,7 @@ __device__ __forceinline__ void store_chunk_tail(const uint32_t (&v)[32], const 
       float a = __uint_as_float(v[j]) + bias[j];
       if (res != nullptr) a += load_as_float(res + int64_t(j) * stride);
       if (RELU) a = fmaxf(a, 0.f);
-      if constexpr (std::is_same<T, __half>::value) dst[int64_t(j) * stride] = __float2half_rn(a);
-      else dst[int64_t(j) * stride] = __float2bfloat16_rn(a);
+      dst[int64_t(j) * stride] = round_to<T>(a);
     }
   }
 }
@@ -155,21 +161,33 @@ __device__ __forceinline__ void chunk_to_staging(const uint32_t (&v)[32], const 
 template <typename T>
 __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const float* bias, T* dst, const T* res, int64_t stride,
                                             int nvalid, int relu) {
-  if (nvalid == 32 && stride == 1 && ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(res)) & 15u) == 0) {
-    if (res != nullptr) {
-      if (relu) store_chunk_contiguous<T, true, true>(v, bias, dst, res);
-      else store_chunk_contiguous<T, false, true>(v, bias, dst, res);
-    } else {
-      if (relu) store_chunk_contiguous<T, true, false>(v, bias, dst, res);
-      else store_chunk_contiguous<T, false, false>(v, bias, dst, res);
+  if constexpr (sizeof(T) == 2) {
+    if (nvalid == 32 && stride == 1 && ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(res)) & 15u) == 0) {
+      if (res != nullptr) {
+        if (relu) store_chunk_contiguous<T, true, true>(v, bias, dst, res);
+        else store_chunk_contiguous<T, false, true>(v, bias, dst, res);
+      } else {
+        if (relu) store_chunk_contiguous<T, true, false>(v, bias, dst, res);
+        else store_chunk_contiguous<T, false, false>(v, bias, dst, res);
+      }
+      return;
     }
-  } else if (nvalid == 32 && res == nullptr) {
+  }
+  if (nvalid == 32 && res == nullptr) {
     if (relu) store_chunk_full<T, true>(v, bias, dst, stride);
     else store_chunk_full<T, false>(v, bias, dst, stride);
   } else {
     if (relu) store_chunk_tail<T, true>(v, bias, dst, res, stride, nvalid);
     else store_chunk_tail<T, false>(v, bias, dst, res, stride, nvalid);
   }
+}
+
+// Output element type by the problem's precision: float for TF32, else the 16-bit storage type.
+template <typename F>
+__device__ __forceinline__ void with_output_type(const ConvTcParams& p, F&& f) {
+  if (p.is_tf32) f(static_cast<float*>(p.y), static_cast<const float*>(p.residual));
+  else if (p.is_bf16) f(static_cast<__nv_bfloat16*>(p.y), static_cast<const __nv_bfloat16*>(p.residual));
+  else f(static_cast<__half*>(p.y), static_cast<const __half*>(p.residual));
 }
 
 // Persistent CTAs: each CTA walks the tile list (tile = blockIdx.x, += gridDim.x; output-channel tiles fastest, then
@@ -261,6 +279,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     // No more producers than ring slots: a warp must never be a full ring ahead of its own previous slab, or the
     // parity of the slot's barrier could not tell its phases apart.
     const int np = min(kProducerWarps, stages);
+    const int esh = p.is_tf32 ? 1 : 0;  // FP32 elements: channel coordinates are half the 2-byte-unit counts
     int s = warp;        // ring slot of this warp's next slab (the ring and its phases continue across tiles)
     uint32_t phase = 0;
     while (s >= stages) { s -= stages; phase ^= 1u; }
@@ -319,14 +338,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         if (lane < nbox) {
           if (p.a_mode == 2) {
             // 64 pixels x BK channels, [channel][pixel] in shared memory
-            ptx::tma_load_3d(a_dst + a_off, &tm_act, &full_bar[s], c1, cb * BK, c3);
+            ptx::tma_load_3d(a_dst + a_off, &tm_act, &full_bar[s], c1, (cb * BK) >> esh, c3);
           } else if (p.a_mode == 1) {
-            ptx::tma_load_2d(a_dst + a_off, &tm_act, &full_bar[s], cb * BK, c1);
+            ptx::tma_load_2d(a_dst + a_off, &tm_act, &full_bar[s], (cb * BK) >> esh, c1);
           } else {
-            ptx::tma_load_im2col_4d(a_dst + a_off, &tm_act, &full_bar[s], cb * BK, c1, c2, c3, uint16_t(sx), uint16_t(r));
+            ptx::tma_load_im2col_4d(a_dst + a_off, &tm_act, &full_bar[s], (cb * BK) >> esh, c1, c2, c3, uint16_t(sx), uint16_t(r));
           }
         }
-        if (lane == 0) ptx::tma_load_2d(a_dst + A_BYTES, &tm_wgt, &full_bar[s], k0 + cb * BK, n0);
+        if (lane == 0) ptx::tma_load_2d(a_dst + A_BYTES, &tm_wgt, &full_bar[s], (k0 + cb * BK) >> esh, n0);
         cb += np;
         while (cb >= p.kb_per_tap) {
           cb -= p.kb_per_tap;
@@ -372,31 +391,41 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       if (!__all_sync(0xffffffffu, drained)) break;
       ptx::tc_fence_after_sync();
       const uint32_t acc = tmem_base + buf * ACC_COLS;
-      for (int i = 0; i < num_kb; ++i) {
-        const bool ok = ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout);
-        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-        ptx::tc_fence_after_sync();
-        const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
-        const uint32_t b_addr = a_addr + A_BYTES;
-        if (ptx::elect_one()) {
+      // The slab loop exists three times (16-bit K-major A, 16-bit pixel-major A, TF32): the operand form and the MMA
+      // kind are compile-time inside it, so the elected lane's issue sequence carries no branch per instruction.
+      auto slab_loop = [&](auto form_tag) {
+        constexpr int FORM = decltype(form_tag)::value;  // 0: kind::f16, K-major A; 1: kind::f16, pixel-major A; 2: kind::tf32
+        for (int i = 0; i < num_kb; ++i) {
+          const bool ok = ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout);
+          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+          if (ptx::elect_one()) {
 #pragma unroll
-          for (int h = 0; h < MH; ++h) {
-            if (h < halves) {
+            for (int h = 0; h < MH; ++h) {
+              if (h < halves) {
 #pragma unroll
-              for (int k = 0; k < MMAS_PER_SLAB; ++k) {
-                // K-major A: 16 channels = 32 bytes along a row.  Pixel-major A (mode 2): 16 channels = 16 rows of 128 B.
-                const uint64_t adesc = p.a_mode == 2
-                                           ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
-                                           : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
-                ptx::mma_f16_ss(acc + h * BN, adesc, ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32), p.idesc, (i | k) != 0);
+                for (int k = 0; k < MMAS_PER_SLAB; ++k) {
+                  // K-major A: one MMA's K extent (16 two-byte or 8 four-byte values) = 32 bytes along a row.
+                  // Pixel-major A (form 1): 16 channels = 16 rows of 128 B.
+                  const uint64_t adesc = FORM == 1 ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
+                                                   : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
+                  const uint64_t bdesc = ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32);
+                  if constexpr (FORM == 2) ptx::mma_tf32_ss(acc + h * BN, adesc, bdesc, p.idesc, (i | k) != 0);
+                  else ptx::mma_f16_ss(acc + h * BN, adesc, bdesc, p.idesc, (i | k) != 0);
+                }
               }
             }
+            ptx::mma_commit(&empty_bar[s]);  // frees the slot once these MMAs have read it
           }
-          ptx::mma_commit(&empty_bar[s]);  // frees the slot once these MMAs have read it
+          __syncwarp();
+          if (++s == stages) { s = 0; phase ^= 1u; }
         }
-        __syncwarp();
-        if (++s == stages) { s = 0; phase ^= 1u; }
-      }
+      };
+      if (p.is_tf32) slab_loop(std::integral_constant<int, 2>{});
+      else if (p.a_mode == 2) slab_loop(std::integral_constant<int, 1>{});
+      else slab_loop(std::integral_constant<int, 0>{});
       // accumulator set complete (also reached after a time-out in the slab loop, so nobody hangs)
       if (ptx::elect_one()) ptx::mma_commit(&acc_full[buf]);
       __syncwarp();
@@ -551,12 +580,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           if (m_ok) {
             const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
             const int64_t off = base + int64_t(chunk * 32) * cstride;
-            if (p.is_bf16)
-              store_chunk<__nv_bfloat16>(v, bias_t + chunk * 32, static_cast<__nv_bfloat16*>(p.y) + off,
-                                         p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + off : nullptr, cstride, nvalid, p.relu);
-            else
-              store_chunk<__half>(v, bias_t + chunk * 32, static_cast<__half*>(p.y) + off,
-                                  p.residual ? static_cast<const __half*>(p.residual) + off : nullptr, cstride, nvalid, p.relu);
+            with_output_type(p, [&](auto* yp, auto* rp) {
+              store_chunk(v, bias_t + chunk * 32, yp + off, rp ? rp + off : nullptr, cstride, nvalid, p.relu);
+            });
           }
         }
         break;  // one tile per CTA in this mode
@@ -611,12 +637,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
                 for (int j = 0; j < 32; ++j)
                   if (j < nvalid) dst[int64_t(j) * cstride] = __uint_as_float(v[j]);
               }
-            } else if (p.is_bf16) {
-              store_chunk<__nv_bfloat16>(v, bias_t + chunk * 32, static_cast<__nv_bfloat16*>(p.y) + off,
-                                         p.residual ? static_cast<const __nv_bfloat16*>(p.residual) + off : nullptr, cstride, nvalid, p.relu);
             } else {
-              store_chunk<__half>(v, bias_t + chunk * 32, static_cast<__half*>(p.y) + off,
-                                  p.residual ? static_cast<const __half*>(p.residual) + off : nullptr, cstride, nvalid, p.relu);
+              with_output_type(p, [&](auto* yp, auto* rp) {
+                store_chunk(v, bias_t + chunk * 32, yp + off, rp ? rp + off : nullptr, cstride, nvalid, p.relu);
+              });
             }
           }
         }
@@ -690,6 +714,9 @@ template <>
 __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+__device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 
@@ -772,17 +799,21 @@ cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, const CUtensorMap
 }
 
 cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total, int out_channels, int pq, const void* bias,
-                                 int bias_fp32, int relu, int is_bf16, const void* residual, int out_nhwc, void* y,
+                                 int bias_fp32, int relu, int out_type, const void* residual, int out_nhwc, void* y,
                                  cudaStream_t stream) {
   const int64_t slice_stride = (total + 3) & ~int64_t(3);
-  const bool vec = (reinterpret_cast<uintptr_t>(y) & 7u) == 0;
+  const bool vec = out_type != 2 && (reinterpret_cast<uintptr_t>(y) & 7u) == 0;
   const int64_t work = vec ? (total + 3) / 4 : total;
   int64_t blocks = (work + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
   const FastDiv fd_pq = FastDiv::make(pq), fd_oc = FastDiv::make(out_channels);
   cudaError_t e;
-  if (is_bf16) {
+  if (out_type == 2) {
+    auto* yy = static_cast<float*>(y);
+    auto* rr = static_cast<const float*>(residual);
+    e = launch_pdl(splitk_reduce_kernel<float, false>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, rr, out_nhwc, yy);
+  } else if (out_type == 1) {
     auto* yy = static_cast<__nv_bfloat16*>(y);
     auto* rr = static_cast<const __nv_bfloat16*>(residual);
     if (vec) e = launch_pdl(splitk_reduce_kernel<__nv_bfloat16, true>, dim3(unsigned(blocks)), dim3(256), 0, stream, partial, splits, total, slice_stride, out_channels, pq, fd_pq, fd_oc, bias, bias_fp32, relu, rr, out_nhwc, yy);

@@ -109,6 +109,9 @@ struct ConvTcParams {
   int stride_h, stride_w, pad_h, pad_w;
   int stages;
   int relu, has_bias, is_bf16, bias_fp32;
+  // 1: FP32 storage computed as TF32 (kind::tf32).  Tile and padding quantities (BK, c_padded, kb_per_tap) stay in
+  // 2-byte units, i.e. twice the FP32 element counts; TMA coordinates along channels are halved; Y is float.
+  int is_tf32;
   // How the activation operand reaches shared memory:
   //   0  im2col-mode TMA over the channel-padded NHWC copy (any kernel / stride / padding)
   //   1  tiled TMA over the same copy seen as the matrix [pixels][c_padded] (1x1, stride 1, pad 0)
@@ -145,11 +148,13 @@ cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, const CUtensorMap
 
 // Sum of split-K partials + bias (+ residual) + ReLU + one rounding; `total` = B*O*P*Q elements in the output's order.
 cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total, int out_channels, int pq,
-                                 const void* bias, int bias_fp32, int relu, int is_bf16, const void* residual, int out_nhwc,
-                                 void* y, cudaStream_t stream);
+                                 const void* bias, int bias_fp32, int relu, int out_type, const void* residual, int out_nhwc,
+                                 void* y, cudaStream_t stream);  // out_type: 0 fp16, 1 bf16, 2 fp32
 
 // 16-bit [B][C][HW] -> [B][HW][Cp] (zero-filled channel padding).
 cudaError_t repack_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream);
+// FP32 [B][C][HW] -> [B][HW][Cp] (Cp in FP32 elements) with every value rounded to TF32 (ties away).
+cudaError_t repack_tf32_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream);
 // Two repacks (activations + weights) in ONE launch; src_b == nullptr runs only the first.
 cudaError_t repack_pair_launch(const void* src_a, void* dst_a, int batch_a, int ch_a, int hw_a, int cp_a, const void* src_b,
                                void* dst_b, int batch_b, int ch_b, int hw_b, int cp_b, cudaStream_t stream);

@@ -276,6 +276,44 @@ cudaError_t gather_rows_launch(const void* x, void* x2, int batch, int channels,
   return cudaGetLastError();
 }
 
+namespace {
+
+// FP32 [B][C][HW] -> [B][HW][Cp] with every value rounded to TF32 (round to nearest, ties away: cvt.rna, the rounding
+// of round_to_tf32 in the reference, src/runtime/reference.cu:95-104), channels zero-padded to Cp.  32 x 32 tiles.
+__global__ void __launch_bounds__(256) repack_tf32_kernel(const float* __restrict__ src, float* __restrict__ dst, int C, int HW, int Cp) {
+  __shared__ float tile[32][33];
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
+  const int b = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 8 rows of 32 threads
+  for (int r = ty; r < 32; r += 8) {
+    const int c = c0 + r, px = p0 + tx;
+    float v = 0.f;
+    if (c < C && px < HW) {
+      uint32_t u;
+      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(src[(size_t(b) * C + c) * HW + px]));
+      v = __uint_as_float(u);
+    }
+    tile[r][tx] = v;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int px = p0 + r, c = c0 + tx;
+    if (px < HW && c < Cp) dst[(size_t(b) * HW + px) * Cp + c] = tile[tx][r];
+  }
+}
+
+}  // namespace
+
+cudaError_t repack_tf32_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream) {
+  const dim3 grid(unsigned((hw + 31) / 32), unsigned((c_padded + 31) / 32), unsigned(batch));
+  if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;
+  const cudaError_t e = launch_pdl(repack_tf32_kernel, grid, dim3(256), 0, stream, static_cast<const float*>(src), static_cast<float*>(dst),
+                                   channels, hw, c_padded);
+  if (e != cudaSuccess) return e;
+  return cudaGetLastError();
+}
+
 cudaError_t repack_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream) {
   return repack_pair_launch(src, dst, batch, channels, hw, c_padded, nullptr, nullptr, 0, 0, 0, 0, stream);
 }

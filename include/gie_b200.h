@@ -43,8 +43,10 @@ typedef enum gieb_status {
   GIEB_INTERNAL = 7
 } gieb_status;
 
-/* Order of gie::Precision (include/gpu_inference/conv2d.h:26). TF32 is accepted by the descriptor and answered
- * with GIEB_UNSUPPORTED: the reference reaches it only through cuBLAS (src/kernels/im2col.cu:108-112). */
+/* Order of gie::Precision (include/gpu_inference/conv2d.h:26).  GIEB_TF32: FP32 tensors (x, w, bias, y), inputs rounded
+ * to TF32 (nearest, ties away) and multiplied on the tensor cores (kind::tf32), FP32 accumulation and output; the
+ * reference reaches this precision only through cuBLAS (src/kernels/im2col.cu:108-112).  cfg.tile_k counts FP32 values
+ * for it (8, 16 or 32 per slab row); routes 1 and 4; no extension flags. */
 typedef enum gieb_precision { GIEB_FP32 = 0, GIEB_FP16 = 1, GIEB_BF16 = 2, GIEB_TF32 = 3 } gieb_precision;
 
 /* Optional behaviour beyond the reference API (all off by default = exact drop-in behaviour). */

@@ -71,8 +71,9 @@ def test_query_precision_routing_and_reasons(pkg):
     idr = pkg.query(P(pkg, 2, 64, 28, 28, 64, 1, 1, precision=pkg.BF16))
     assert idr.supported and idr.variant == 2                       # H*W % 8 == 0 -> straight from NCHW, no activation repack
     assert not pkg.query(P(pkg, 2, 64, 14, 14, 64, 1, 1, precision=pkg.FP16), pkg.make_cfg(variant=2)).supported
-    tf = pkg.query(P(pkg, *base, precision=pkg.TF32))
-    assert not tf.supported and b"TF32" in tf.reason
+    tf = pkg.query(P(pkg, *base, precision=pkg.TF32))  # FP32 storage on the tensor cores (kind::tf32)
+    assert tf.supported and tf.variant in (1, 4) and tf.cfg.tile_k in (8, 16, 32)
+    assert not pkg.query(P(pkg, *base, precision=pkg.TF32, flags=pkg.FLAG_OUTPUT_NHWC)).supported
     big_stride = pkg.query(P(pkg, 1, 16, 64, 64, 16, 3, 3, 9, 9, 1, 1, precision=pkg.FP16))
     assert not big_stride.supported and b"stride" in big_stride.reason
     assert not pkg.query(P(pkg, *base, precision=pkg.FP16), pkg.make_cfg(variant=3)).supported

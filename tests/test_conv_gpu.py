@@ -27,16 +27,16 @@ def _suite_cases(orc):
     cases = []
     cell = 0
     for name, args in orc.CORRECTNESS_SHAPES.items():
-        for prec in (orc.FP32, orc.FP16, orc.BF16):
+        for prec in (orc.FP32, orc.FP16, orc.BF16, orc.TF32):
             mode = cell % 3
             cell += 1
             cases.append((name, args, prec, mode, cell % 4, 0xC0FFEE + cell))
     return cases
 
 
-@pytest.mark.parametrize("prec_name", ["fp32", "fp16", "bf16"])
+@pytest.mark.parametrize("prec_name", ["fp32", "fp16", "bf16", "tf32"])
 def test_correctness_shape_suite(pkg, orc, oracle, prec_name):
-    prec = {"fp32": orc.FP32, "fp16": orc.FP16, "bf16": orc.BF16}[prec_name]
+    prec = {"fp32": orc.FP32, "fp16": orc.FP16, "bf16": orc.BF16, "tf32": orc.TF32}[prec_name]
     ran = 0
     for name, args, pr, mode, dist, seed in _suite_cases(orc):
         if pr != prec:
@@ -117,6 +117,31 @@ DIRECT_CASES = [
     ((2, 1024, 4, 4, 256, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=256, tile_k=64, stages=4, split_k=4, reduce=2), 0),
     ((3, 256, 4, 6, 200, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=128, tile_k=64, stages=2, split_k=2, reduce=2), 0),
 ]
+
+
+TF32_CASES = [
+    # FP32 storage on the tensor cores (kind::tf32): inputs rounded to TF32 (ties away) by the repack, FP32 accumulate and output
+    ((2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict()),
+    ((2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=32, stages=3, split_k=2, reduce=1)),
+    ((2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_n=64, tile_k=16, stages=4, split_k=2, reduce=2)),
+    ((2, 130, 9, 9, 130, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=8, stages=3)),
+    ((3, 70, 10, 20, 255, 1, 1, 1, 1, 0, 0), dict(variant=4, tile_n=128, tile_k=32)),
+    ((3, 70, 10, 20, 255, 1, 1, 1, 1, 0, 0), dict(variant=1)),
+    ((1, 3, 33, 31, 20, 7, 7, 2, 2, 3, 3), dict()),
+    ((2, 64, 28, 28, 128, 3, 3, 2, 2, 1, 1), dict(tile_m=256, tile_n=128, tile_k=32, stages=2)),
+    ((8, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict()),
+]
+
+
+@pytest.mark.parametrize("case", range(len(TF32_CASES)))
+def test_tf32_tensor_path(pkg, orc, oracle, case):
+    args, kw = TF32_CASES[case]
+    p = orc.Problem.P(*args, precision=orc.TF32, bias=(case % 3 != 0), relu=(case % 2 == 0))
+    x, w, b = oracle.make_conv_data(p, 6000 + case, case % 4)
+    ref, scale = oracle.conv2d(p, x, w, b if p.has_bias else None)
+    got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b if p.has_bias else None, cfg=pkg.make_cfg(**kw))
+    assert plan.info.variant in (1, 4)
+    _check(oracle, p, got, ref, scale, f"tf32 case {case} {kw}")
 
 
 GATHER_CASES = [
