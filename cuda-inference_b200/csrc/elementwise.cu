@@ -85,6 +85,41 @@ maxpool2d_kernel(const T* __restrict__ x, T* __restrict__ y, int planes, int h, 
   }
 }
 
+// 3x3 / stride 2 / pad 1 on 16-bit planes with an even width (the ResNet stem pool): output column ox needs input
+// columns 2ox-1, 2ox, 2ox+1.  One aligned 32-bit load fetches (2ox, 2ox+1); column 2ox-1 is the upper half of the left
+// neighbour's word, taken with a warp shuffle (lane 0 of a warp loads it itself).  Three loads per output instead of nine.
+template <typename T2>
+__global__ void __launch_bounds__(256)
+maxpool_3x3s2p1_kernel(const uint32_t* __restrict__ x, uint16_t* __restrict__ y, int planes, int h, int w2, int oh, int ow) {
+  const int ox = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per output column, consecutive in a warp
+  const int oy = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const bool live = ox < ow;
+  const int cx = live ? ox : ow - 1;  // dead lanes shadow the last column so that shuffles stay defined
+  for (int plane = blockIdx.z; plane < planes; plane += gridDim.z) {
+    const uint32_t* xp = x + size_t(plane) * h * w2;
+    T2 best = T2();
+    bool first = true;
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+      const int iy = 2 * oy - 1 + r;
+      if (iy < 0 || iy >= h) continue;  // block-uniform (oy is per block)
+      const uint32_t word = xp[size_t(iy) * w2 + cx];  // columns 2cx, 2cx+1 (2cx+1 < w: w is even, cx < ow = w/2)
+      uint32_t left = __shfl_up_sync(0xffffffffu, word, 1);
+      if (lane == 0) left = cx > 0 ? xp[size_t(iy) * w2 + cx - 1] : 0u;
+      const T2 cur = *reinterpret_cast<const T2*>(&word);
+      T2 m = __hmax2(cur, T2(cur.y, cur.y));            // max(col 2cx, col 2cx+1) in .x
+      if (cx > 0) {
+        const T2 lf = *reinterpret_cast<const T2*>(&left);
+        m = __hmax2(m, T2(lf.y, lf.y));                  // col 2cx-1
+      }
+      best = first ? m : __hmax2(best, m);
+      first = false;
+    }
+    if (live) y[(size_t(plane) * oh + oy) * ow + ox] = *reinterpret_cast<const uint16_t*>(&best.x);
+  }
+}
+
 // Channel-contiguous variant ([B][H][W][C], C % 8 == 0, 16-bit types): one thread per (output pixel, group of 8
 // channels); consecutive threads take consecutive groups, so every window tap is a coalesced 16-byte load.
 template <typename T2>
@@ -165,6 +200,16 @@ cudaError_t maxpool2d_launch(int precision, int batch, int channels, int h, int 
   const int64_t planes64 = int64_t(batch) * channels;
   if (planes64 > 2147483647LL || int64_t(oh) * ow > 2147483647LL) return cudaErrorInvalidValue;
   const int planes = int(planes64);
+  if ((precision == 1 || precision == 2) && k == 3 && stride == 2 && pad == 1 && (w & 1) == 0 && (h & 1) == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 3u) == 0 && oh <= 65535) {
+    const dim3 g3(unsigned((ow + 255) / 256), unsigned(oh), unsigned(planes < 4096 ? planes : 4096));
+    const dim3 b3(unsigned(ow < 256 ? ((ow + 31) / 32) * 32 : 256));
+    if (precision == 1)
+      maxpool_3x3s2p1_kernel<__half2><<<g3, b3, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint16_t*>(y), planes, h, w / 2, oh, ow);
+    else
+      maxpool_3x3s2p1_kernel<__nv_bfloat162><<<g3, b3, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint16_t*>(y), planes, h, w / 2, oh, ow);
+    return cudaGetLastError();
+  }
   const dim3 g(unsigned((oh * ow + 255) / 256), unsigned(planes < 32768 ? planes : 32768));
   switch (precision) {
     case 0: maxpool2d_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(y), planes, h, w, oh, ow, k, stride, pad); break;
