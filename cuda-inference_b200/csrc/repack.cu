@@ -72,19 +72,24 @@ __device__ __forceinline__ void repack_tile(uint32_t* tile, const uint16_t* __re
   }
 }
 
-// Small-HW variant (filter taps: HW = R*S <= 64).  One CTA handles 64 channels of one batch entry: the source
-// slab [64][HW] is contiguous, so it is read linearly, then written as [HW][64].  `slab` holds kTile * kSmallHwMax
-// 16-bit words (the same shared memory as the tiled variant's tile).
+// Small-HW variant (filter taps: HW = R*S <= 64).  One CTA handles `span` channels of one batch entry (a multiple of
+// 64, as many as fit the shared memory: 448 for a 3x3 filter, 4096 for 1x1): the source slab [span][HW] is
+// contiguous, so it is read linearly (128-bit loads when aligned), then written as [HW][span].  `slab` holds
+// kTile * kSmallHwMax 16-bit words (the same shared memory as the tiled variant's tile).
 constexpr int kSmallHwMax = 64;
 __device__ __forceinline__ void repack_small_hw(uint16_t* slab, const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
-                                                int C, int HW, int Cp, int c_tile, int b) {
-  const int c0 = c_tile * kTile;
-  const int nch = min(kTile, C - c0);  // may be <= 0 for pure padding tiles
+                                                int C, int HW, int Cp, int span, int c_tile, int b) {
+  const int c0 = c_tile * span;
+  const int nch = min(span, C - c0);  // may be <= 0 for pure padding tiles
   const int n = nch > 0 ? nch * HW : 0;
   const uint16_t* s = src + (size_t(b) * C + c0) * HW;
-  for (int i = threadIdx.x; i < n; i += 256) slab[i] = s[i];
+  if ((reinterpret_cast<uintptr_t>(s) & 15u) == 0 && (n & 7) == 0) {
+    for (int i = threadIdx.x; i < (n >> 3); i += 256) reinterpret_cast<uint4*>(slab)[i] = reinterpret_cast<const uint4*>(s)[i];
+  } else {
+    for (int i = threadIdx.x; i < n; i += 256) slab[i] = s[i];
+  }
   __syncthreads();
-  const int groups = min(kTile, Cp - c0) >> 3;  // 8-channel vectors in this tile
+  const int groups = min(span, Cp - c0) >> 3;  // 8-channel vectors in this tile
   for (int v = threadIdx.x; v < HW * groups; v += 256) {
     const int px = v / groups, cg = v - px * groups;
     uint16_t o[8];
@@ -109,6 +114,7 @@ struct RepackJob {
   int C, HW, Cp, batch;
   int mode;
   int hw_tiles, c_tiles;
+  int span;  // mode 2: channels per CTA
   unsigned blocks;  // hw_tiles * c_tiles * batch
 };
 
@@ -126,7 +132,7 @@ __global__ void __launch_bounds__(256) repack_jobs_kernel(const RepackJob a, con
   id /= unsigned(j.hw_tiles);
   const int c_tile = int(id % unsigned(j.c_tiles));
   const int bi = int(id / unsigned(j.c_tiles));
-  if (j.mode == 2) repack_small_hw(reinterpret_cast<uint16_t*>(smem), j.src, j.dst, j.C, j.HW, j.Cp, c_tile, bi);
+  if (j.mode == 2) repack_small_hw(reinterpret_cast<uint16_t*>(smem), j.src, j.dst, j.C, j.HW, j.Cp, j.span, c_tile, bi);
   else if (j.mode == 1) repack_tile<true>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
   else repack_tile<false>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
 }
@@ -218,9 +224,13 @@ RepackJob make_job(const void* src, void* dst, int batch, int channels, int hw, 
   j.dst = static_cast<uint16_t*>(dst);
   j.C = channels; j.HW = hw; j.Cp = c_padded; j.batch = batch;
   j.c_tiles = (c_padded + kTile - 1) / kTile;
+  j.span = kTile;
   if (hw < 32 && hw <= kSmallHwMax) {
     j.mode = 2;
     j.hw_tiles = 1;
+    j.span = (kTile * kSmallHwMax / hw) / kTile * kTile;  // as many 64-channel groups as the slab holds
+    if (j.span > ((c_padded + kTile - 1) / kTile) * kTile) j.span = ((c_padded + kTile - 1) / kTile) * kTile;
+    j.c_tiles = (c_padded + j.span - 1) / j.span;
   } else {
     j.mode = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (hw & 7) == 0) ? 1 : 0;
     j.hw_tiles = (hw + kTile - 1) / kTile;
