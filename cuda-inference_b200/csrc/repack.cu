@@ -18,7 +18,9 @@ constexpr int kTile = 64;          // channels and pixels per CTA tile
 constexpr int kLdWords = 33;       // 32-bit words per shared-memory row (64 px + 1 word of padding)
 
 // Tiled transpose of one 64-channel x 64-pixel tile by 256 threads; `tile` is kTile * kLdWords words of shared memory.
-template <bool VEC_LOAD>
+// LOAD: 0 = 2-byte loads (any alignment), 1 = 16-byte loads (HW % 8 == 0, 16-byte aligned source), 2 = 4-byte loads
+// (HW even, 4-byte aligned source).
+template <int LOAD>
 __device__ __forceinline__ void repack_tile(uint32_t* tile, const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int C,
                                             int HW, int Cp, int hw_tile, int c_tile, int b) {
   const int px0 = hw_tile * kTile;
@@ -26,7 +28,7 @@ __device__ __forceinline__ void repack_tile(uint32_t* tile, const uint16_t* __re
   const uint16_t* s = src + (size_t(b) * C + c0) * HW + px0;
   const int t = threadIdx.x;
 
-  if (VEC_LOAD) {
+  if (LOAD == 1) {
     // 64 channels x 8 vectors of 8 pixels; a vector never straddles HW because HW % 8 == 0.
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -36,6 +38,16 @@ __device__ __forceinline__ void repack_tile(uint32_t* tile, const uint16_t* __re
       if (c0 + ch < C && px0 + pv * 8 < HW) q = *reinterpret_cast<const uint4*>(s + size_t(ch) * HW + pv * 8);
       uint32_t* d = &tile[ch * kLdWords + pv * 4];
       d[0] = q.x; d[1] = q.y; d[2] = q.z; d[3] = q.w;
+    }
+  } else if (LOAD == 2) {
+    // 64 channels x 32 pixel pairs; a pair never straddles HW because HW is even, and every row starts 4-byte aligned
+    const int pp = t & 31;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int ch = (t >> 5) + i * 8;
+      uint32_t v = 0;
+      if (c0 + ch < C && px0 + 2 * pp < HW) v = *reinterpret_cast<const uint32_t*>(s + size_t(ch) * HW + 2 * pp);
+      tile[ch * kLdWords + pp] = v;
     }
   } else {
     uint16_t* tile16 = reinterpret_cast<uint16_t*>(tile);
@@ -107,7 +119,8 @@ __device__ __forceinline__ void repack_small_hw(uint16_t* slab, const uint16_t* 
   }
 }
 
-// One repack job: a whole tensor.  mode 0 = tiled with 2-byte loads, 1 = tiled with 128-bit loads, 2 = small-HW slab.
+// One repack job: a whole tensor.  mode 0 = tiled with 2-byte loads, 1 = tiled with 128-bit loads, 2 = small-HW slab,
+// 3 = tiled with 32-bit loads.
 struct RepackJob {
   const uint16_t* src;
   uint16_t* dst;
@@ -133,8 +146,9 @@ __global__ void __launch_bounds__(256) repack_jobs_kernel(const RepackJob a, con
   const int c_tile = int(id % unsigned(j.c_tiles));
   const int bi = int(id / unsigned(j.c_tiles));
   if (j.mode == 2) repack_small_hw(reinterpret_cast<uint16_t*>(smem), j.src, j.dst, j.C, j.HW, j.Cp, j.span, c_tile, bi);
-  else if (j.mode == 1) repack_tile<true>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
-  else repack_tile<false>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
+  else if (j.mode == 1) repack_tile<1>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
+  else if (j.mode == 3) repack_tile<2>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
+  else repack_tile<0>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
 }
 
 // ---- row gather for convolutions with very few input channels ------------------------------------------------------
@@ -232,7 +246,8 @@ RepackJob make_job(const void* src, void* dst, int batch, int channels, int hw, 
     if (j.span > ((c_padded + kTile - 1) / kTile) * kTile) j.span = ((c_padded + kTile - 1) / kTile) * kTile;
     j.c_tiles = (c_padded + j.span - 1) / j.span;
   } else {
-    j.mode = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (hw & 7) == 0) ? 1 : 0;
+    j.mode = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (hw & 7) == 0) ? 1
+             : (((reinterpret_cast<uintptr_t>(src) & 3u) == 0 && (hw & 1) == 0) ? 3 : 0);
     j.hw_tiles = (hw + kTile - 1) / kTile;
   }
   j.blocks = 0;
