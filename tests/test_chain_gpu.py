@@ -94,7 +94,7 @@ def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed, layout="nch
 
 def test_chain_small_images_batch2_fp16(pkg, orc, oracle):
     worst, nodes = _run_chain_case(pkg, orc, oracle, batch=2, image=64, precision=orc.FP16, seed=0)
-    assert nodes >= 53 * 2 + 17
+    assert nodes >= 53 + 17 + 17  # every convolution, pool and add; a repack launch only where a tensor must be rearranged
 
 
 def test_chain_channel_contiguous_fused_residual_fp16(pkg, orc, oracle):
