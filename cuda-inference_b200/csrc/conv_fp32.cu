@@ -22,6 +22,7 @@ struct Fp32Args {
   int batch, c, h, wd, o, r, s, stride_h, stride_w, pad_h, pad_w, out_h, out_w, relu;
   int pixels;  // batch * out_h * out_w
   int k;       // c * r * s
+  FastDiv fd_rs, fd_s, fd_pq, fd_out_w;  // multiply-high reciprocals of r*s, s, out_h*out_w, out_w
 };
 
 // KG = number of thread groups that split the reduction inside one CTA (slab s goes to group s % KG); their partial
@@ -52,8 +53,8 @@ conv_fp32_kernel(const Fp32Args a) {
   int ih0 = 0, iw0 = 0;
   const float* xb = a.x;
   if (lp_ok) {
-    const int b = lpix / pq, rem = lpix - b * pq;
-    const int oh = rem / a.out_w, ow = rem - oh * a.out_w;
+    const int b = a.fd_pq.div(lpix), rem = lpix - b * pq;
+    const int oh = a.fd_out_w.div(rem), ow = rem - oh * a.out_w;
     ih0 = oh * a.stride_h - a.pad_h;
     iw0 = ow * a.stride_w - a.pad_w;
     xb = a.x + size_t(b) * a.c * a.h * a.wd;
@@ -69,8 +70,8 @@ conv_fp32_kernel(const Fp32Args a) {
       const int k = k0 + kk;
       float v = 0.f;
       if (lp_ok && k < a.k) {
-        const int c = k / rs, q = k - c * rs;
-        const int r = q / a.s, s = q - r * a.s;
+        const int c = a.fd_rs.div(k), q = k - c * rs;
+        const int r = a.fd_s.div(q), s = q - r * a.s;
         const int ih = ih0 + r, iw = iw0 + s;
         if (ih >= 0 && ih < a.h && iw >= 0 && iw < a.wd) v = __ldg(xb + (size_t(c) * a.h + ih) * a.wd + iw);
       }
@@ -145,7 +146,7 @@ conv_fp32_kernel(const Fp32Args a) {
     for (int i = 0; i < 4; ++i) {
       const int pix = pix0 + tx * 4 + i;
       if (pix >= a.pixels) continue;
-      const int b = pix / pq, rem = pix - b * pq;
+      const int b = a.fd_pq.div(pix), rem = pix - b * pq;
       float v = acc[i][j] + bv;
       if (a.relu) v = fmaxf(v, 0.f);
       a.y[(size_t(b) * a.o + oc) * pq + rem] = v;
@@ -179,6 +180,10 @@ cudaError_t conv_fp32_launch(const void* x, const void* w, const void* bias, voi
   a.out_h = out_h; a.out_w = out_w; a.relu = relu;
   a.pixels = batch * out_h * out_w;
   a.k = c * r * s;
+  a.fd_rs = FastDiv::make(r * s);
+  a.fd_s = FastDiv::make(s);
+  a.fd_pq = FastDiv::make(out_h * out_w);
+  a.fd_out_w = FastDiv::make(out_w);
   if (use_small_tile(a.pixels, o)) {
     dim3 grid(unsigned((a.pixels + 31) / 32), unsigned((o + 31) / 32));
     conv_fp32_kernel<32, 32, 4><<<grid, 256, 0, stream>>>(a);
