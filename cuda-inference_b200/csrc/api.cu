@@ -111,6 +111,7 @@ struct Resolved {
   int c_padded, kb_per_tap, total_kb, kb_per_split;
   int tiles_m, tiles_n;
   size_t smem;
+  int epi_warps;  // 8, or 16 when the CTA has its SM to itself (see conv_tc_kernel)
   size_t ws_x, ws_w, ws_part, ws_total;  // workspace layout (bytes; offsets are cumulative in this order)
 };
 
@@ -366,6 +367,9 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   r->stages = stages;
   r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, r->tma_epilogue != 0);
   if (r->smem > kMaxDynamicSmem) return no("configuration needs more shared memory than one CTA may have (227 KiB)");
+  // A CTA that has its SM to itself drains 256-column accumulators with 16 warps instead of 8 (measured: 2-7 % per
+  // step on 128x256 tiles; 128-column tiles have only one chunk per warp left and lose more to the wider CTA).
+  r->epi_warps = (r->tile_n >= 256 && resident_ctas(r->tile_m, r->tile_n, r->smem) == 1) ? 16 : 8;
 
   // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
   // src/kernels/tensor_core_mma.cu:265-278)
@@ -403,7 +407,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
     out->launches = 1;
   } else {
     out->dynamic_smem_bytes = uint32_t(r.smem);
-    out->threads_per_block = kTcThreads;
+    out->threads_per_block = conv_tc_threads(r.epi_warps);
     out->num_blocks = int64_t(r.tiles_m) * r.tiles_n * r.split_k;
     // repack (activations and weights in one launch; none when both are consumed in place), convolution, reduction
     const bool x_in_place = r.variant == 2 || (d.flags & GIEB_FLAG_INPUT_NHWC);
@@ -661,7 +665,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
       p.res_tma = 1;
     }
   }
-  GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
+  GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
   if (r.reduce == 1)
     GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_tf32 ? 2 : p.is_bf16, residual,
@@ -737,7 +741,7 @@ int gieb_conv_plan_create(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, 
       cudaStreamDestroy(s);
     }
   }
-  if (e == cudaSuccess && r.variant != 3) e = conv_tc_prepare(r.tile_m, r.tile_n, r.tile_k, kMaxDynamicSmem);
+  if (e == cudaSuccess && r.variant != 3) e = conv_tc_prepare(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, kMaxDynamicSmem);
   if (e != cudaSuccess) {
     if (pl->d_status) cudaFree(pl->d_status);
     delete pl;
@@ -870,7 +874,7 @@ int gieb_conv_forward_static(const gieb_conv_desc* desc, const gieb_conv_cfg* cf
   GIEB_CUDA(cudaGetDevice(&pl.device));
   pl.d_status = reinterpret_cast<uint32_t*>(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (pl.r.variant != 3) GIEB_CUDA(conv_tc_prepare(pl.r.tile_m, pl.r.tile_n, pl.r.tile_k, kMaxDynamicSmem));
+  if (pl.r.variant != 3) GIEB_CUDA(conv_tc_prepare(pl.r.tile_m, pl.r.tile_n, pl.r.tile_k, pl.r.epi_warps, kMaxDynamicSmem));
   // The array keeps whatever the previous call left: the status word must start at zero.  Everything else in the
   // scratch is fully rewritten by the repack kernels (padding channels included) and the split-K slices before use.
   GIEB_CUDA(cudaMemsetAsync(base, 0, kStaticScratchHeader, s));

@@ -196,8 +196,11 @@ __device__ __forceinline__ void with_output_type(const ConvTcParams& p, F&& f) {
 // loads and MMAs of tile t+1.
 // MH = number of 128-pixel halves per tile (1 or 2).  With MH = 2 the tile is 256 pixels: two activation loads and two
 // accumulators share every weight tile, which halves the weight traffic per FLOP.
-template <int BN, int BK, int MH>
-__global__ void __launch_bounds__(kTcThreads, 2)  // at most 80 registers: two CTAs of 12 warps fit the register file
+// EW = number of epilogue warps, 8 or 16.  The epilogue is a long dependent instruction stream per warp (TMEM load ->
+// bias -> ReLU -> rounding -> store, ~1100 cycles per 32-column chunk even with a warp alone on its scheduler), so
+// CTAs that own an SM anyway (ring too large for two) run 16 epilogue warps: four per TMEM lane quarter.
+template <int BN, int BK, int MH, int EW>
+__global__ void __launch_bounds__(32 * (kProducerWarps + 1 + EW), EW == 16 ? 1 : 2)  // EW = 8: at most 80 registers, two CTAs per SM
 conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_wgt,
                const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res, const ConvTcParams p) {
   constexpr int ROW_BYTES = BK * 2;
@@ -206,6 +209,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   constexpr uint32_t B_BYTES = BN * ROW_BYTES;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int MMAS_PER_SLAB = BK / 16;
+  constexpr bool PAIR_SLABS = BN <= 128;                       // narrow MMAs are issue-bound: see the MMA role
   constexpr uint32_t ACC_COLS = MH * BN;                       // columns of one accumulator set
   constexpr int ACC_BUFS = ACC_COLS <= 256 ? 2 : 1;            // double-buffer when it fits
   constexpr uint32_t TMEM_COLS = ACC_COLS * ACC_BUFS < 32 ? 32 : ACC_COLS * ACC_BUFS;
@@ -218,9 +222,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* acc_full = empty_bar + kMaxStages;     // [2] MMA -> epilogue: accumulator complete
   uint64_t* acc_empty = acc_full + 2;              // [2] epilogue -> MMA: accumulator drained
-  constexpr int kEpiBufs = BN >= 64 ? BN / 64 : 1;  // 32-column chunks one epilogue warp owns per 128-pixel half
-  uint64_t* res_bar = acc_empty + 2;               // [8 epilogue warps][kEpiBufs] residual tile landed (TMA epilogue only)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + 8 * kEpiBufs);
+  constexpr int EG = EW / 4;                        // epilogue warps per TMEM lane quarter
+  constexpr int kEpiBufs = (BN / 32 + EG - 1) / EG;  // 32-column chunks one epilogue warp owns per 128-pixel half
+  uint64_t* res_bar = acc_empty + 2;               // [EW epilogue warps][kEpiBufs] residual tile landed (TMA epilogue only)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + EW * kEpiBufs);
   uint8_t* stage_base = smem + kCtrlBytes;
   // TMA epilogue staging: per epilogue warp kEpiBufs boxes of 32 pixels x 32 channels (2 KiB, 64-byte swizzle)
   uint8_t* epi_base = stage_base + size_t(p.stages) * STAGE_BYTES;
@@ -242,9 +247,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&acc_full[b], 1);
-      ptx::mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+      ptx::mbar_init(&acc_empty[b], EW);  // one arrival per epilogue warp
     }
-    for (int b = 0; b < 8 * kEpiBufs; ++b) ptx::mbar_init(&res_bar[b], 1);
+    for (int b = 0; b < EW * kEpiBufs; ++b) ptx::mbar_init(&res_bar[b], 1);
     ptx::fence_mbar_init();
   }
   if (warp == kProducerWarps) {
@@ -395,32 +400,45 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       // kind are compile-time inside it, so the elected lane's issue sequence carries no branch per instruction.
       auto slab_loop = [&](auto form_tag) {
         constexpr int FORM = decltype(form_tag)::value;  // 0: kind::f16, K-major A; 1: kind::f16, pixel-major A; 2: kind::tf32
-        for (int i = 0; i < num_kb; ++i) {
-          const bool ok = ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout);
-          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-          ptx::tc_fence_after_sync();
-          const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(s) * STAGE_BYTES);
+        // one slab's MMAs and the commit that frees its ring slot (elected lane only)
+        auto issue_slab = [&](int slot, bool first) {
+          const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(slot) * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
-          if (ptx::elect_one()) {
 #pragma unroll
-            for (int h = 0; h < MH; ++h) {
-              if (h < halves) {
+          for (int h = 0; h < MH; ++h) {
+            if (h < halves) {
 #pragma unroll
-                for (int k = 0; k < MMAS_PER_SLAB; ++k) {
-                  // K-major A: one MMA's K extent (16 two-byte or 8 four-byte values) = 32 bytes along a row.
-                  // Pixel-major A (form 1): 16 channels = 16 rows of 128 B.
-                  const uint64_t adesc = FORM == 1 ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
-                                                   : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
-                  const uint64_t bdesc = ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32);
-                  if constexpr (FORM == 2) ptx::mma_tf32_ss(acc + h * BN, adesc, bdesc, p.idesc, (i | k) != 0);
-                  else ptx::mma_f16_ss(acc + h * BN, adesc, bdesc, p.idesc, (i | k) != 0);
-                }
+              for (int k = 0; k < MMAS_PER_SLAB; ++k) {
+                // K-major A: one MMA's K extent (16 two-byte or 8 four-byte values) = 32 bytes along a row.
+                // Pixel-major A (form 1): 16 channels = 16 rows of 128 B.
+                const uint64_t adesc = FORM == 1 ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
+                                                 : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
+                const uint64_t bdesc = ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32);
+                if constexpr (FORM == 2) ptx::mma_tf32_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
+                else ptx::mma_f16_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
               }
             }
-            ptx::mma_commit(&empty_bar[s]);  // frees the slot once these MMAs have read it
+          }
+          ptx::mma_commit(&empty_bar[slot]);  // frees the slot once these MMAs have read it
+        };
+        for (int i = 0; i < num_kb;) {
+          const bool ok = ptx::mbar_wait(&full_bar[s], phase, p.status, kStatusMmaTimeout);
+          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+          // When the next slab has landed as well (the issue, not the feed, is the bottleneck), both go out in one
+          // elected block: the wait / vote / fence sequence between slabs costs as much as three MMA issues.
+          const int s2 = s + 1 == stages ? 0 : s + 1;
+          const uint32_t phase2 = s + 1 == stages ? phase ^ 1u : phase;
+          const bool two = PAIR_SLABS && i + 1 < num_kb && __all_sync(0xffffffffu, ptx::mbar_try_wait(&full_bar[s2], phase2));
+          ptx::tc_fence_after_sync();
+          if (ptx::elect_one()) {
+            issue_slab(s, i == 0);
+            if (two) issue_slab(s2, false);
           }
           __syncwarp();
-          if (++s == stages) { s = 0; phase ^= 1u; }
+          const int adv = two ? 2 : 1;
+          i += adv;
+          s += adv;
+          if (s >= stages) { s -= stages; phase ^= 1u; }
         }
       };
       if (p.is_tf32) slab_loop(std::integral_constant<int, 2>{});
@@ -438,9 +456,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     // ---------------- epilogue: 8 warps.  Warp w may read TMEM lanes 32*(w%4)..+31; warps 4..7 take the even
     // 32-column chunks of a tile, warps 8..11 the odd ones (two warps per scheduler hide each other's latencies).
     const int quad = warp & 3;
-    const int par = (warp - kProducerWarps - 1) >> 2;  // 0 or 1: which chunks this warp owns
-    const int et = threadIdx.x - 32 * (kProducerWarps + 1);  // 0..255 among the epilogue threads
-    const int we = warp - kProducerWarps - 1;                // 0..7 among the epilogue warps
+    const int par = (warp - kProducerWarps - 1) >> 2;  // 0 .. EG-1: which chunks this warp owns
+    const int et = threadIdx.x - 32 * (kProducerWarps + 1);  // index among the epilogue threads
+    const int we = warp - kProducerWarps - 1;                // index among the epilogue warps
     uint32_t res_phase = 0;                                  // bit k: parity of this warp's residual barrier k (TMA epilogue)
     // GEMM row -> (image, pixel within the image, row holds an output pixel at all)
     auto decode_row = [&](int m, bool& m_ok, int& img, int& pix) {
@@ -477,7 +495,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 
       join_setup();
       // stage this tile's bias as float (two buffers: a fast warp may already be one tile ahead of a slow one)
-      for (int i = et; i < BN; i += 256) {
+      for (int i = et; i < BN; i += 32 * EW) {
         const int oc = n0 + i;
         float b = 0.f;
         if (p.has_bias && p.partial == nullptr && oc < p.out_channels) {
@@ -487,7 +505,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         }
         bias_t[i] = b;
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");  // epilogue warps only
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");  // epilogue warps only
 
       // TMA epilogue (channel-contiguous output): this warp's chunk c of half h is staged in its own 2 KiB box and
       // leaves as one TMA store; with a residual, TMA first loads the residual box into the same place, issued here
@@ -498,7 +516,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         __syncwarp();
         if (p.res_tma && lane == 0) {
           for (int k = 0; k < kEpiBufs; ++k) {
-            const int chunk = par + 2 * k;
+            const int chunk = par + EG * k;
             if (chunk >= BN / 32 || n0 + chunk * 32 >= p.out_channels) break;
             ptx::mbar_arrive_expect_tx(&res_bar[we * kEpiBufs + k], 2048);
             ptx::tma_load_2d(stage_box(k), &tm_res, &res_bar[we * kEpiBufs + k], n0 + chunk * 32, m0 + h * kTileM + quad * 32);
@@ -531,7 +549,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         const int row = quad * 32 + lane;
         const uint32_t recv = ptx::smem_u32(stage_base);
         ptx::cluster_sync_all();  // every CTA of the cluster has finished its MMAs: all rings are idle
-        for (int chunk = par; chunk < BN / 32; chunk += 2) {
+        for (int chunk = par; chunk < BN / 32; chunk += EG) {
           if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform, same in every CTA of the cluster
           const int owner = chunk / cpr;
           if (owner == rank) continue;
@@ -553,7 +571,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         const int64_t cstride = p.out_nhwc ? 1 : p.pq;
         const int64_t base = p.out_nhwc ? (int64_t(img) * p.pq + pix) * p.out_channels + n0
                                         : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
-        for (int chunk = par; chunk < BN / 32; chunk += 2) {
+        for (int chunk = par; chunk < BN / 32; chunk += EG) {
           if (n0 + chunk * 32 >= p.out_channels) break;
           if (chunk / cpr != rank) continue;
           uint32_t v[32];
@@ -598,13 +616,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
                                         : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
         if (p.out_tma && h > 0) prefetch_residual(h);
 #pragma unroll 1
-        for (int chunk = par; chunk < BN / 32; chunk += 2) {
+        for (int chunk = par; chunk < BN / 32; chunk += EG) {
           if (n0 + chunk * 32 >= p.out_channels) break;  // warp-uniform
           uint32_t v[32];
           ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(h * BN + chunk * 32), v);
           ptx::tmem_ld_wait();
           if (p.out_tma) {
-            const int k = chunk >> 1;
+            const int k = chunk / EG;
             uint8_t* box = stage_box(k);
             bool landed = true;
             if (p.res_tma) {
@@ -662,46 +680,58 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   }
 }
 
-template <int BN, int BK, int MH>
+template <int BN, int BK, int MH, int EW>
 cudaError_t prepare_one(size_t smem_bytes) {
-  return cudaFuncSetAttribute(conv_tc_kernel<BN, BK, MH>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
+  return cudaFuncSetAttribute(conv_tc_kernel<BN, BK, MH, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes));
 }
 
-template <int BN, int BK, int MH>
+template <int BN, int BK, int MH, int EW>
 cudaError_t launch_one(const CUtensorMap& ta, const CUtensorMap& tw, const CUtensorMap& to, const CUtensorMap& tr, const ConvTcParams& p,
                        dim3 grid, size_t smem, cudaStream_t st) {
-  cudaError_t e = launch_pdl_cluster(conv_tc_kernel<BN, BK, MH>, grid, dim3(kTcThreads), smem, st,
+  cudaError_t e = launch_pdl_cluster(conv_tc_kernel<BN, BK, MH, EW>, grid, dim3(32 * (kProducerWarps + 1 + EW)), smem, st,
                                      unsigned(p.cluster_split > 1 ? p.cluster_split : 1), ta, tw, to, tr, p);
   if (e != cudaSuccess) return e;
   return cudaGetLastError();
 }
 
-#define GIEB_TC_DISPATCH(FN, ...)                                                     \
-  switch (tile_m / 128 * 100000 + tile_n * 100 + tile_k) {                            \
-    case 1 * 100000 + 32 * 100 + 16: return FN<32, 16, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 32 * 100 + 16: return FN<32, 16, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 32 * 100 + 32: return FN<32, 32, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 32 * 100 + 32: return FN<32, 32, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 32 * 100 + 64: return FN<32, 64, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 32 * 100 + 64: return FN<32, 64, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 64 * 100 + 16: return FN<64, 16, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 64 * 100 + 16: return FN<64, 16, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 64 * 100 + 32: return FN<64, 32, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 64 * 100 + 32: return FN<64, 32, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 64 * 100 + 64: return FN<64, 64, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 64 * 100 + 64: return FN<64, 64, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 128 * 100 + 16: return FN<128, 16, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 128 * 100 + 16: return FN<128, 16, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 128 * 100 + 32: return FN<128, 32, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 128 * 100 + 32: return FN<128, 32, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 128 * 100 + 64: return FN<128, 64, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 128 * 100 + 64: return FN<128, 64, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 256 * 100 + 16: return FN<256, 16, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 256 * 100 + 16: return FN<256, 16, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 256 * 100 + 32: return FN<256, 32, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 256 * 100 + 32: return FN<256, 32, 2>(__VA_ARGS__);                \
-    case 1 * 100000 + 256 * 100 + 64: return FN<256, 64, 1>(__VA_ARGS__);                \
-    case 2 * 100000 + 256 * 100 + 64: return FN<256, 64, 2>(__VA_ARGS__);                \
+#define GIEB_TC_DISPATCH(FN, ...) \
+  switch ((epi_warps == 16 ? 1000000 : 0) + tile_m / 128 * 100000 + tile_n * 100 + tile_k) { \
+    case 0 + 1 * 100000 + 32 * 100 + 16: return FN<32, 16, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 32 * 100 + 16: return FN<32, 16, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 32 * 100 + 32: return FN<32, 32, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 32 * 100 + 32: return FN<32, 32, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 32 * 100 + 64: return FN<32, 64, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 32 * 100 + 64: return FN<32, 64, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 64 * 100 + 16: return FN<64, 16, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 64 * 100 + 16: return FN<64, 16, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 64 * 100 + 32: return FN<64, 32, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 64 * 100 + 32: return FN<64, 32, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 64 * 100 + 64: return FN<64, 64, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 64 * 100 + 64: return FN<64, 64, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 128 * 100 + 16: return FN<128, 16, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 128 * 100 + 16: return FN<128, 16, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 128 * 100 + 32: return FN<128, 32, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 128 * 100 + 32: return FN<128, 32, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 128 * 100 + 64: return FN<128, 64, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 128 * 100 + 64: return FN<128, 64, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 256 * 100 + 16: return FN<256, 16, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 256 * 100 + 16: return FN<256, 16, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 256 * 100 + 32: return FN<256, 32, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 256 * 100 + 32: return FN<256, 32, 2, 8>(__VA_ARGS__); \
+    case 0 + 1 * 100000 + 256 * 100 + 64: return FN<256, 64, 1, 8>(__VA_ARGS__); \
+    case 0 + 2 * 100000 + 256 * 100 + 64: return FN<256, 64, 2, 8>(__VA_ARGS__); \
+    case 1000000 + 1 * 100000 + 128 * 100 + 16: return FN<128, 16, 1, 16>(__VA_ARGS__); \
+    case 1000000 + 2 * 100000 + 128 * 100 + 16: return FN<128, 16, 2, 16>(__VA_ARGS__); \
+    case 1000000 + 1 * 100000 + 128 * 100 + 32: return FN<128, 32, 1, 16>(__VA_ARGS__); \
+    case 1000000 + 2 * 100000 + 128 * 100 + 32: return FN<128, 32, 2, 16>(__VA_ARGS__); \
+    case 1000000 + 1 * 100000 + 128 * 100 + 64: return FN<128, 64, 1, 16>(__VA_ARGS__); \
+    case 1000000 + 2 * 100000 + 128 * 100 + 64: return FN<128, 64, 2, 16>(__VA_ARGS__); \
+    case 1000000 + 1 * 100000 + 256 * 100 + 16: return FN<256, 16, 1, 16>(__VA_ARGS__); \
+    case 1000000 + 2 * 100000 + 256 * 100 + 16: return FN<256, 16, 2, 16>(__VA_ARGS__); \
+    case 1000000 + 1 * 100000 + 256 * 100 + 32: return FN<256, 32, 1, 16>(__VA_ARGS__); \
+    case 1000000 + 2 * 100000 + 256 * 100 + 32: return FN<256, 32, 2, 16>(__VA_ARGS__); \
+    case 1000000 + 1 * 100000 + 256 * 100 + 64: return FN<256, 64, 1, 16>(__VA_ARGS__); \
+    case 1000000 + 2 * 100000 + 256 * 100 + 64: return FN<256, 64, 2, 16>(__VA_ARGS__); \
     default: return cudaErrorInvalidValue;                                            \
   }
 
@@ -782,17 +812,20 @@ splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t tota
 
 }  // namespace
 
+// 8 epilogue warps x ceil(chunks / 2) boxes = 16 warps x ceil(chunks / 4) boxes for the tile widths that may run 16 warps
 size_t conv_tc_epilogue_staging_bytes(int tile_n) { return size_t(8) * (tile_n >= 64 ? tile_n / 64 : 1) * 2048; }
+
+int conv_tc_threads(int epi_warps) { return 32 * (kProducerWarps + 1 + epi_warps); }
 
 size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, bool tma_epilogue) {
   return 1024 + kCtrlBytes + size_t(stages) * (size_t(tile_m) + tile_n) * tile_k * 2 + (tma_epilogue ? conv_tc_epilogue_staging_bytes(tile_n) : 0);
 }
 
-cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, size_t smem_bytes) {
+cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, int epi_warps, size_t smem_bytes) {
   GIEB_TC_DISPATCH(prepare_one, smem_bytes)
 }
 
-cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
+cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, int epi_warps, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
                            const CUtensorMap& tm_out, const CUtensorMap& tm_res, const ConvTcParams& p, dim3 grid, size_t smem_bytes,
                            cudaStream_t stream) {
   GIEB_TC_DISPATCH(launch_one, tm_act, tm_wgt, tm_out, tm_res, p, grid, smem_bytes, stream)

@@ -18,7 +18,7 @@ enum : uint32_t {
 constexpr int kTileM = 128;        // output pixels per CTA tile = TMEM lanes = UMMA M
 constexpr int kMaxStages = 8;
 constexpr int kProducerWarps = 3;  // warps 0..2 issue the TMA loads, slab by slab in turn
-constexpr int kTcThreads = 384;    // + warp 3: MMA issuer and TMEM owner, warps 4..11: epilogue
+constexpr int kTcThreads = 384;    // + warp 3: MMA issuer and TMEM owner, warps 4..11: epilogue (4..19 with 16 epilogue warps)
 static_assert((kProducerWarps + 1) % 4 == 0, "epilogue warp w must sit on TMEM lane quarter w % 4");
 
 // Division by a run-time constant as multiply-high + shift (round-up reciprocal method): exact for 0 <= n < 2^31 and
@@ -139,10 +139,12 @@ struct ConvTcParams {
 // tma_epilogue: add the staging boxes of the TMA-store epilogue (channel-contiguous output).
 size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, bool tma_epilogue);
 size_t conv_tc_epilogue_staging_bytes(int tile_n);
-cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, size_t smem_bytes);  // opt in to large dynamic shared memory
+// epi_warps: 8, or 16 for CTAs that have an SM to themselves (tile_n >= 128 only)
+int conv_tc_threads(int epi_warps);
+cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, int epi_warps, size_t smem_bytes);  // opt in to large dynamic shared memory
 // tm_out / tm_res: the output and the residual as 2-D tensors {channels, pixels} with a 32 x 32 box and 64-byte swizzle;
 // read only when p.out_tma / p.res_tma are set.
-cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
+cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, int epi_warps, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
                            const CUtensorMap& tm_out, const CUtensorMap& tm_res, const ConvTcParams& p, dim3 grid, size_t smem_bytes,
                            cudaStream_t stream);
 
