@@ -168,7 +168,8 @@ bool cluster_reduce_ok(int tile_m, int tile_n, int tile_k, int stages, int split
 }
 
 // Cost model in SM cycles, fitted to per-CTA clock stamps of the kernel on B200:
-//  * a converged issuer needs >= 78 cycles per tcgen05.mma plus ~215 per slab for the commit and the barrier wait;
+//  * a converged issuer needs >= 78 cycles per tcgen05.mma plus ~215 per wait / vote / fence / commit round (one round
+//    per slab, or per two slabs of a narrow tile when they have queued up);
 //    256-column instructions (128 pipe cycles each) hide all of that behind the tensor pipe;
 //  * with every SM busy, L2 delivers ~74 B/clk of operands to each SM;
 //  * CTAs that share an SM interleave their issue latencies but share pipe and feed;
@@ -188,7 +189,7 @@ double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, i
   const double sharing = fmin(double(resident), tiles_per_sm);   // CTAs that really run side by side on an SM
   const double mmas = double(mh) * (tile_k / 16);
   const double pipe = mmas * (tile_n / 2.0);
-  const double issue = tile_n >= 256 ? pipe : mmas * 78.0 + 215.0;
+  const double issue = tile_n >= 256 ? pipe : mmas * 78.0 + 110.0;  // narrow tiles: two slabs per wait / vote / fence when they queue up
   const double feed = double(stage_bytes_of(tile_m, tile_n, tile_k)) / 74.0;
   const double slab = fmax(fmax(pipe, feed), issue / sharing);
   double epilogue = 500.0 + 16.0 * mh * tile_n;
@@ -196,8 +197,8 @@ double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, i
   const bool overlapped = sharing >= 2.0 || (mh * tile_n <= 256 && tiles_per_sm >= 2.0);
   double total = 4500.0 + tiles_per_sm * kb_per_split * slab + (overlapped ? epilogue : tiles_per_sm * epilogue);
   if (real_split > 1) {
-    if (reduce == 2)  // two cluster barriers + pushing all but the own share of the FP32 tile at ~24 B/clk
-      total += 2000.0 + double(real_split - 1) / real_split * (double(kTileM) * tile_n * 4.0) / 24.0;
+    if (reduce == 2)  // two cluster barriers + pushing all but the own share of the FP32 tile at ~16 B/clk
+      total += 2000.0 + double(real_split - 1) / real_split * (double(kTileM) * tile_n * 4.0) / 16.0;
     else total += 6000.0 + 2.0 * real_split * double(g.y_elems) * 4.0 / 1500.0;      // extra launch + partial traffic
   }
   return total;
@@ -367,9 +368,6 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   r->stages = stages;
   r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, r->tma_epilogue != 0);
   if (r->smem > kMaxDynamicSmem) return no("configuration needs more shared memory than one CTA may have (227 KiB)");
-  // A CTA that has its SM to itself drains 256-column accumulators with 16 warps instead of 8 (measured: 2-7 % per
-  // step on 128x256 tiles; 128-column tiles have only one chunk per warp left and lose more to the wider CTA).
-  r->epi_warps = (r->tile_n >= 256 && resident_ctas(r->tile_m, r->tile_n, r->smem) == 1) ? 16 : 8;
 
   // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
   // src/kernels/tensor_core_mma.cu:265-278)
@@ -378,6 +376,14 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   // how the split-K slices are summed
   if (c.reduce < 0 || c.reduce > 2) return no("reduce must be 0 (auto), 1 (workspace) or 2 (cluster)");
   r->reduce = r->split_k > 1 ? best_mode : 0;
+  // A CTA that has its SM to itself drains its accumulators with 16 warps instead of 8: always for 256-column tiles
+  // (measured 2-7 % per step), for 128-column tiles only when the CTA has a single tile, whose epilogue nothing hides
+  // (with several tiles per CTA the extra polling warps cost more than the last epilogue gains).
+  {
+    const bool alone = resident_ctas(r->tile_m, r->tile_n, r->smem) == 1;
+    const bool single_tile = int64_t(r->tiles_m) * r->tiles_n * r->split_k <= kNumSms;
+    r->epi_warps = (alone && (r->tile_n >= 256 || (r->tile_n >= 128 && single_tile && r->reduce != 2))) ? 16 : 8;
+  }
   if (r->reduce == 2 && !cluster_reduce_ok(r->tile_m, r->tile_n, r->tile_k, stages, r->split_k))
     return no("cluster reduction needs tile_m 128, split_k 2, 4 or 8 dividing tile_n / 32, and a ring that holds the received slices");
   r->ws_part = r->split_k > 1 && r->reduce == 1 ? align256(size_t(r->split_k) * size_t((g.y_elems + 3) & ~int64_t(3)) * 4) : 0;
@@ -411,7 +417,8 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
     out->num_blocks = int64_t(r.tiles_m) * r.tiles_n * r.split_k;
     // repack (activations and weights in one launch; none when both are consumed in place), convolution, reduction
     const bool x_in_place = r.variant == 2 || (d.flags & GIEB_FLAG_INPUT_NHWC);
-    const bool w_in_place = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) != 0;
+    const bool w_in_place = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) != 0 ||
+                            (x_in_place && d.precision != GIEB_TF32 && d.kernel_h * d.kernel_w == 1 && r.c_padded == d.in_channels);  // 16-byte aligned w assumed
     out->launches = (x_in_place && w_in_place ? 0 : 1) + 1 + (r.reduce == 1 ? 1 : 0) + (d.precision == GIEB_TF32 ? 1 : 0);  // TF32: X and W repacked by two launches
   }
 }
@@ -585,6 +592,12 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
     xn = const_cast<void*>(x);
   }
   const int64_t rows = mode == 2 ? int64_t(d.batch) * r.boxes_per_image * 64 : pl->g.pixels;
+  // 1x1 filters over unpadded channels: OIHW *is* the [O][RS][C] layout, so when no activation repack would share the
+  // launch the weights are read where they lie and the step is the convolution kernel alone (measured on 512 -> 128
+  // channels at 28x28: 16.4 instead of 17.5 us per step).
+  const bool w_direct = (mode == 2 || in_nhwc) && !(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) && d.precision != GIEB_TF32 &&
+                        d.kernel_h * d.kernel_w == 1 && r.c_padded == d.in_channels && reinterpret_cast<uintptr_t>(w) % 16 == 0;
+  if (w_direct) wk = w;
 
   CUtensorMap tm_act, tm_wgt;
   const int st_maps = encode_maps(pl, mode, mode == 2 ? x : xn, wk, &tm_act, &tm_wgt);
@@ -598,7 +611,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
     GIEB_CUDA(gather_rows_launch(x, xn, d.batch, d.in_channels, d.in_h, d.in_w, pl->g.out_w, d.kernel_w, d.stride_w, d.pad_w, r.c_padded,
                                  (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? nullptr : w, const_cast<void*>(wk), d.out_channels, d.kernel_h, st));
   } else if (mode == 2 || in_nhwc) {
-    if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED))
+    if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) && !w_direct)
       GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
   } else if (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)
     GIEB_CUDA(repack_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, st));
