@@ -88,7 +88,7 @@ struct Point {
     k.backend = PREC == int(Precision::kFp32) ? Backend::kImplicitGemm : Backend::kTensorCore;
     k.version = kLibraryVersion;
     k.params = {{"tile_pixels", TM}, {"tile_channels", TN}, {"tile_k", TK}, {"stages", ST}, {"split_k", SK}, {"reduce", RD}};
-    k.threads_per_block = PREC == int(Precision::kFp32) ? 256 : 384;
+    k.threads_per_block = PREC == int(Precision::kFp32) ? 256 : 384;  // nominal: a plan whose CTAs own their SM runs 640 (gieb_conv_info reports it)
     k.tile_m = TN ? TN : 128;   // reference orientation: M = output channels
     k.tile_n = TM ? TM : 128;   //                        N = output pixels
     k.tile_k = TK ? TK : 64;
