@@ -232,6 +232,78 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const GatherJob j) {
   }
 }
 
+// Whole-row variant for the common case (Q <= kGatherRows, W % 8 == 0, 16-byte aligned x, pad_w <= 8, c2 = 32 so that
+// a thread keeps one 8-channel group): a block takes kFastRows consecutive input rows of one image.  The rows are read
+// with 16-byte loads into shared memory at column offset 8 (zero margins stand in for the padding), every thread
+// keeps the eight strip offsets of its channel group in registers, and the block's output
+// X2[n][h0 .. h0+kFastRows)[0 .. Q)[c2] is one contiguous run written with 16-byte stores.
+constexpr int kFastRows = 4;
+__global__ void __launch_bounds__(256) gather_rows_fast_kernel(const GatherJob j, int sw) {
+  extern __shared__ __align__(16) uint8_t gsm[];
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
+  if (blockIdx.x >= j.x_blocks) {  // weights: one thread per (o, r, e)
+    const int64_t total = int64_t(j.O) * j.R * j.c2;
+    for (int64_t i = int64_t(blockIdx.x - j.x_blocks) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x - j.x_blocks) * 256) {
+      const int e = int(i % j.c2);
+      const int64_t orr = i / j.c2;
+      const int r = int(orr % j.R), o = int(orr / j.R);
+      uint16_t v = 0;
+      if (e < j.S * j.C) {
+        const int s = e / j.C, c = e - s * j.C;
+        v = j.w[((int64_t(o) * j.C + c) * j.R + r) * j.S + s];
+      }
+      j.w2[i] = v;
+    }
+    return;
+  }
+  const int groups = (j.H + kFastRows - 1) / kFastRows;
+  const int n = int(blockIdx.x / unsigned(groups));
+  const int h0 = int(blockIdx.x % unsigned(groups)) * kFastRows;
+  const int rows = min(kFastRows, j.H - h0);
+  uint16_t* strip = reinterpret_cast<uint16_t*>(gsm);  // [rows][C][sw]; input column w sits at index 8 + w
+  const int vec_w = j.W >> 3;
+  const int64_t plane = int64_t(j.H) * j.W;
+  const uint16_t* x0 = j.x + (int64_t(n) * j.C * j.H + h0) * j.W;
+  for (int i = threadIdx.x; i < rows * j.C * vec_w; i += 256) {
+    const int v = i % vec_w, rc = i / vec_w;
+    const int c = rc % j.C, r = rc / j.C;
+    const uint4 val = __ldg(reinterpret_cast<const uint4*>(x0 + c * plane + int64_t(r) * j.W) + v);
+    *reinterpret_cast<uint4*>(strip + (r * j.C + c) * sw + 8 + v * 8) = val;
+  }
+  const int margin = sw - j.W;  // 8 leading zeros, the rest trailing
+  for (int i = threadIdx.x; i < rows * j.C * margin; i += 256) {
+    const int m = i % margin, rc = i / margin;
+    strip[rc * sw + (m < 8 ? m : j.W + m)] = 0;
+  }
+  // this thread's channel group k = threadIdx.x % 4 never changes (256 % 4 == 0)
+  const int k = threadIdx.x & 3;
+  int off[8];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    const int e = k * 8 + t;
+    const int s = e / j.C, c = e - s * j.C;
+    off[t] = e < j.S * j.C ? c * sw + s + 8 - j.pad_w : -1;
+  }
+  __syncthreads();
+  uint4* dst = reinterpret_cast<uint4*>(j.x2 + ((int64_t(n) * j.H + h0) * j.Q) * j.c2);
+  const int per_row = j.Q * 4;
+  for (int i = threadIdx.x; i < rows * per_row; i += 256) {
+    const int r = i / per_row;
+    const int rl = (i - r * per_row) >> 2;
+    const uint16_t* sp = strip + r * j.C * sw + rl * j.stride_w;
+    uint16_t o[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) o[t] = off[t] >= 0 ? sp[off[t]] : uint16_t(0);
+    uint4 v;
+    v.x = uint32_t(o[0]) | (uint32_t(o[1]) << 16);
+    v.y = uint32_t(o[2]) | (uint32_t(o[3]) << 16);
+    v.z = uint32_t(o[4]) | (uint32_t(o[5]) << 16);
+    v.w = uint32_t(o[6]) | (uint32_t(o[7]) << 16);
+    dst[i] = v;
+  }
+}
+
 RepackJob make_job(const void* src, void* dst, int batch, int channels, int hw, int c_padded) {
   RepackJob j;
   j.src = static_cast<const uint16_t*>(src);
@@ -290,6 +362,19 @@ cudaError_t gather_rows_launch(const void* x, void* x2, int batch, int channels,
   if (wsrc != nullptr) {
     wb = (int64_t(out_channels) * kernel_h * c2 + 255) / 256;
     if (wb > 1024) wb = 1024;
+  }
+  if (x != nullptr && q <= kGatherRows && (w & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && pad_w <= 8 && c2 == 32) {
+    int need = (q - 1) * stride_w + kernel_w + 8 - pad_w;
+    if (need < w + 16) need = w + 16;
+    const int sw = (need + 7) & ~7;
+    const size_t fast_smem = size_t(kFastRows) * channels * sw * 2;
+    const int64_t fb = int64_t(batch) * ((h + kFastRows - 1) / kFastRows);
+    if (fast_smem <= 48 * 1024 && fb + wb <= 2147483647LL) {
+      j.x_blocks = unsigned(fb);
+      const cudaError_t e = launch_pdl(gather_rows_fast_kernel, dim3(unsigned(fb + wb)), dim3(256), fast_smem, stream, j, sw);
+      if (e != cudaSuccess) return e;
+      return cudaGetLastError();
+    }
   }
   if (xb + wb > 2147483647LL || xb + wb == 0) return cudaErrorInvalidValue;
   j.x_blocks = unsigned(xb);

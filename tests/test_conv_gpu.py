@@ -152,6 +152,8 @@ GATHER_CASES = [
     ((2, 4, 18, 18, 48, 5, 5, 1, 1, 2, 2), dict(variant=5, tile_n=64)),  # 5 x 4 = 20 -> 32
     ((2, 8, 16, 20, 96, 3, 5, 2, 1, 1, 2), dict(variant=5, tile_k=16, split_k=2)),   # 5 x 8 = 40 -> 48: three 16-channel slabs per row
     ((1, 3, 64, 64, 32, 7, 7, 2, 2, 3, 3), dict(variant=5, tile_m=256, tile_n=32)),
+    ((2, 3, 30, 40, 64, 7, 7, 2, 2, 3, 3), dict(variant=5)),             # whole-row gather, rows not a multiple of four
+    ((3, 4, 9, 16, 32, 5, 5, 1, 1, 2, 2), dict(variant=5)),              # whole-row gather, stride 1, 20 -> 32 channels
 ]
 
 
