@@ -13,6 +13,7 @@ namespace gieb {
 namespace {
 
 constexpr int kBK = 16;
+constexpr int kLutMax = 2048;  // reduction length up to which the (c, r, s) decode of k is tabulated in shared memory
 
 struct Fp32Args {
   const float* x;
@@ -28,7 +29,10 @@ struct Fp32Args {
 // KG = number of thread groups that split the reduction inside one CTA (slab s goes to group s % KG); their partial
 // accumulators are summed in a fixed order at the end, so results are deterministic.  KG > 1 gives small problems
 // (few CTAs, long dependent slab chains) enough warps per SM to hide global-load latency.
-template <int TP, int TO, int KG>
+// LUT: k -> (offset of (c, r, s) inside one image, r, s) comes from a table built once per CTA (the analogue of
+// build_conv_lut, src/kernels/conv_common.cu:25-37) instead of two divisions per gathered element: the gather is
+// instruction-bound, and the table cuts a load from ~30 to ~10 instructions.
+template <int TP, int TO, int KG, bool LUT>
 __global__ void __launch_bounds__((TP / 4) * (TO / 4) * KG)
 conv_fp32_kernel(const Fp32Args a) {
   constexpr int NT = (TP / 4) * (TO / 4);  // threads per group
@@ -38,6 +42,7 @@ conv_fp32_kernel(const Fp32Args a) {
   __shared__ __align__(16) float tiles[XS_FLOATS + WS_FLOATS];  // operand tiles; reused for the group reduction
   float (*xs)[kBK][TP] = reinterpret_cast<float (*)[kBK][TP]>(tiles);
   float (*ws)[kBK][TO + 4] = reinterpret_cast<float (*)[kBK][TO + 4]>(tiles + XS_FLOATS);
+  __shared__ int2 lut[LUT ? kLutMax : 1];
 
   const int grp = threadIdx.x / NT;
   const int t = threadIdx.x - grp * NT;
@@ -59,6 +64,20 @@ conv_fp32_kernel(const Fp32Args a) {
     iw0 = ow * a.stride_w - a.pad_w;
     xb = a.x + size_t(b) * a.c * a.h * a.wd;
   }
+  const int xoff0 = ih0 * a.wd + iw0;  // offset of tap (0, 0) of this pixel inside a channel plane (may be negative)
+  if (LUT) {
+    const int kend = (a.k + kBK * KG - 1) / (kBK * KG) * (kBK * KG);  // slabs beyond K read zeros
+    for (int k = threadIdx.x; k < kend; k += NT * KG) {
+      int2 e = make_int2(0, 0x7fff0000);  // r far outside every image: never loaded
+      if (k < a.k) {
+        const int c = a.fd_rs.div(k), q = k - c * rs;
+        const int r = a.fd_s.div(q), sx = q - r * a.s;
+        e = make_int2((c * a.h + r) * a.wd + sx, (r << 16) | sx);
+      }
+      lut[k] = e;
+    }
+    __syncthreads();
+  }
   // W: thread owns k offset (t % kBK) and channels (t / kBK) + i * (NT / kBK)  -> coalesced along k.
   const int wk = t % kBK;
 
@@ -69,7 +88,11 @@ conv_fp32_kernel(const Fp32Args a) {
       const int kk = t / TP + i * (NT / TP);
       const int k = k0 + kk;
       float v = 0.f;
-      if (lp_ok && k < a.k) {
+      if (LUT) {
+        const int2 e = lut[k];
+        const int ih = ih0 + (e.y >> 16), iw = iw0 + (e.y & 0xffff);
+        if (lp_ok && unsigned(ih) < unsigned(a.h) && unsigned(iw) < unsigned(a.wd)) v = __ldg(xb + (e.x + xoff0));
+      } else if (lp_ok && k < a.k) {
         const int c = a.fd_rs.div(k), q = k - c * rs;
         const int r = a.fd_s.div(q), s = q - r * a.s;
         const int ih = ih0 + r, iw = iw0 + s;
@@ -184,12 +207,15 @@ cudaError_t conv_fp32_launch(const void* x, const void* w, const void* bias, voi
   a.fd_s = FastDiv::make(s);
   a.fd_pq = FastDiv::make(out_h * out_w);
   a.fd_out_w = FastDiv::make(out_w);
+  const bool lut = (a.k + 63) / 64 * 64 <= kLutMax && int64_t(c) * h * wd < (int64_t(1) << 31) && r < 0x7fff && s <= 0xffff;
   if (use_small_tile(a.pixels, o)) {
     dim3 grid(unsigned((a.pixels + 31) / 32), unsigned((o + 31) / 32));
-    conv_fp32_kernel<32, 32, 4><<<grid, 256, 0, stream>>>(a);
+    if (lut) conv_fp32_kernel<32, 32, 4, true><<<grid, 256, 0, stream>>>(a);
+    else conv_fp32_kernel<32, 32, 4, false><<<grid, 256, 0, stream>>>(a);
   } else {
     dim3 grid(unsigned((a.pixels + 63) / 64), unsigned((o + 63) / 64));
-    conv_fp32_kernel<64, 64, 1><<<grid, 256, 0, stream>>>(a);
+    if (lut) conv_fp32_kernel<64, 64, 1, true><<<grid, 256, 0, stream>>>(a);
+    else conv_fp32_kernel<64, 64, 1, false><<<grid, 256, 0, stream>>>(a);
   }
   return cudaGetLastError();
 }
