@@ -248,6 +248,25 @@ def test_misaligned_tensor_pointers(pkg, orc, oracle):
         _check(oracle, p, got, ref, scale, f"misaligned prec={prec}")
 
 
+@pytest.mark.parametrize("woff", [0, 1, 8])
+def test_pointwise_weights_in_place_and_fallback(pkg, orc, oracle, woff):
+    """1x1 filters over unpadded channels are read where the caller keeps them when the pointer is 16-byte aligned
+    (one launch); a pointer that is not takes the prepack launch.  Both must give the oracle's values, on the
+    direct-NCHW route and with a channel-contiguous input."""
+    for flags_name in ("nchw", "nhwc_in"):
+        p = orc.Problem.P(3, 64, 8, 16, 96, 1, 1, 1, 1, 0, 0, orc.FP16, True, True)
+        x, w, b = oracle.make_conv_data(p, 77 + woff)
+        ref, scale = oracle.conv2d(p, x, w, b)
+        flags = 0
+        xin = x
+        if flags_name == "nhwc_in":
+            flags = pkg.FLAG_INPUT_NHWC
+            xin = np.ascontiguousarray(x.reshape(3, 64, 8 * 16).transpose(0, 2, 1))
+        got, plan, _ = gu.run_conv(pkg, oracle, p, xin, w, b, flags=flags, offsets=(0, woff, 0))
+        assert plan.info.launches == 1   # the plan counts on aligned weights
+        _check(oracle, p, got, ref, scale, f"1x1 weights offset {woff} elements, {flags_name}")
+
+
 def test_relu_gives_exact_zeros_and_runs_are_deterministic(pkg, orc, oracle):
     """ReLU outputs are exactly zero where the reference is zero-clamped well below zero (tests/test_fusion.cpp:15-30);
     two launches give identical bits."""
