@@ -60,6 +60,19 @@ def test_validation_matches_oracle_on_the_correctness_shapes(pkg, orc, oracle):
             assert info.supported == 1, (name, prec, info.reason)   # no (shape, precision) cell may be left without a kernel
 
 
+def test_epilogue_warp_count_follows_the_plan(pkg):
+    """CTAs that own their SM run 16 epilogue warps (640 threads): every 256-column tile whose ring leaves no room for a
+    second CTA, and 128-column tiles with one tile per CTA; everything else keeps 8 (384 threads)."""
+    c2 = pkg.query(P(pkg, 32, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1, precision=pkg.FP16))
+    assert c2.supported and c2.threads_per_block == 640 and (c2.cfg.tile_m, c2.cfg.tile_n, c2.cfg.split_k) == (128, 128, 1)
+    c3 = pkg.query(P(pkg, 64, 512, 28, 28, 128, 1, 1, precision=pkg.FP16))
+    assert c3.supported and c3.variant == 2 and c3.threads_per_block == 384 and c3.launches == 1   # 416 tiles on 148 CTAs; weights in place
+    wide = pkg.query(P(pkg, 16, 128, 56, 56, 256, 3, 3, 2, 2, 1, 1, precision=pkg.FP16), pkg.make_cfg(tile_n=256, tile_k=64, stages=4))
+    assert wide.supported and wide.threads_per_block == 640
+    shallow = pkg.query(P(pkg, 16, 128, 56, 56, 256, 3, 3, 2, 2, 1, 1, precision=pkg.FP16), pkg.make_cfg(tile_n=128, tile_k=64, stages=2))
+    assert shallow.supported and shallow.threads_per_block == 384                                   # two CTAs share an SM
+
+
 def test_query_precision_routing_and_reasons(pkg):
     base = (2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1)
     i32 = pkg.query(P(pkg, *base, precision=pkg.FP32))

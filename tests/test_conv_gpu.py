@@ -72,6 +72,11 @@ TILE_CASES = [
     ((1, 512, 7, 7, 512, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=64, stages=4, split_k=8, reduce=2)),
     ((32, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=4, split_k=2, reduce=2)),
     ((3, 200, 10, 20, 255, 1, 1, 1, 1, 0, 0), dict(tile_n=256, tile_k=32, stages=3, split_k=2, reduce=2, variant=4)),
+    # CTAs that own their SM drain the accumulators with 16 epilogue warps (640 threads): deep rings, partial channel chunks
+    ((2, 64, 12, 12, 100, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=6)),                 # one tile per CTA, last chunk 4 channels wide
+    ((4, 64, 14, 14, 200, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=64, stages=4)),                 # 256-column tile, channels end inside chunk 6
+    ((40, 32, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=32, stages=8)),                # several tiles per persistent CTA
+    ((2, 64, 16, 16, 72, 1, 1, 1, 1, 0, 0), dict(tile_n=128, tile_k=64, stages=6, variant=2)),       # direct-NCHW route
     # 256-pixel tiles: two accumulators per CTA share each weight tile
     ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=64, tile_k=64, stages=3)),
     ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=256, tile_k=64, stages=3, split_k=2)),
