@@ -31,7 +31,7 @@ import __graft_entry__ as entry  # noqa: E402
 NCU_TRAFFIC_BYTES = {"c2": 4470784,             # profiles/conv_tc_kernel_c2_fp16.md
                      "c3_fp16": 51898880}       # profiles/conv_tc_kernel_c3_fp16.md
 
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
 def load_peaks():
@@ -545,13 +545,18 @@ def run_chain_primary(args, torch, pkg, ranks, peaks, peak_kind, local_rank):
     sampler.start()
     ch = time_chain(torch, pkg, ranks, steps=args.steps, warmup=args.warmup, layout=args.layout, tune=args.tune)
     clocks = sampler.stop()
+    # a timed region of seconds runs under the power cap: compare it with the sustained GEMM peak, a short one with the burst
+    timed_s = ch["ms_per_pass"] * args.steps * 1e-3
+    sustained = timed_s > 2.0 and "bf16_tflops_sustained" in peaks
+    peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+    peak_kind = f"{peak_kind} ({'sustained' if sustained else 'burst'} cuBLAS bf16; the timed region lasted {timed_s:.1f} s)"
     out = {"metric": "conv-chain images/s (ResNet-50-shaped FP16 inference chain, batch 256)", "value": ch["images_per_s"], "unit": "images/s",
            "n_gpus": ranks.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ch["ms_per_pass"], "higher_is_better": True,
            "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)", "data": "synthetic",
            "config": {"workload": "c5: 53-conv ResNet-50-shaped chain, 224x224x3 input N(0,1), batch 256 sharded contiguously over the ranks, "
                                   "replicated random weights, one CUDA graph per replica", "cold_cache": "activations per pass exceed L2 (5.6 GB)"},
-           "roofline": {"bound": "tensor", "achieved": ch["tflops"] / ranks.world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                        "frac": ch["tflops"] / ranks.world / peaks["bf16_tflops"], "traffic": None, "kernel": "whole chain (per GPU)",
+           "roofline": {"bound": "tensor", "achieved": ch["tflops"] / ranks.world, "peak": peak, "unit": "TFLOP/s",
+                        "frac": ch["tflops"] / ranks.world / peak, "traffic": None, "kernel": "whole chain (per GPU)",
                         "peak_source": peak_kind},
            "gpu_launches": ch["launches_per_pass"] * args.steps, "clocks": clocks, "chain": ch}
     if ranks.rank == 0:

@@ -43,7 +43,7 @@ def candidate_cfgs(out_channels: int):
         for tile_n in (64, 128, 256):
             if tile_n > 64 and tile_n // 2 >= out_channels:
                 continue
-            for stages in (2, 3, 4):
+            for stages in (2, 3, 4, 6):
                 cfgs.append(dict(tile_m=tile_m, tile_n=tile_n, stages=stages))
     return cfgs
 
