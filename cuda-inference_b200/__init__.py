@@ -41,7 +41,7 @@ class ConvDesc(C.Structure):
 
 class ConvCfg(C.Structure):
     _fields_ = [("tile_n", C.c_int32), ("tile_k", C.c_int32), ("stages", C.c_int32), ("split_k", C.c_int32),
-                ("variant", C.c_int32), ("tile_m", C.c_int32), ("reduce", C.c_int32), ("reserved", C.c_int32)]
+                ("variant", C.c_int32), ("tile_m", C.c_int32), ("reduce", C.c_int32), ("cta_pair", C.c_int32)]
 
 
 class ConvInfo(C.Structure):
@@ -81,6 +81,8 @@ def lib() -> C.CDLL:
         L.gieb_conv_time_stages.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp, i32, C.POINTER(C.c_float)]
         L.gieb_conv_forward_static.argtypes = [C.POINTER(ConvDesc), C.POINTER(ConvCfg), vp, vp, vp, vp, vp]
         L.gieb_conv_plan_device_status.argtypes = [vp, C.POINTER(C.c_uint32)]
+        L.gieb_conv_static_status.argtypes = [C.POINTER(C.c_uint32), vp]
+        L.gieb_conv_plan_inject_stall.argtypes = [vp, C.c_uint32, C.c_uint64]
         L.gieb_repack_nchw_to_nhwc.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.gieb_prepack_weights.argtypes = [vp, vp, i32, i32, i32, i32, vp]
         L.gieb_rmsnorm_launch.argtypes = [C.POINTER(RmsNormDesc), vp, vp, vp, vp, vp, vp]
@@ -142,8 +144,8 @@ class ConvProblem:
         return 2 * self.out_channels * self.batch * self.out_h * self.out_w * self.in_channels * self.kernel_h * self.kernel_w
 
 
-def make_cfg(tile_n=0, tile_k=0, stages=0, split_k=0, variant=0, tile_m=0, reduce=0) -> ConvCfg:
-    return ConvCfg(tile_n, tile_k, stages, split_k, variant, tile_m, reduce, 0)
+def make_cfg(tile_n=0, tile_k=0, stages=0, split_k=0, variant=0, tile_m=0, reduce=0, cta_pair=0) -> ConvCfg:
+    return ConvCfg(tile_n, tile_k, stages, split_k, variant, tile_m, reduce, cta_pair)
 
 
 def validate_problem(p: ConvProblem) -> None:
@@ -203,6 +205,11 @@ class ConvPlan:
         check(lib().gieb_conv_plan_device_status(self._h, C.byref(v)))
         return int(v.value)
 
+    def inject_stall(self, roles: int, wait_limit_cycles: int) -> None:
+        """Test hook: later launches skip the given roles (bit 0 producers, bit 1 MMA issuer) and every device-side wait
+        gives up after `wait_limit_cycles` SM cycles; roles = 0 restores normal behaviour."""
+        check(lib().gieb_conv_plan_inject_stall(self._h, roles, wait_limit_cycles))
+
     def close(self) -> None:
         if self._h:
             lib().gieb_conv_plan_destroy(self._h)
@@ -221,6 +228,14 @@ def conv_forward_static(problem: ConvProblem, x: int, w: int, bias: int | None, 
     instead of a plan and a workspace.  Calls that overlap on the GPU race on that scratch; larger problems raise
     GieError(WORKSPACE_TOO_SMALL)."""
     check(lib().gieb_conv_forward_static(C.byref(problem.desc()), C.byref(cfg) if cfg is not None else None, x, w, bias, y, stream))
+
+
+def conv_static_status(stream: int = 0) -> int:
+    """Status word of the last conv_forward_static call on the current device (waits for `stream`): 0 = every bounded
+    device-side wait was satisfied, so y is complete.  Allocates nothing."""
+    v = C.c_uint32()
+    check(lib().gieb_conv_static_status(C.byref(v), stream))
+    return int(v.value)
 
 
 def repack_nchw_to_nhwc(src: int, dst: int, batch: int, channels: int, hw: int, c_padded: int, stream: int = 0) -> None:

@@ -102,6 +102,7 @@ struct Resolved {
   int variant;
   int boxes_per_image;  // variant 2: ceil(H*W / 64)
   int tile_m, tile_n, tile_k, stages, split_k;
+  int pair;  // 1: the 256-pixel tile belongs to a pair of CTAs (tcgen05.mma.cta_group::2), each staging half of the weight tile
   // Width geometry the kernel and its tensor maps see: the problem's own, except on the row-gather route (variant 5),
   // where the S taps of a filter row have become channels of a tensor of width Q (kernel width 1, stride 1, no padding).
   int eff_in_w, eff_kernel_w, eff_stride_w, eff_pad_w;
@@ -122,12 +123,15 @@ int pick_tile_k(int c) {
   return 16;
 }
 
-// Measured on B200 (profiles/): one SM pulls about 48 B/clk of operands from L2 through TMA, well below the 128 B/clk
-// the tensor pipe of a 128x128 tile would need, so operand bytes per slab usually decide.  CTAs that fit together on
-// an SM (shared memory and the 512 TMEM columns permitting) hide each other's prologue and epilogue.
-constexpr double kFeedBytesPerClk = 48.0;
+// Measured on B200: with every SM pulling, one SM receives about 74 B/clk of operands from L2 through TMA, well below
+// the 128 B/clk the tensor pipe of a 128x128 tile would need, so operand bytes per slab usually decide.  CTAs that fit
+// together on an SM (shared memory and the 512 TMEM columns permitting) hide each other's prologue and epilogue.
+constexpr double kFeedBytesPerClk = 74.0;
+constexpr int kNumSmPairs = kNumSms / 2;  // SM pairs that can host a two-CTA cluster
 
 size_t stage_bytes_of(int tile_m, int tile_n, int tile_k) { return size_t(tile_m + tile_n) * tile_k * 2; }
+// bytes one CTA of a pair stages per slab: its 128 activation rows and half of the weight rows
+size_t pair_stage_bytes_of(int tile_n, int tile_k) { return size_t(kTileM + tile_n / 2) * tile_k * 2; }
 
 // TMEM columns one CTA allocates: one accumulator set per 128-pixel half, doubled when two sets fit 256 columns.
 int tmem_cols_of(int tile_m, int tile_n) {
@@ -190,7 +194,7 @@ double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, i
   const double mmas = double(mh) * (tile_k / 16);
   const double pipe = mmas * (tile_n / 2.0);
   const double issue = tile_n >= 256 ? pipe : mmas * 78.0 + 110.0;  // narrow tiles: two slabs per wait / vote / fence when they queue up
-  const double feed = double(stage_bytes_of(tile_m, tile_n, tile_k)) / 74.0;
+  const double feed = double(stage_bytes_of(tile_m, tile_n, tile_k)) / kFeedBytesPerClk;
   const double slab = fmax(fmax(pipe, feed), issue / sharing);
   double epilogue = 500.0 + 16.0 * mh * tile_n;
   if (real_split > 1 && reduce == 1) epilogue *= 2.0;  // FP32 partials: twice the bytes
@@ -203,6 +207,39 @@ double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, i
   }
   return total;
 }
+
+// Ring depth of a CTA pair: each CTA owns its SM, so the ring takes what shared memory is left.
+int pick_pair_stages(int tile_n, int tile_k, int kb_per_split, size_t extra_smem) {
+  const size_t sb = pair_stage_bytes_of(tile_n, tile_k);
+  int stages = int((kMaxDynamicSmem - 1024 - 3072 - extra_smem) / sb);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > kb_per_split) stages = kb_per_split;
+  if (stages < 2) stages = 2;
+  return stages;
+}
+
+// The same model for 256-pixel tiles of CTA pairs: one instruction stream drives both SMs, each SM's tensor pipe works on
+// 128 x tile_n x 16 per instruction and receives (128 + tile_n / 2) operand rows per slab.
+double estimate_cycles_pair(const gieb_conv_desc& d, const Geometry& g, int64_t rows, int tile_n, int tile_k, int split, int total_kb) {
+  const int kb_per_split = ceil_div(total_kb, split);
+  const int real_split = ceil_div(total_kb, kb_per_split);
+  const int64_t pairs = int64_t(ceil_div(rows, 2 * kTileM)) * ceil_div(d.out_channels, tile_n) * real_split;
+  const double tiles_per_sm = double((pairs + kNumSmPairs - 1) / kNumSmPairs);
+  const double mmas = tile_k / 16;
+  const double pipe = mmas * (tile_n / 2.0);
+  const double issue = tile_n >= 256 ? pipe : mmas * 78.0 + 110.0;
+  const double feed = double(pair_stage_bytes_of(tile_n, tile_k)) / kFeedBytesPerClk;
+  const double slab = fmax(fmax(pipe, feed), issue);
+  double epilogue = 500.0 + 16.0 * tile_n;
+  if (real_split > 1) epilogue *= 2.0;  // FP32 partials: twice the bytes
+  const bool overlapped = tile_n <= 256 && tiles_per_sm >= 2.0;  // accumulators are double-buffered
+  double total = 5000.0 + tiles_per_sm * kb_per_split * slab + (overlapped ? epilogue : tiles_per_sm * epilogue);
+  if (real_split > 1) total += 6000.0 + 2.0 * real_split * double(g.y_elems) * 4.0 / 1500.0;  // extra launch + partial traffic
+  return total;
+}
+
+// Whether the heuristic may choose CTA-pair tiles unasked (a configuration can always ask for them).
+constexpr bool kAutoPair = false;
 
 }  // namespace
 
@@ -306,11 +343,32 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   }
   if (c.split_k < 0) return no("split_k must be >= 0");
   if (c.tile_m != 0 && c.tile_m != 128 && c.tile_m != 256) return no("tile_m must be 128 or 256");
-  // search (tile_m, tile_n, split_k) unless fixed
+  if (c.cta_pair < 0 || c.cta_pair > 2) return no("cta_pair must be 0 (auto), 1 (single CTA) or 2 (CTA pair)");
+  if (c.cta_pair == 2) {
+    if (tf32) return no("CTA-pair tiles are offered for FP16 / BF16");
+    if (c.tile_m != 0 && c.tile_m != 256) return no("a CTA pair computes 256-pixel tiles (tile_m 0 or 256)");
+    if (c.tile_n != 0 && c.tile_n < 64) return no("CTA-pair tiles are 64, 128 or 256 output channels wide");
+    if (c.reduce == 2) return no("a CTA pair is a cluster already: its split-K slices are summed through the workspace (reduce 0 or 1)");
+  }
+  // search (tile_m, tile_n, split_k, pair) unless fixed
   double best = 1e300;
-  int best_m = 0, best_n = 0, best_s = 0, best_mode = 0;
+  int best_m = 0, best_n = 0, best_s = 0, best_mode = 0, best_pair = 0;
   const int n_opts[4] = {32, 64, 128, 256};
-  for (int tm = 128; tm <= 256; tm += 128) {
+  // 256-pixel tiles of CTA pairs: only the workspace reduction for split-K
+  for (int ni = 1; ni < 4 && !tf32 && c.cta_pair != 1 && (c.cta_pair == 2 || kAutoPair) && (c.tile_m == 0 || c.tile_m == 256) && c.reduce != 2; ++ni) {
+    const int tn = n_opts[ni];
+    if (r->tile_n && tn != r->tile_n) continue;
+    if (!r->tile_n && tn / 2 >= d.out_channels) continue;
+    if (c.cta_pair != 2 && rows <= kTileM) continue;  // the peer CTA would own no pixel
+    for (int s = 1; s <= 16; ++s) {
+      if (c.split_k && s != c.split_k) continue;
+      if (s > 1 && r->total_kb < 2 * s) break;
+      if (s > 1 && size_t(s) * size_t(g.y_elems) * 4 > (size_t(1) << 31)) continue;
+      const double t = estimate_cycles_pair(d, g, rows, tn, r->tile_k, s, r->total_kb);
+      if (t < best) { best = t; best_m = 2 * kTileM; best_n = tn; best_s = s; best_mode = s > 1 ? 1 : 0; best_pair = 1; }
+    }
+  }
+  for (int tm = 128; tm <= 256 && c.cta_pair != 2; tm += 128) {
     if (c.tile_m && tm != c.tile_m) continue;
     if (!c.tile_m && tm == 256 && int64_t(ceil_div(g.pixels, 256)) * ceil_div(d.out_channels, 128) < 4 * kNumSms) continue;  // big tiles only where wave quantisation is negligible
     for (int ni = 0; ni < 4; ++ni) {
@@ -333,7 +391,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
             if (c.reduce == 0 && ctas > kNumSms) continue;
           }
           const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s, mode, r->total_kb) + (r->variant == 2 && tn < d.out_channels && tn < 256 ? 1e6 : 0.0);
-          if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; best_mode = mode; }
+          if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; best_mode = mode; best_pair = 0; }
         }
       }
     }
@@ -345,6 +403,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   }
   r->tile_m = best_m;
   r->tile_n = best_n;
+  r->pair = best_pair;
   r->est_cycles = best;
   r->kb_per_split = ceil_div(r->total_kb, best_s);
   r->split_k = ceil_div(r->total_kb, r->kb_per_split);  // every slice non-empty
@@ -357,17 +416,21 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   r->tma_epilogue = (d.flags & GIEB_FLAG_OUTPUT_NHWC) && d.out_channels % 8 == 0 && r->variant != 2 && r->split_k == 1;
   const size_t epi_smem = r->tma_epilogue ? conv_tc_epilogue_staging_bytes(r->tile_n) : 0;
   int stages = c.stages ? c.stages
-                        : pick_stages(r->tile_m, r->tile_n, r->tile_k, r->kb_per_split, int64_t(r->tiles_m) * r->tiles_n * r->split_k, epi_smem);
+               : r->pair ? pick_pair_stages(r->tile_n, r->tile_k, r->kb_per_split, epi_smem)
+                         : pick_stages(r->tile_m, r->tile_n, r->tile_k, r->kb_per_split, int64_t(r->tiles_m) * r->tiles_n * r->split_k, epi_smem);
   // Activations streamed once from DRAM (direct-NCHW route) with a long reduction: one CTA per SM with a deep ring
   // keeps more loads in flight than two shallow ones (measured on 512 -> 128 channels at 28x28: 17.5 vs 18.4 us).
-  if (!c.stages && r->variant == 2 && r->kb_per_split >= 8) {
+  if (!c.stages && !r->pair && r->variant == 2 && r->kb_per_split >= 8) {
     const size_t sb = stage_bytes_of(r->tile_m, r->tile_n, r->tile_k);
     if (3072 + 1024 + 6 * sb + epi_smem <= kMaxDynamicSmem) stages = 6;
   }
   if (stages < 2 || stages > kMaxStages) return no("stages must be in [2, 8]");
   r->stages = stages;
-  r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, r->tma_epilogue != 0);
+  r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, r->tma_epilogue != 0, r->pair != 0);
   if (r->smem > kMaxDynamicSmem) return no("configuration needs more shared memory than one CTA may have (227 KiB)");
+  // A CTA of a pair keeps its SM to itself (the tensor-memory allocation of a pair spans two SMs): a short ring still
+  // asks for more than half of an SM's shared memory.
+  if (r->pair && r->smem < kMaxDynamicSmem / 2 + 2048) r->smem = kMaxDynamicSmem / 2 + 2048;
 
   // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
   // src/kernels/tensor_core_mma.cu:265-278)
@@ -379,7 +442,9 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   // A CTA that has its SM to itself drains its accumulators with 16 warps instead of 8: always for 256-column tiles
   // (measured 2-7 % per step), for 128-column tiles only when the CTA has a single tile, whose epilogue nothing hides
   // (with several tiles per CTA the extra polling warps cost more than the last epilogue gains).
-  {
+  if (r->pair) {
+    r->epi_warps = conv_tc_pair_epi_warps(r->tile_n);
+  } else {
     const bool alone = resident_ctas(r->tile_m, r->tile_n, r->smem) == 1;
     const bool single_tile = int64_t(r->tiles_m) * r->tiles_n * r->split_k <= kNumSms;
     r->epi_warps = (alone && (r->tile_n >= 256 || (r->tile_n >= 128 && single_tile && r->reduce != 2))) ? 16 : 8;
@@ -403,6 +468,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
   out->cfg.split_k = r.split_k;
   out->cfg.variant = r.variant;
   out->cfg.reduce = r.reduce;
+  out->cfg.cta_pair = r.variant == 3 ? 0 : (r.pair ? 2 : 1);
   out->workspace_bytes = r.ws_total;
   out->persistent_bytes = sizeof(uint32_t);
   out->padded_channels = d.precision == GIEB_TF32 ? r.c_padded / 2 : r.c_padded;
@@ -414,7 +480,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
   } else {
     out->dynamic_smem_bytes = uint32_t(r.smem);
     out->threads_per_block = conv_tc_threads(r.epi_warps);
-    out->num_blocks = int64_t(r.tiles_m) * r.tiles_n * r.split_k;
+    out->num_blocks = int64_t(r.tiles_m) * r.tiles_n * r.split_k * (r.pair ? 2 : 1);
     // repack (activations and weights in one launch; none when both are consumed in place), convolution, reduction
     const bool x_in_place = r.variant == 2 || (d.flags & GIEB_FLAG_INPUT_NHWC);
     const bool w_in_place = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) != 0 ||
@@ -467,6 +533,8 @@ struct gieb_conv_plan {
   Geometry g;
   int device;
   uint32_t* d_status;
+  long long wait_limit = ptx::kWaitLimitCycles;  // bound of every device-side wait, in SM cycles
+  uint32_t debug_skip = 0;                       // see gieb_conv_plan_inject_stall
 };
 
 namespace {
@@ -516,7 +584,7 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
     const cuuint64_t kp = cuuint64_t(d.kernel_h) * r.eff_kernel_w * r.c_padded;  // in 2-byte units
     const cuuint64_t dims[2] = {kp >> esh, cuuint64_t(d.out_channels)};
     const cuuint64_t strides[1] = {kp * 2};
-    const cuuint32_t box[2] = {cuuint32_t(r.tile_k >> esh), cuuint32_t(r.tile_n)};
+    const cuuint32_t box[2] = {cuuint32_t(r.tile_k >> esh), cuuint32_t(r.pair ? r.tile_n / 2 : r.tile_n)};  // a CTA of a pair loads half of the rows
     const cuuint32_t estr[2] = {1, 1};
     const CUresult res = g_encode_tiled(tm_wgt, dt, 2, const_cast<void*>(wk), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -640,13 +708,16 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.is_tf32 = d.precision == GIEB_TF32;
   p.bias_fp32 = (p.is_tf32 || (d.flags & GIEB_FLAG_BIAS_FP32)) ? 1 : 0;
   p.a_mode = mode;
-  p.idesc = p.is_tf32 ? ptx::make_idesc_tf32(kTileM, r.tile_n, false, false) : ptx::make_idesc_f16(kTileM, r.tile_n, p.is_bf16, mode == 2, false);
+  p.idesc = p.is_tf32 ? ptx::make_idesc_tf32(kTileM, r.tile_n, false, false)
+                      : ptx::make_idesc_f16(r.pair ? 2 * kTileM : kTileM, r.tile_n, p.is_bf16, mode == 2, false);  // a pair's instruction spans 256 rows
   p.bias = bias;
   p.residual = residual;
   p.out_nhwc = (d.flags & GIEB_FLAG_OUTPUT_NHWC) ? 1 : 0;
   p.y = y;
   p.partial = part;
   p.status = pl->d_status;
+  p.wait_limit = pl->wait_limit;
+  p.debug_skip = pl->debug_skip;
   p.tiles_m = ceil_div(rows, r.tile_m);
   p.tiles_n = r.tiles_n;
   p.num_tiles = p.tiles_m * p.tiles_n * r.split_k;
@@ -660,9 +731,10 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.fd_kernel_w = FastDiv::make(p.kernel_w);
   p.fd_boxes = FastDiv::make(p.boxes_per_image > 0 ? p.boxes_per_image : 1);
   // persistent CTAs: as many as can be resident at once, each walking the tile list
-  const int64_t resident = int64_t(kNumSms) * resident_ctas(r.tile_m, r.tile_n, r.smem);
-  // cluster mode: one tile per CTA, blockIdx.x = tile * split + slice (the grid is a multiple of the cluster size)
-  dim3 grid(unsigned(p.cluster_split > 1 || p.num_tiles < resident ? p.num_tiles : resident));
+  const int64_t resident = r.pair ? kNumSmPairs : int64_t(kNumSms) * resident_ctas(r.tile_m, r.tile_n, r.smem);
+  // cluster mode: one tile per CTA, blockIdx.x = tile * split + slice (the grid is a multiple of the cluster size);
+  // pair mode: blockIdx.x = 2 * pair + rank, every pair walks the tile list
+  dim3 grid(unsigned(p.cluster_split > 1 || p.num_tiles < resident ? p.num_tiles : resident) * (r.pair ? 2u : 1u));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[1], st));
   // TMA epilogue: needs 16-byte aligned tensors; a call that is not takes the direct stores (the staging stays unused)
   CUtensorMap tm_out, tm_res;
@@ -678,7 +750,8 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
       p.res_tma = 1;
     }
   }
-  GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
+  if (r.pair) GIEB_CUDA(conv_tc_pair_launch(r.tile_n, r.tile_k, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
+  else GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
   if (r.reduce == 1)
     GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_tf32 ? 2 : p.is_bf16, residual,
@@ -754,7 +827,8 @@ int gieb_conv_plan_create(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, 
       cudaStreamDestroy(s);
     }
   }
-  if (e == cudaSuccess && r.variant != 3) e = conv_tc_prepare(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, kMaxDynamicSmem);
+  if (e == cudaSuccess && r.variant != 3)
+    e = r.pair ? conv_tc_pair_prepare(r.tile_n, r.tile_k, kMaxDynamicSmem) : conv_tc_prepare(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, kMaxDynamicSmem);
   if (e != cudaSuccess) {
     if (pl->d_status) cudaFree(pl->d_status);
     delete pl;
@@ -871,6 +945,8 @@ int gieb_conv_forward_static(const gieb_conv_desc* desc, const gieb_conv_cfg* cf
                              const void* bias, void* y, void* stream) {
   const int st = validate(desc);
   if (st != GIEB_OK) return st;
+  if (desc->flags & GIEB_FLAG_RESIDUAL)
+    return fail(GIEB_UNSUPPORTED, "the allocation-free call has no residual operand; problems with GIEB_FLAG_RESIDUAL go through a plan");
   gieb_conv_plan pl;  // lives on the host stack for the duration of this call only
   char why[256] = "";
   if (resolve(*desc, cfg, &pl.r, why, sizeof(why)) != GIEB_OK) return fail(GIEB_UNSUPPORTED, "%.255s", why);
@@ -885,13 +961,39 @@ int gieb_conv_forward_static(const gieb_conv_desc* desc, const gieb_conv_cfg* cf
   pl.desc = *desc;
   pl.g = geometry(*desc);
   GIEB_CUDA(cudaGetDevice(&pl.device));
+  int cc_major = 0;
+  GIEB_CUDA(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, pl.device));
+  if (cc_major != 10) return fail(GIEB_UNSUPPORTED, "this library contains sm_100a code only; device %d has compute capability %d.x", pl.device, cc_major);
   pl.d_status = reinterpret_cast<uint32_t*>(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (pl.r.variant != 3) GIEB_CUDA(conv_tc_prepare(pl.r.tile_m, pl.r.tile_n, pl.r.tile_k, pl.r.epi_warps, kMaxDynamicSmem));
+  if (pl.r.variant != 3)
+    GIEB_CUDA(pl.r.pair ? conv_tc_pair_prepare(pl.r.tile_n, pl.r.tile_k, kMaxDynamicSmem)
+                        : conv_tc_prepare(pl.r.tile_m, pl.r.tile_n, pl.r.tile_k, pl.r.epi_warps, kMaxDynamicSmem));
   // The array keeps whatever the previous call left: the status word must start at zero.  Everything else in the
   // scratch is fully rewritten by the repack kernels (padding channels included) and the split-K slices before use.
   GIEB_CUDA(cudaMemsetAsync(base, 0, kStaticScratchHeader, s));
   return launch_impl(&pl, x, w, bias, y, base + kStaticScratchHeader, kStaticScratchBytes, s);
+}
+
+int gieb_conv_plan_inject_stall(gieb_conv_plan* plan, uint32_t roles, uint64_t wait_limit_cycles) {
+  if (plan == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null plan");
+  if (roles > 3u) return fail(GIEB_INVALID_ARGUMENT, "roles is a mask of bit 0 (producers) and bit 1 (MMA issuer)");
+  if (roles != 0 && (wait_limit_cycles == 0 || wait_limit_cycles > 2000000000ull))
+    return fail(GIEB_INVALID_ARGUMENT, "an injected stall needs a wait limit between 1 and 2e9 SM cycles (about a second)");
+  plan->debug_skip = roles;
+  plan->wait_limit = roles != 0 ? static_cast<long long>(wait_limit_cycles) : ptx::kWaitLimitCycles;
+  return GIEB_OK;
+}
+
+int gieb_conv_static_status(uint32_t* status_out, void* stream) {
+  if (status_out == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null argument");
+  unsigned char* base = nullptr;
+  const int ss = static_scratch_for_current_device(&base);
+  if (ss != GIEB_OK) return ss;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  GIEB_CUDA(cudaMemcpyAsync(status_out, base, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+  GIEB_CUDA(cudaStreamSynchronize(s));
+  return GIEB_OK;
 }
 
 int gieb_conv_plan_device_status(const gieb_conv_plan* plan, uint32_t* status_out) {

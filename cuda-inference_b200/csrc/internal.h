@@ -133,11 +133,14 @@ struct ConvTcParams {
   void* y;            // output in the storage type (split_k == 1 or cluster reduction)
   float* partial;     // [splits][B*O*P*Q] FP32 partial sums in the output's element order (workspace reduction), else null
   uint32_t* status;
+  long long wait_limit;  // SM cycles a device-side wait may last before its role gives up and reports to *status
+  uint32_t debug_skip;   // test hook, 0 in production: bit 0 = the producers load nothing, bit 1 = the MMA warp issues nothing
 };
 
 // tile_m is 128 or 256 output pixels per CTA (one or two TMEM accumulators sharing each weight tile).
 // tma_epilogue: add the staging boxes of the TMA-store epilogue (channel-contiguous output).
-size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, bool tma_epilogue);
+// pair: the tile belongs to a CTA pair (tile_m = 256), each CTA stages 128 activation rows and tile_n / 2 weight rows.
+size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, bool tma_epilogue, bool pair = false);
 size_t conv_tc_epilogue_staging_bytes(int tile_n);
 // epi_warps: 8, or 16 for CTAs that have an SM to themselves (tile_n >= 128 only)
 int conv_tc_threads(int epi_warps);
@@ -147,6 +150,12 @@ cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, int epi_warps, s
 cudaError_t conv_tc_launch(int tile_m, int tile_n, int tile_k, int epi_warps, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
                            const CUtensorMap& tm_out, const CUtensorMap& tm_res, const ConvTcParams& p, dim3 grid, size_t smem_bytes,
                            cudaStream_t stream);
+
+// CTA-pair points (tcgen05.mma.cta_group::2): tile_m = 256, tile_n 64 / 128 / 256; `grid` = 2 x the number of pairs.
+int conv_tc_pair_epi_warps(int tile_n);
+cudaError_t conv_tc_pair_prepare(int tile_n, int tile_k, size_t smem_bytes);
+cudaError_t conv_tc_pair_launch(int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt, const CUtensorMap& tm_out,
+                                const CUtensorMap& tm_res, const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream);
 
 // Sum of split-K partials + bias (+ residual) + ReLU + one rounding; `total` = B*O*P*Q elements in the output's order.
 cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total, int out_channels, int pq,

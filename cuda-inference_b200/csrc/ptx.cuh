@@ -67,6 +67,11 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrival on an mbarrier of any CTA of the cluster (`cluster_addr` from map_to_cta); release at cluster scope, so the
+// arriving thread's earlier accesses are ordered before the waiter's.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -85,12 +90,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // ORs `code` into *status (global memory) and returns false; the caller abandons its role and falls through to the
 // kernel's common exit so the CTA still releases TMEM and terminates.
 constexpr long long kWaitLimitCycles = 4000000000LL;  // about two seconds at B200 clocks
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t code,
+                                          long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 0x3ffu) == 0 && clock64() - t0 > kWaitLimitCycles) {
+    if ((++polls & 0x3ffu) == 0 && clock64() - t0 > limit_cycles) {
       atomicOr(status, code);
       return false;
     }
@@ -145,6 +151,33 @@ __device__ __forceinline__ void tma_load_im2col_4d(void* dst, const CUtensorMap*
       : "memory");
 }
 
+// ---- TMA loads of a CTA pair (tcgen05 cta_group::2) ---------------------------------------------------------------
+// Each CTA of the pair loads its own operand halves into its own shared memory, but the bytes are counted on ONE
+// mbarrier, the one of the pair's leader CTA (`bar_cluster_addr` = map_to_cta(barrier, leader rank)): the .cta_group::2
+// form of the instruction is what allows the barrier to live in the peer CTA.  No multicast: every CTA fetches its data.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int32_t x, int32_t y,
+                                                 int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int32_t c,
+                                                        int32_t w, int32_t h, int32_t n, uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c), "r"(w), "r"(h), "r"(n),
+      "h"(off_w), "h"(off_h)
+      : "memory");
+}
+
 // ---- tcgen05: tensor memory --------------------------------------------------------------------------------------
 // Whole-warp calls (.sync.aligned).  `cols` is a power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
@@ -156,6 +189,19 @@ __device__ __forceinline__ void tmem_relinquish() {
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// The same for a CTA pair (cta_group::2): one warp of EACH CTA of the pair executes the instruction, the same warp index
+// in both, with the same shared-memory offset for the result; the columns are reserved in both CTAs' tensor memory at
+// the same address.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -223,6 +269,29 @@ __device__ __forceinline__ void mma_tf32_ss(uint32_t tmem_d, uint64_t adesc, uin
 // tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// ---- tcgen05 across a CTA pair (cta_group::2) ------------------------------------------------------------------
+// One thread of the pair's leader CTA (even rank in the cluster) issues the instruction for both SMs.  M = 256: CTA r of
+// the pair supplies rows 128 r .. 128 r + 127 of A and rows N/2 * r .. of B, each from its OWN shared memory at the
+// offsets the two descriptors name, and receives rows 128 r .. of D in its own tensor memory (lane = row, N columns,
+// same address in both CTAs).  Every SM therefore fetches only half of the B tile.
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate))
+      : "memory");
+}
+// Arrival on the mbarrier at this shared-memory offset in every CTA of `cta_mask` (bit i = cluster rank i) once all
+// MMAs issued so far by this thread have finished.  (A multicast of the barrier SIGNAL, not of any load.)
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask)
+               : "memory");
 }
 
 // ---- tcgen05: TMEM -> registers ---------------------------------------------------------------------------------

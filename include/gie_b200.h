@@ -94,7 +94,10 @@ typedef struct gieb_conv_cfg {
                        2 = inside the convolution kernel: the slices of a tile form a thread-block cluster and are
                            summed through distributed shared memory (split_k 2, 4 or 8 dividing tile_n / 32,
                            tile_m 128); no partials in the workspace, no extra launch                       */
-  int32_t reserved;
+  int32_t cta_pair; /* 0 = auto; 1 = every tile is computed by one CTA; 2 = 256-pixel tiles computed by pairs of CTAs (clusters
+                       of two, tcgen05.mma.cta_group::2): each CTA stages its own 128 pixels and half of the weight tile, so
+                       the weight traffic per SM is halved.  FP16 / BF16, tile_n 64, 128 or 256, tile_m 0 or 256, split-K
+                       slices through the workspace (reduce 0 or 1)                                                  */
 } gieb_conv_cfg;
 
 /* What KernelDesc::supports / workspace_bytes / dynamic_smem_bytes / num_blocks answer
@@ -178,15 +181,34 @@ GIEB_API int gieb_conv_time_stages(const gieb_conv_plan* plan, const void* x, co
  *     call outside any stream capture;
  *   - all calls on a device share the one array: two calls whose GPU work overlaps (different streams, different
  *     threads) race on it -- serialise them on one stream or with events.  Nothing is carried from call to call:
- *     the status word is cleared and the rest rewritten on every call.
+ *     the status word is cleared and the rest rewritten on every call;
+ *   - a bounded device-side wait that runs out leaves y incomplete and is reported only through
+ *     gieb_conv_static_status: call it (it waits for the stream) before using y;
+ *   - there is no residual operand: GIEB_FLAG_RESIDUAL is refused, sm_100 devices only.
  * Results are bit-identical to gieb_conv_launch with the same configuration. */
 GIEB_API int gieb_conv_forward_static(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, const void* x, const void* w,
                                       const void* bias, void* y, void* stream);
+
+/* No counterpart in the reference.  Companion of gieb_conv_forward_static, equally allocation-free: the kernels
+ * report a bounded device-side wait that ran out (the result of that call is then incomplete) in a status word at the
+ * head of the built-in scratch; gieb_conv_forward_static clears it at the start of every call.  This copies the word of
+ * the current device to *status_out on `stream` and waits for that stream, so pass the stream the forward call ran on:
+ * 0 means the last call on this device computed everything.  Check it before trusting y. */
+GIEB_API int gieb_conv_static_status(uint32_t* status_out, void* stream);
 
 /* Device-side status word of the plan: 0 = no kernel of this plan ever gave up on a bounded wait.  Synchronises
  * nothing itself; call after the stream has been synchronised.  (No reference counterpart: the reference's
  * kernels have no asynchronous waits.) */
 GIEB_API int gieb_conv_plan_device_status(const gieb_conv_plan* plan, uint32_t* status_out);
+
+/* Test hook (no reference counterpart; the reference's kernels cannot stall).  Makes later launches of this plan fail
+ * the way a lost TMA completion would, without faulting anything: `roles` bit 0 = the TMA producer warps issue no
+ * loads, bit 1 = the MMA warp issues nothing and signals nobody; the warps that wait for them give up after
+ * `wait_limit_cycles` SM cycles (at most 2e9, about a second), set their bit in the plan's status word (1 = producer,
+ * 2 = MMA issuer, 4 = epilogue), and the kernel ends by itself with its tensor memory freed.  The output of such a
+ * launch is garbage by construction.  roles = 0 restores normal behaviour.  Not thread-safe: call it while no other
+ * thread uses the plan. */
+GIEB_API int gieb_conv_plan_inject_stall(gieb_conv_plan* plan, uint32_t roles, uint64_t wait_limit_cycles);
 
 /* transpose_c_hw as used for X (src/kernels/tensor_core_mma.cu:61-82,309): 16-bit [B][C][HW] -> [B][HW][Cp],
  * Cp = c_padded >= C (extra channels zero).  Bit-exact permutation.  `src` needs only 2-byte alignment,

@@ -104,6 +104,41 @@ def test_explicit_tile_configurations(pkg, orc, oracle, case, prec_name):
     _check(oracle, p, got, ref, scale, f"case {case} {kw} {prec_name}")
 
 
+PAIR_CASES = [
+    # 256-pixel tiles computed by pairs of CTAs (tcgen05.mma.cta_group::2): each CTA loads its own 128 pixels and half of
+    # the weight rows; the leader issues the MMAs for both.  (shape args, cfg kwargs)
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(cta_pair=2, tile_n=64, tile_k=64, stages=3)),        # 1568 px: 7 pair tiles, the last one half empty
+    ((8, 64, 14, 14, 128, 3, 3, 1, 1, 1, 1), dict(cta_pair=2, tile_n=128, tile_k=32, stages=4)),
+    ((8, 64, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict(cta_pair=2, tile_n=256, tile_k=64, stages=6)),
+    ((2, 130, 9, 9, 130, 3, 3, 1, 1, 1, 1), dict(cta_pair=2, tile_n=256, tile_k=16, stages=5)),       # 162 px: the peer owns 34; channel tails
+    ((1, 16, 5, 5, 8, 1, 1, 1, 1, 0, 0), dict(cta_pair=2, tile_n=64, tile_k=16, stages=2)),           # 25 px: the peer owns nothing
+    ((2, 64, 28, 28, 128, 3, 3, 2, 2, 1, 1), dict(cta_pair=2, tile_n=128, tile_k=64, stages=2)),      # stride 2
+    ((4, 96, 27, 27, 192, 5, 5, 1, 1, 2, 2), dict(cta_pair=2, tile_n=128, tile_k=32, stages=8)),      # 5x5, 2916 px, channel tile tail
+    ((1, 512, 7, 7, 512, 3, 3, 1, 1, 1, 1), dict(cta_pair=2, tile_n=256, tile_k=64, stages=6, split_k=4)),   # split-K through the workspace
+    ((8, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1), dict(cta_pair=2, tile_n=64, tile_k=32, stages=4, split_k=3)),
+    ((96, 64, 28, 28, 64, 3, 3, 1, 1, 1, 1), dict(cta_pair=2, tile_n=64, tile_k=64, stages=4)),       # 294 pair tiles: several per pair (persistent walk)
+    ((40, 32, 14, 14, 512, 3, 3, 1, 1, 1, 1), dict(cta_pair=2, tile_n=256, tile_k=32, stages=6)),     # 62 tiles, double-buffered accumulators
+    ((3, 200, 10, 20, 255, 1, 1, 1, 1, 0, 0), dict(cta_pair=2, variant=4, tile_n=256, tile_k=32, stages=3)),  # tiled activation loads
+    ((2, 512, 28, 28, 128, 1, 1, 1, 1, 0, 0), dict(cta_pair=2, variant=2, tile_n=128, tile_k=64, stages=4)),  # direct NCHW (pixel-major operand)
+    ((3, 70, 10, 20, 255, 1, 1, 1, 1, 0, 0), dict(cta_pair=2, variant=2, tile_n=256, tile_k=32, stages=3)),
+    ((2, 3, 37, 29, 64, 7, 7, 2, 2, 3, 3), dict(cta_pair=2, variant=5, tile_n=64)),                   # row-gather route
+]
+
+
+@pytest.mark.parametrize("case", range(len(PAIR_CASES)))
+@pytest.mark.parametrize("prec_name", ["fp16", "bf16"])
+def test_cta_pair_tiles(pkg, orc, oracle, case, prec_name):
+    args, kw = PAIR_CASES[case]
+    prec = orc.FP16 if prec_name == "fp16" else orc.BF16
+    p = orc.Problem.P(*args, precision=prec, bias=True, relu=(case % 2 == 0))
+    x, w, b = oracle.make_conv_data(p, 7000 + case, case % 4)
+    ref, scale = oracle.conv2d(p, x, w, b)
+    got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b, cfg=pkg.make_cfg(**kw), repeats=2)
+    assert plan.info.cfg.cta_pair == 2 and plan.info.cfg.tile_m == 256
+    assert plan.info.num_blocks % 2 == 0
+    _check(oracle, p, got, ref, scale, f"pair case {case} {kw} {prec_name}")
+
+
 DIRECT_CASES = [
     # 1x1 / stride 1 / pad 0 with H*W % 8 == 0: activations are read straight from NCHW (pixel-major operand)
     ((2, 64, 8, 8, 64, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=64, tile_k=64, stages=2), 0),
@@ -369,3 +404,41 @@ def test_repack_is_bit_exact(pkg, orc, oracle):
         exp[:, :, :c] = src.reshape(bt, c, hw).transpose(0, 2, 1)
         assert np.array_equal(got[:exp.size].reshape(exp.shape), exp), (bt, c, hw, cp, off)
         assert np.all(got[exp.size:] == 0xFFFF)
+
+
+@pytest.mark.parametrize("kw", [dict(tile_n=128, tile_k=64, stages=4), dict(tile_n=64, tile_k=32, stages=3, split_k=2, reduce=2),
+                                dict(cta_pair=2, tile_n=128, tile_k=64, stages=4)])
+@pytest.mark.parametrize("roles,expect", [(1, 2), (2, 1 | 4)])
+def test_bounded_waits_run_out_and_report(pkg, orc, oracle, kw, roles, expect):
+    """A device-side wait that is never satisfied gives up after its limit, sets its bit in the plan's status word, the
+    kernel ends by itself with its tensor memory freed, and the next launch of the same plan is correct again.  The stall
+    is injected on the host (a role that issues nothing); nothing faults.  roles 1: the producers load nothing, so the MMA
+    issuer gives up (bit 1 = value 2); roles 2: the issuer does nothing, so the producers (value 1) and the epilogue
+    (value 4) give up."""
+    import time
+    import torch
+    p = orc.Problem.P(4, 64, 14, 14, 128, 3, 3, 1, 1, 1, 1, precision=orc.FP16, bias=True, relu=True)
+    x, w, b = oracle.make_conv_data(p, 31, 1)
+    ref, scale = oracle.conv2d(p, x, w, b)
+    plan = pkg.ConvPlan(gu.pkg_problem(pkg, p), pkg.make_cfg(**kw))
+    got, _, _ = gu.run_conv(pkg, oracle, p, x, w, b, plan=plan)
+    _check(oracle, p, got, ref, scale, "before the injected stall")
+    plan.inject_stall(roles, 2_000_000)  # about a millisecond per wait
+    tx, px = gu.to_device_storage(oracle, p.precision, x)
+    tw, pw = gu.to_device_storage(oracle, p.precision, w)
+    tb, pb = gu.to_device_storage(oracle, p.precision, b)
+    out = gu.OutBuf(p.precision, int(np.prod(p.y_shape)))
+    ws = gu.Workspace(plan.workspace_bytes)
+    t0 = time.time()
+    plan.launch(px, pw, pb, out.ptr, ws.ptr, plan.workspace_bytes, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()  # the kernel returns by itself
+    assert time.time() - t0 < 5.0
+    status = plan.device_status()
+    assert status & expect == expect and status != 0, f"status word {status}, expected bits {expect}"
+    out.read(oracle)  # guard bands intact
+    ws.check_guard()
+    plan.close()
+    # the device and its tensor memory are fine: a fresh plan of the same configuration computes the right answer
+    plan2 = pkg.ConvPlan(gu.pkg_problem(pkg, p), pkg.make_cfg(**kw))
+    got2, _, _ = gu.run_conv(pkg, oracle, p, x, w, b, plan=plan2)
+    _check(oracle, p, got2, ref, scale, "after the injected stall")

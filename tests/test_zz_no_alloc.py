@@ -23,10 +23,12 @@ def _both_ways(pkg, orc, oracle, args, prec, seed, cfg_kw):
     out = gu.OutBuf(p.precision, int(np.prod(p.y_shape)))
     st = torch.cuda.current_stream().cuda_stream
     pkg.conv_forward_static(gu.pkg_problem(pkg, p), px, pw, pb, out.ptr, st, cfg)  # first call: address look-up, module load
+    assert pkg.conv_static_status(st) == 0
     torch.cuda.synchronize()
     out.t.view(torch.uint8).fill_(0xFF)
     free_before = torch.cuda.mem_get_info()[0]
     pkg.conv_forward_static(gu.pkg_problem(pkg, p), px, pw, pb, out.ptr, st, cfg)
+    assert pkg.conv_static_status(st) == 0, "a bounded device-side wait ran out inside the allocation-free call"
     torch.cuda.synchronize()
     assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
     got = out.read(oracle).reshape(p.y_shape)  # also checks the guard bands
@@ -51,4 +53,16 @@ def test_static_scratch_refuses_problems_beyond_its_size(pkg, orc):
         pkg.conv_forward_static(gu.pkg_problem(pkg, big), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), 0)
     assert e.value.code == pkg.WORKSPACE_TOO_SMALL
     assert "bytes of scratch" in str(e.value)
+    torch.cuda.synchronize()
+
+
+def test_static_scratch_call_refuses_a_fused_residual(pkg, orc):
+    """The allocation-free call has no residual operand: the flag is refused before anything is launched."""
+    import torch
+    p = orc.Problem.P(2, 32, 8, 8, 32, 3, 3, 1, 1, 1, 1, precision=orc.FP16, bias=True, relu=True)
+    t = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    with pytest.raises(pkg.GieError) as e:
+        pkg.conv_forward_static(gu.pkg_problem(pkg, p, pkg.FLAG_RESIDUAL | pkg.FLAG_OUTPUT_NHWC), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+                                t.data_ptr(), 0)
+    assert e.value.code == pkg.UNSUPPORTED
     torch.cuda.synchronize()
