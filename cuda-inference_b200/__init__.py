@@ -78,6 +78,7 @@ def lib() -> C.CDLL:
         L.gieb_conv_plan_prepacked_weight_bytes.argtypes = [vp, C.POINTER(C.c_uint64)]
         L.gieb_conv_plan_prepack_weights.argtypes = [vp, vp, vp, vp]
         L.gieb_conv_launch_fused.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, vp]
+        L.gieb_conv_launch_stages.argtypes = [vp, C.c_uint, vp, vp, vp, vp, vp, sz, vp]
         L.gieb_conv_time_stages.argtypes = [vp, vp, vp, vp, vp, vp, sz, vp, i32, C.POINTER(C.c_float)]
         L.gieb_conv_forward_static.argtypes = [C.POINTER(ConvDesc), C.POINTER(ConvCfg), vp, vp, vp, vp, vp]
         L.gieb_conv_plan_device_status.argtypes = [vp, C.POINTER(C.c_uint32)]
@@ -193,6 +194,12 @@ class ConvPlan:
         """launch() with a residual tensor (shape, layout and type of y) added before the activation; for plans whose
         problem carries FLAG_RESIDUAL."""
         check(lib().gieb_conv_launch_fused(self._h, x, w, bias, residual, y, workspace, workspace_bytes, stream))
+
+    def launch_stages(self, stage_mask: int, x: int, w: int, bias: int | None, y: int, workspace: int | None, workspace_bytes: int,
+                      stream: int = 0) -> None:
+        """launch() restricted to some stages (bit 0 repack + prepack, bit 1 convolution kernel, bit 2 split-K reduction);
+        without bit 0 the workspace must hold the repacked tensors of an earlier full launch.  For measurements."""
+        check(lib().gieb_conv_launch_stages(self._h, stage_mask, x, w, bias, y, workspace, workspace_bytes, stream))
 
     def time_stages(self, x, w, bias, y, workspace, workspace_bytes, stream=0, iters=100):
         """Average milliseconds per call of (repack + prepack, convolution kernel, split-K reduction)."""

@@ -44,11 +44,24 @@ def candidate_cfgs(out_channels: int):
             if tile_n > 64 and tile_n // 2 >= out_channels:
                 continue
             for stages in (2, 3, 4, 6):
-                cfgs.append(dict(tile_m=tile_m, tile_n=tile_n, stages=stages))
+                cfgs.append(dict(tile_m=tile_m, tile_n=tile_n, stages=stages, cta_pair=1))
+    for tile_n in (128, 256):  # 256-pixel tiles computed by CTA pairs (the ring takes what shared memory is left)
+        if tile_n // 2 < out_channels:
+            cfgs.append(dict(tile_n=tile_n, cta_pair=2))
     return cfgs
 
 
 _TUNED: dict = {}  # (problem fields, flags) -> best cfg kwargs (or None), per process
+
+
+def tuned_configs() -> dict:
+    """The configurations measured so far in this process (picklable: send it to the other replicas)."""
+    return dict(_TUNED)
+
+
+def set_tuned_configs(table: dict) -> None:
+    """Adopts configurations measured elsewhere (rank 0 of a multi-GPU run), so that every replica runs the same kernels."""
+    _TUNED.update(table)
 
 
 class ConvChain:
@@ -57,7 +70,8 @@ class ConvChain:
         """weights: optional list of (w, b) host numpy arrays in storage bit patterns per convolution, in the order of
         resnet50_chain (tests); when None, weights are generated on the device from `seed` + layer index with the
         benchmark distributions.
-        layout "nchw": every tensor NCHW, every layer repacks (the reference API's contract, layer by layer).
+        layout "nchw": every tensor NCHW (the reference API's tensor contract, layer by layer); the weights, which the chain
+        owns, are converted once at construction, so a layer's repack launch rearranges activations only.
         layout "nhwc": the input image stays NCHW; every later tensor is channel-contiguous, weights are prepacked once
         at construction, and each block's residual add + ReLU runs inside the epilogue of its last convolution
         (no repack launches, no add launches).
@@ -73,6 +87,8 @@ class ConvChain:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         base_ops, self.slot_shapes = resnet50_chain(batch, precision, image)
         nhwc = layout == "nhwc"
+        self.base_ops = base_ops  # the unfused layer list (convolutions, max-pool, residual adds)
+        self.oihw_weights = []    # OIHW weights per entry of self.convs, as generated (the nhwc layout launches converted copies)
         base_relu = {op.layer: op.relu for op in base_ops if op.kind == "conv"}
         self.ops = fuse_residuals(base_ops) if nhwc else base_ops
         self.flops = chain_flops(self.ops)
@@ -84,7 +100,8 @@ class ConvChain:
                 continue
             s = op.shape
             li = op.layer
-            flags = 0
+            # the chain owns its weights: they are converted once, here, to the layout each plan's kernel reads
+            flags = FLAG_WEIGHTS_PREPACKED
             if nhwc:
                 flags = FLAG_OUTPUT_NHWC | FLAG_WEIGHTS_PREPACKED
                 if op.src != 0:
@@ -105,10 +122,10 @@ class ConvChain:
                 bound = layer_weight_bound(s, base_relu[li])
                 w = ((torch.rand(s.w_elems, device=self.device, generator=g) * 2 - 1) * bound).to(self.dtype)
                 b = ((torch.rand(s.out_channels, device=self.device, generator=g) * 2 - 1) * 0.1).to(self.dtype)
-            if nhwc:  # static weights: converted once, here, to the layout the plan's kernel reads
-                wp = torch.empty(plan.prepacked_weight_bytes // 2, dtype=self.dtype, device=self.device)
-                plan.prepack_weights(w.data_ptr(), wp.data_ptr(), torch.cuda.current_stream().cuda_stream)
-                w = wp
+            self.oihw_weights.append(w)
+            wp = torch.empty(plan.prepacked_weight_bytes // 2, dtype=self.dtype, device=self.device)
+            plan.prepack_weights(w.data_ptr(), wp.data_ptr(), torch.cuda.current_stream().cuda_stream)
+            w = wp
             self.convs.append((op, plan, w, b))
             ws_bytes = max(ws_bytes, plan.workspace_bytes)
         torch.cuda.current_stream().synchronize()

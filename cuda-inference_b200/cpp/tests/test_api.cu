@@ -11,6 +11,7 @@
 
 #include <fstream>
 
+#include "gie_b200_family.h"
 #include "gpu_inference/autotuner.h"
 #include "gpu_inference/cuda_graph.h"
 #include "gpu_inference/fused_ops.h"
@@ -134,7 +135,7 @@ CASE(forward_api_end_to_end_with_validation) {
 // ---------------------------------------------------------------------------------------------------------------
 CASE(selection_routes_by_precision_and_honours_forced_kernels) {
   const DeviceInfo& dev = DeviceInfo::current();
-  EXPECT(dev.supports_tcgen05());
+  EXPECT(dev.cc_major == 10);  // the family is sm_100a code
   const Conv2DParams g = ts::geom(4, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1);
   Conv2DOptions opt;
   Selection s = Dispatcher::select(ts::problem(g, Precision::kFp16, true, true), dev, opt);
@@ -165,7 +166,7 @@ CASE(selection_routes_by_precision_and_honours_forced_kernels) {
   // names, string round trips
   EXPECT(backend_from_string("tensor_core") == Backend::kTensorCore && precision_from_string("bf16") == Precision::kBf16);
   EXPECT_THROWS(precision_from_string("fp8"), StatusCode::kInvalidArgument);
-  EXPECT(std::string(to_string(StatusCode::kWorkspaceTooSmall)) == "workspace_too_small");
+  EXPECT(std::string(to_string(StatusCode::kWorkspaceTooSmall)) == "WorkspaceTooSmall");
 }
 
 CASE(plan_cache_reuses_plans) {
@@ -181,6 +182,18 @@ CASE(plan_cache_reuses_plans) {
   const double first = std::chrono::duration<double, std::micro>(t1 - t0).count();
   const double later = std::chrono::duration<double, std::micro>(t2 - t1).count() / 100.0;
   EXPECT_MSG(later < first, "cached look-ups must be cheaper than plan creation");
+}
+
+CASE(device_status_of_live_plans_is_clear_after_forward_calls) {
+  // the family's own accessor: no bounded device-side wait has run out in any plan that is still alive
+  const ConvProblem prob = ts::problem(ts::geom(2, 32, 12, 12, 48, 3, 3, 1, 1, 1, 1), Precision::kFp16, true, true);
+  ts::Bundle b = ts::make_bundle(prob, 77, Distribution::kUniform);
+  bool ran = false;
+  const ErrorMetrics m = ts::run_kernel(*find_kernel("b200_tc_fp16_auto"), b, &ran, nullptr);
+  EXPECT(ran && m.passed());
+  auto plan = ExecutionPlan::create(prob, *find_kernel("b200_tc_fp16_256x128x64_s6_sk1_pair"));  // stays alive across the query
+  GIE_CUDA_CHECK(cudaDeviceSynchronize());
+  EXPECT(kernels::b200_device_status() == 0u);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -544,7 +557,6 @@ void inject_faulty_entries() {
     k.num_blocks = &one_block;
     k.persistent_bytes = &no_bytes;
     k.create_state = &no_state;
-    k.estimate_us = &instant;
     k.launch = which == 0 ? &launch_zeros : &launch_throws;
     kernel_registry_for_testing().push_back(k);
   }

@@ -108,6 +108,7 @@ struct Resolved {
   int eff_in_w, eff_kernel_w, eff_stride_w, eff_pad_w;
   double est_cycles;  // the cost model's estimate for the chosen configuration (SM cycles; 0 on the FP32 path)
   int tma_epilogue;  // channel-contiguous output staged in shared memory and written by TMA stores
+  int nchw_stage;    // NCHW output transposed through 1 KiB of shared memory per epilogue warp and written as 4..16-byte vectors
   int reduce;  // 1 workspace partials + reduction launch, 2 cluster (distributed shared memory); 0 when split_k == 1
   int c_padded, kb_per_tap, total_kb, kb_per_split;
   int tiles_m, tiles_n;
@@ -185,7 +186,7 @@ double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, i
   const int real_split = ceil_div(total_kb, kb_per_split);
   const int64_t ctas = int64_t(ceil_div(g.pixels, tile_m)) * ceil_div(d.out_channels, tile_n) * real_split;
   const int stages = pick_stages(tile_m, tile_n, tile_k, kb_per_split, ctas);
-  const size_t smem = conv_tc_smem_bytes(tile_m, tile_n, tile_k, stages, false);
+  const size_t smem = conv_tc_smem_bytes(tile_m, tile_n, tile_k, stages, 0);
   if (smem > kMaxDynamicSmem) return 1e300;
   const int mh = tile_m / kTileM;
   const int resident = resident_ctas(tile_m, tile_n, smem);
@@ -414,19 +415,49 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   // Channel-contiguous output goes through shared-memory boxes and TMA stores when the rows of the [pixels][O] matrix
   // are 16-byte multiples, rows are numbered by pixel (not the direct-NCHW route) and each CTA finishes its tiles alone.
   r->tma_epilogue = (d.flags & GIEB_FLAG_OUTPUT_NHWC) && d.out_channels % 8 == 0 && r->variant != 2 && r->split_k == 1;
-  const size_t epi_smem = r->tma_epilogue ? conv_tc_epilogue_staging_bytes(r->tile_n) : 0;
-  int stages = c.stages ? c.stages
-               : r->pair ? pick_pair_stages(r->tile_n, r->tile_k, r->kb_per_split, epi_smem)
-                         : pick_stages(r->tile_m, r->tile_n, r->tile_k, r->kb_per_split, int64_t(r->tiles_m) * r->tiles_n * r->split_k, epi_smem);
-  // Activations streamed once from DRAM (direct-NCHW route) with a long reduction: one CTA per SM with a deep ring
-  // keeps more loads in flight than two shallow ones (measured on 512 -> 128 channels at 28x28: 17.5 vs 18.4 us).
-  if (!c.stages && !r->pair && r->variant == 2 && r->kb_per_split >= 8) {
-    const size_t sb = stage_bytes_of(r->tile_m, r->tile_n, r->tile_k);
-    if (3072 + 1024 + 6 * sb + epi_smem <= kMaxDynamicSmem) stages = 6;
-  }
+  // NCHW output of a 16-bit problem that each CTA finishes alone: the epilogue warps transpose their 32-pixel x 16-channel
+  // pieces through shared memory (1 KiB per warp) so that every store instruction writes whole runs of one channel.
+  bool nchw_stage = !tf32 && !(d.flags & (GIEB_FLAG_OUTPUT_NHWC | GIEB_FLAG_RESIDUAL)) && r->split_k == 1 && g.pq % 2 == 0;
+  const int64_t total_tiles = int64_t(r->tiles_m) * r->tiles_n * r->split_k;
+  auto stages_for = [&](size_t epi_smem) {
+    int st = c.stages ? c.stages
+             : r->pair ? pick_pair_stages(r->tile_n, r->tile_k, r->kb_per_split, epi_smem)
+                       : pick_stages(r->tile_m, r->tile_n, r->tile_k, r->kb_per_split, total_tiles, epi_smem);
+    // Activations streamed once from DRAM (direct-NCHW route) with a long reduction: one CTA per SM with a deep ring
+    // keeps more loads in flight than two shallow ones (measured on 512 -> 128 channels at 28x28: 17.5 vs 18.4 us).
+    if (!c.stages && !r->pair && r->variant == 2 && r->kb_per_split >= 8) {
+      const size_t sb = stage_bytes_of(r->tile_m, r->tile_n, r->tile_k);
+      if (3072 + 1024 + 6 * sb + epi_smem <= kMaxDynamicSmem) st = 6;
+    }
+    return st;
+  };
+  // A CTA that has its SM to itself drains its accumulators with 16 warps instead of 8: always for 256-column tiles
+  // (measured 2-7 % per step), for 128-column tiles only when the CTA has a single tile, whose epilogue nothing hides
+  // (with several tiles per CTA the extra polling warps cost more than the last epilogue gains).
+  auto epi_warps_for = [&](size_t smem) {
+    if (r->pair) return conv_tc_pair_epi_warps(r->tile_n);
+    const bool alone = resident_ctas(r->tile_m, r->tile_n, smem) == 1;
+    const bool single_tile = total_tiles <= kNumSms;
+    return (alone && (r->tile_n >= 256 || (r->tile_n >= 128 && single_tile && best_mode != 2))) ? 16 : 8;
+  };
+  size_t epi_smem = r->tma_epilogue ? conv_tc_epilogue_staging_bytes(r->tile_n) : (nchw_stage ? size_t(8) * 1024 : 0);
+  int stages = stages_for(epi_smem);
   if (stages < 2 || stages > kMaxStages) return no("stages must be in [2, 8]");
+  r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, epi_smem, r->pair != 0);
+  r->epi_warps = epi_warps_for(r->smem);
+  if (nchw_stage && r->epi_warps == 16) {  // sixteen warps stage 16 KiB
+    epi_smem = size_t(16) * 1024;
+    stages = stages_for(epi_smem);
+    r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, epi_smem, r->pair != 0);
+  }
+  if (nchw_stage && r->smem > kMaxDynamicSmem) {  // a ring depth that was asked for leaves no room: plain stores
+    nchw_stage = false;
+    stages = stages_for(0);
+    r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, 0, r->pair != 0);
+    r->epi_warps = epi_warps_for(r->smem);
+  }
+  r->nchw_stage = nchw_stage;
   r->stages = stages;
-  r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, r->tma_epilogue != 0, r->pair != 0);
   if (r->smem > kMaxDynamicSmem) return no("configuration needs more shared memory than one CTA may have (227 KiB)");
   // A CTA of a pair keeps its SM to itself (the tensor-memory allocation of a pair spans two SMs): a short ring still
   // asks for more than half of an SM's shared memory.
@@ -439,16 +470,6 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   // how the split-K slices are summed
   if (c.reduce < 0 || c.reduce > 2) return no("reduce must be 0 (auto), 1 (workspace) or 2 (cluster)");
   r->reduce = r->split_k > 1 ? best_mode : 0;
-  // A CTA that has its SM to itself drains its accumulators with 16 warps instead of 8: always for 256-column tiles
-  // (measured 2-7 % per step), for 128-column tiles only when the CTA has a single tile, whose epilogue nothing hides
-  // (with several tiles per CTA the extra polling warps cost more than the last epilogue gains).
-  if (r->pair) {
-    r->epi_warps = conv_tc_pair_epi_warps(r->tile_n);
-  } else {
-    const bool alone = resident_ctas(r->tile_m, r->tile_n, r->smem) == 1;
-    const bool single_tile = int64_t(r->tiles_m) * r->tiles_n * r->split_k <= kNumSms;
-    r->epi_warps = (alone && (r->tile_n >= 256 || (r->tile_n >= 128 && single_tile && r->reduce != 2))) ? 16 : 8;
-  }
   if (r->reduce == 2 && !cluster_reduce_ok(r->tile_m, r->tile_n, r->tile_k, stages, r->split_k))
     return no("cluster reduction needs tile_m 128, split_k 2, 4 or 8 dividing tile_n / 32, and a ring that holds the received slices");
   r->ws_part = r->split_k > 1 && r->reduce == 1 ? align256(size_t(r->split_k) * size_t((g.y_elems + 3) & ~int64_t(3)) * 4) : 0;
@@ -613,7 +634,8 @@ int encode_epilogue_map(const gieb_conv_plan* pl, const void* ptr, CUtensorMap* 
 // `ev`, when given, receives four stage marks: before the repack, before the convolution kernel, after it, and
 // after the split-K reduction (LaunchArgs::stage_events analogue, include/gpu_inference/kernel_registry.h:38-40).
 int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
-                cudaStream_t st, cudaEvent_t* ev = nullptr, const void* residual = nullptr) {
+                cudaStream_t st, cudaEvent_t* ev = nullptr, const void* residual = nullptr, unsigned stage_mask = 7u) {
+  // stage_mask (measurement only): bit 0 = layout repack + weight prepack, bit 1 = convolution kernel, bit 2 = split-K reduction
   if (pl == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null plan");
   const gieb_conv_desc& d = pl->desc;
   const Resolved& r = pl->r;
@@ -672,7 +694,9 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   if (st_maps != GIEB_OK) return st_maps;
 
   if (ev) GIEB_CUDA(cudaEventRecord(ev[0], st));
-  if (d.precision == GIEB_TF32) {  // FP32 tensors rounded to TF32 while they are repacked (two launches)
+  if (!(stage_mask & 1u)) {
+    // the workspace already holds the repacked tensors of an earlier full launch
+  } else if (d.precision == GIEB_TF32) {  // FP32 tensors rounded to TF32 while they are repacked (two launches)
     GIEB_CUDA(repack_tf32_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded / 2, st));
     GIEB_CUDA(repack_tf32_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded / 2, st));
   } else if (r.variant == 5) {  // row gather of the activations (and of the weights unless they come gathered)
@@ -715,6 +739,11 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.out_nhwc = (d.flags & GIEB_FLAG_OUTPUT_NHWC) ? 1 : 0;
   p.y = y;
   p.partial = part;
+  if (r.nchw_stage && part == nullptr && residual == nullptr && !p.out_nhwc) {  // widest pixel run the plane size and y's alignment allow
+    const uintptr_t ya = reinterpret_cast<uintptr_t>(y);
+    const int pq = pl->g.pq;
+    p.out_vec = (pq % 8 == 0 && ya % 16 == 0) ? 8 : ((pq % 4 == 0 && ya % 8 == 0) ? 4 : ((pq % 2 == 0 && ya % 4 == 0) ? 2 : 0));
+  }
   p.status = pl->d_status;
   p.wait_limit = pl->wait_limit;
   p.debug_skip = pl->debug_skip;
@@ -750,10 +779,11 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
       p.res_tma = 1;
     }
   }
-  if (r.pair) GIEB_CUDA(conv_tc_pair_launch(r.tile_n, r.tile_k, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
+  if (!(stage_mask & 2u)) {
+  } else if (r.pair) GIEB_CUDA(conv_tc_pair_launch(r.tile_n, r.tile_k, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
   else GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
-  if (r.reduce == 1)
+  if (r.reduce == 1 && (stage_mask & 4u))
     GIEB_CUDA(splitk_reduce_launch(part, r.split_k, pl->g.y_elems, d.out_channels, pl->g.pq, bias, p.bias_fp32, d.relu, p.is_tf32 ? 2 : p.is_bf16, residual,
                                    p.out_nhwc, y, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[3], st));
@@ -881,6 +911,14 @@ int gieb_conv_plan_prepack_weights(const gieb_conv_plan* plan, const void* w, vo
 int gieb_conv_launch_fused(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, const void* residual, void* y,
                            void* workspace, size_t workspace_bytes, void* stream) {
   return launch_impl(plan, x, w, bias, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), nullptr, residual);
+}
+
+int gieb_conv_launch_stages(const gieb_conv_plan* plan, unsigned stage_mask, const void* x, const void* w, const void* bias, void* y,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+  if (stage_mask == 0 || stage_mask > 7u) return fail(GIEB_INVALID_ARGUMENT, "stage_mask is a non-empty mask of bits 0 (repack), 1 (convolution), 2 (reduction)");
+  if (plan != nullptr && plan->r.variant == 3 && !(stage_mask & 2u)) return GIEB_OK;  // the FP32 path is one kernel
+  return launch_impl(plan, x, w, bias, y, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), nullptr, nullptr,
+                     plan != nullptr && plan->r.variant == 3 ? 7u : stage_mask);
 }
 
 int gieb_conv_time_stages(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y, void* workspace,

@@ -142,9 +142,9 @@ size_t conv_tc_epilogue_staging_bytes(int tile_n) { return size_t(8) * (tile_n >
 
 int conv_tc_threads(int epi_warps) { return 32 * (kProducerWarps + 1 + epi_warps); }
 
-size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, bool tma_epilogue, bool pair) {
+size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, size_t epilogue_bytes, bool pair) {
   const size_t rows = pair ? size_t(kTileM) + tile_n / 2 : size_t(tile_m) + tile_n;  // operand rows one CTA stages per slab
-  return 1024 + kCtrlBytes + size_t(stages) * rows * tile_k * 2 + (tma_epilogue ? conv_tc_epilogue_staging_bytes(tile_n) : 0);
+  return 1024 + kCtrlBytes + size_t(stages) * rows * tile_k * 2 + epilogue_bytes;
 }
 
 cudaError_t conv_tc_prepare(int tile_m, int tile_n, int tile_k, int epi_warps, size_t smem_bytes) {

@@ -158,6 +158,66 @@ __device__ __forceinline__ void chunk_to_staging(const uint32_t (&v)[32], const 
   }
 }
 
+// NCHW output through a per-warp staging tile: the 32 lanes of the warp hold 32 consecutive pixels and, in v, 32 consecutive
+// channels of each.  Sixteen channels at a time are rounded and written to `stage` as [channel][pixel] (a lane writes two
+// bytes per channel: 64 contiguous bytes per warp instruction, no bank conflict), then read back as vectors of V pixels of
+// one channel and stored: one store instruction covers 32 / (32 / V) ... whole runs of 2 V bytes instead of 32 two-byte pieces.
+// `gdst` = address of (this lane's pixel group, first channel of the chunk); channels are `cstride` elements apart.
+// Lane l owns pixel group l % (32 / V) and the channel rows l / (32 / V) + k * V of each sixteen.
+template <typename T, int V, bool RELU>
+__device__ __forceinline__ void store_chunk_staged(const uint32_t (&v)[32], const float* __restrict__ bias, T* stage, int lane, T* gdst,
+                                                   int64_t cstride, bool group_ok, int nvalid) {
+  constexpr int GROUPS = 32 / V;      // pixel groups per staged row: 4, 8 or 16
+  constexpr int RSTEP = 32 / GROUPS;  // channel rows one pass of the warp covers: 8, 4 or 2
+  using Vec = typename std::conditional<V == 8, uint4, typename std::conditional<V == 4, uint2, uint32_t>::type>::type;
+  const int g = lane % GROUPS, r0 = lane / GROUPS;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    // two channels per conversion; the ReLU is applied to the rounded pair (rounding is monotonic and keeps zero)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float2 b = reinterpret_cast<const float2*>(bias)[half * 8 + j];
+      const float a0 = __uint_as_float(v[half * 16 + 2 * j]) + b.x;
+      const float a1 = __uint_as_float(v[half * 16 + 2 * j + 1]) + b.y;
+      if constexpr (std::is_same<T, __half>::value) {
+        __half2 o = __floats2half2_rn(a0, a1);
+        if (RELU) o = __hmax2(o, __half2half2(__ushort_as_half(0)));
+        stage[(2 * j) * 32 + lane] = __low2half(o);
+        stage[(2 * j + 1) * 32 + lane] = __high2half(o);
+      } else {
+        __nv_bfloat162 o = __floats2bfloat162_rn(a0, a1);
+        if (RELU) o = __hmax2(o, __bfloat162bfloat162(__ushort_as_bfloat16(0)));
+        stage[(2 * j) * 32 + lane] = __low2bfloat16(o);
+        stage[(2 * j + 1) * 32 + lane] = __high2bfloat16(o);
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 16 / RSTEP; ++i) {
+      const int row = r0 + i * RSTEP;
+      const int c = half * 16 + row;
+      const Vec q = *reinterpret_cast<const Vec*>(stage + row * 32 + g * V);
+      if (group_ok && c < nvalid) *reinterpret_cast<Vec*>(gdst + int64_t(c) * cstride) = q;
+    }
+    __syncwarp();
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_chunk_staged(const uint32_t (&v)[32], const float* bias, T* stage, int lane, T* gdst, int64_t cstride,
+                                                   bool group_ok, int nvalid, int vec, int relu) {
+  if (vec == 8) {
+    if (relu) store_chunk_staged<T, 8, true>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
+    else store_chunk_staged<T, 8, false>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
+  } else if (vec == 4) {
+    if (relu) store_chunk_staged<T, 4, true>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
+    else store_chunk_staged<T, 4, false>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
+  } else {
+    if (relu) store_chunk_staged<T, 2, true>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
+    else store_chunk_staged<T, 2, false>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
+  }
+}
+
 // dst / res point at the first element of the chunk for this row; consecutive channels are `stride` elements apart
 // (P*Q for NCHW, 1 for channel-contiguous output).
 template <typename T>
@@ -574,6 +634,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       };
       if (p.out_tma) prefetch_residual(0);
 
+      // Row decode and output addresses, done while the main loop still runs (the accumulator is not needed for them).
+      const bool staged = p.out_vec != 0 && p.partial == nullptr;  // warp-uniform: NCHW stores through the staging tile
+      const int64_t cstride = p.out_nhwc ? 1 : p.pq;
+      bool m_ok_h[MH], g_ok_h[MH];
+      int64_t base_h[MH], gbase_h[MH];
+#pragma unroll
+      for (int h = 0; h < MH; ++h) {
+        int img, pix;
+        decode_row(m0 + h * kTileM + quad * 32 + lane, m_ok_h[h], img, pix);
+        base_h[h] = p.out_nhwc ? (int64_t(img) * p.pq + pix) * p.out_channels + n0 : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
+        g_ok_h[h] = false;
+        gbase_h[h] = 0;
+        if (staged) {  // this lane's group of out_vec pixels within the warp's 32 (a group never straddles an image)
+          const int gsh = p.out_vec == 8 ? 2 : (p.out_vec == 4 ? 3 : 4);  // log2 of the groups per 32 pixels
+          decode_row(m0 + h * kTileM + quad * 32 + (lane & ((1 << gsh) - 1)) * p.out_vec, g_ok_h[h], img, pix);
+          gbase_h[h] = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
+        }
+      }
+
       const bool ok = ptx::mbar_wait(&acc_full[buf], acc_phase, p.status, kStatusEpilogueTimeout, p.wait_limit);
       __syncwarp();
       ptx::tc_fence_after_sync();
@@ -617,7 +696,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         int img, pix;
         decode_row(m, m_ok, img, pix);
         // element offset of (this row, channel n0) and the distance between consecutive channels
-        const int64_t cstride = p.out_nhwc ? 1 : p.pq;
         const int64_t base = p.out_nhwc ? (int64_t(img) * p.pq + pix) * p.out_channels + n0
                                         : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
         for (int chunk = par; chunk < BN / 32; chunk += EG) {
@@ -655,14 +733,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         break;  // one tile per CTA in this mode
       }
       float* part = p.partial ? p.partial + int64_t(z) * ((p.y_elems + 3) & ~int64_t(3)) : nullptr;
-      for (int h = 0; h < halves; ++h) {
-        const int m = m0 + h * kTileM + quad * 32 + lane;
-        bool m_ok;
-        int img, pix;
-        decode_row(m, m_ok, img, pix);
-        const int64_t cstride = p.out_nhwc ? 1 : p.pq;
-        const int64_t base = p.out_nhwc ? (int64_t(img) * p.pq + pix) * p.out_channels + n0
-                                        : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
+#pragma unroll
+      for (int h = 0; h < MH; ++h) {
+        if (h >= halves) break;
+        const bool m_ok = m_ok_h[h], g_ok = g_ok_h[h];
+        const int64_t base = base_h[h], gbase = gbase_h[h];
         if (p.out_tma && h > 0) prefetch_residual(h);
 #pragma unroll 1
         for (int chunk = par; chunk < BN / 32; chunk += EG) {
@@ -670,6 +745,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           uint32_t v[32];
           ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(h * BN + chunk * 32), v);
           ptx::tmem_ld_wait();
+          if (staged) {
+            const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
+            const int64_t goff = gbase + int64_t(chunk * 32) * p.pq;
+            if (p.is_bf16) {
+              store_chunk_staged(v, bias_t + chunk * 32, reinterpret_cast<__nv_bfloat16*>(epi_base + we * 1024), lane,
+                                 static_cast<__nv_bfloat16*>(p.y) + goff, int64_t(p.pq), g_ok, nvalid, p.out_vec, p.relu);
+            } else {
+              store_chunk_staged(v, bias_t + chunk * 32, reinterpret_cast<__half*>(epi_base + we * 1024), lane,
+                                 static_cast<__half*>(p.y) + goff, int64_t(p.pq), g_ok, nvalid, p.out_vec, p.relu);
+            }
+            continue;
+          }
           if (p.out_tma) {
             const int k = chunk / EG;
             uint8_t* box = stage_box(k);

@@ -130,6 +130,10 @@ struct ConvTcParams {
   const void* residual;  // optional tensor of the output's shape, layout and type, added before the activation
   int out_nhwc;          // 0: y (and residual, partials) are NCHW; 1: channel-contiguous [B][P][Q][O]
   int out_tma, res_tma;  // channel-contiguous output leaves through TMA stores / the residual arrives through TMA loads
+  // NCHW output of 16-bit type: 0 = one 2-byte store per element; 8 / 4 / 2 = the epilogue warps transpose their pieces
+  // through shared memory and store runs of that many pixels (16 / 8 / 4 bytes) of one channel.  Needs P*Q % out_vec == 0,
+  // y aligned to 2 * out_vec bytes and 1 KiB of staging per epilogue warp behind the ring.
+  int out_vec;
   void* y;            // output in the storage type (split_k == 1 or cluster reduction)
   float* partial;     // [splits][B*O*P*Q] FP32 partial sums in the output's element order (workspace reduction), else null
   uint32_t* status;
@@ -138,9 +142,9 @@ struct ConvTcParams {
 };
 
 // tile_m is 128 or 256 output pixels per CTA (one or two TMEM accumulators sharing each weight tile).
-// tma_epilogue: add the staging boxes of the TMA-store epilogue (channel-contiguous output).
 // pair: the tile belongs to a CTA pair (tile_m = 256), each CTA stages 128 activation rows and tile_n / 2 weight rows.
-size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, bool tma_epilogue, bool pair = false);
+// epilogue_bytes: staging of the epilogue behind the ring (TMA-store boxes, or the NCHW transposition tiles).
+size_t conv_tc_smem_bytes(int tile_m, int tile_n, int tile_k, int stages, size_t epilogue_bytes, bool pair = false);
 size_t conv_tc_epilogue_staging_bytes(int tile_n);
 // epi_warps: 8, or 16 for CTAs that have an SM to themselves (tile_n >= 128 only)
 int conv_tc_threads(int epi_warps);

@@ -168,6 +168,14 @@ GIEB_API int gieb_conv_launch_fused(const gieb_conv_plan* plan, const void* x, c
 GIEB_API int gieb_conv_time_stages(const gieb_conv_plan* plan, const void* x, const void* w, const void* bias, void* y,
                                    void* workspace, size_t workspace_bytes, void* stream, int iters, float* stage_ms);
 
+/* Measurement helper (the stage_events hook again, include/gpu_inference/kernel_registry.h:38-40, in a form that can
+ * be captured into a CUDA graph): gieb_conv_launch restricted to the stages in `stage_mask` -- bit 0 = layout repack +
+ * weight prepack, bit 1 = convolution kernel, bit 2 = split-K reduction launch.  A call without bit 0 reads the
+ * repacked tensors a previous full launch left in `workspace`; a benchmark replays graphs of single-stage calls to
+ * time one kernel back to back.  Not for plans with a fused residual. */
+GIEB_API int gieb_conv_launch_stages(const gieb_conv_plan* plan, unsigned stage_mask, const void* x, const void* w,
+                                     const void* bias, void* y, void* workspace, size_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference.  One-shot forward call for callers that are not allowed to allocate device memory
  * -- code running inside someone else's memory budget (a serving process whose pool owns the whole GPU, a plug-in
  * loaded into a host application, a real-time loop) where cudaMalloc either fails or stalls everything on the device.

@@ -332,6 +332,14 @@ class Reference:
         L.ref_compare.argtypes = [C.POINTER(ConvDesc), C.c_int] + [C.POINTER(C.c_float)] * 3 + [C.c_int64, C.POINTER(C.c_double)]
         L.ref_tol.argtypes = [C.POINTER(ConvDesc), C.c_int, C.c_double, C.c_double]
         L.ref_tol.restype = C.c_double
+        L.ref_set_num_threads.argtypes = [C.c_int]
+
+    def set_num_threads(self, n: int) -> None:
+        """OpenMP threads of the reference's CPU convolution (an OpenMP loop over the outputs)."""
+        self.lib.ref_set_num_threads(n)
+
+    def num_threads(self) -> int:
+        return self.lib.ref_num_threads()
 
     @staticmethod
     def available() -> bool:

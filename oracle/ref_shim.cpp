@@ -7,6 +7,7 @@
 //
 // The four stubs at the bottom satisfy the linker for Conv2D::forward's dependencies (dispatcher, execution
 // plan, device query); the oracle path never reaches them and they throw if called.
+#include <omp.h>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -140,6 +141,13 @@ void ref_compare(const Desc* d, int intermediate_rounding, const float* test, co
   out[4] = m.max_abs; out[5] = m.mean_abs; out[6] = m.rms; out[7] = m.max_rel; out[8] = m.frac_over_tol;
   out[9] = m.worst_tol_ratio;
 }
+
+// The reference's CPU convolution is an OpenMP loop over the outputs (src/cpu/cpu_reference.cpp:23): these set and
+// report the number of threads it will use, whatever OMP_NUM_THREADS a launcher exported.
+void ref_set_num_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
+int ref_num_threads(void) { return omp_get_max_threads(); }
 
 double ref_tol(const Desc* d, int intermediate_rounding, double ref, double scale) {
   return gie::TolerancePolicy::for_problem(to_problem(*d), intermediate_rounding != 0).tol(ref, scale);
