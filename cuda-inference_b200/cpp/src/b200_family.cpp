@@ -46,11 +46,13 @@ gieb_conv_desc to_desc(const ConvProblem& pr) {
 
 [[noreturn]] void rethrow(int status) { throw Error(static_cast<StatusCode>(status), gieb_last_error()); }
 
-// Live plans, so that b200_device_status() can read their status words.
-std::mutex g_live_mu;
+// Live plans, so that b200_device_status() can read their status words.  Both objects are never destroyed: plans held
+// by the process-lifetime plan cache (src/runtime/conv2d.cpp:125-128) are released during static destruction, in an order
+// this file does not control.
+std::mutex& g_live_mu = *new std::mutex;
 std::set<gieb_conv_plan*>& live_plans() {
-  static std::set<gieb_conv_plan*> s;
-  return s;
+  static std::set<gieb_conv_plan*>* s = new std::set<gieb_conv_plan*>;
+  return *s;
 }
 
 struct PlanHandle {

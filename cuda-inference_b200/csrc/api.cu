@@ -1118,54 +1118,6 @@ int gieb_conv_estimate_us(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, 
   return GIEB_OK;
 }
 
-int gieb_conv_reference_launch(const gieb_conv_desc* desc, const void* x, const void* w, const void* bias, float* ref, float* scale,
-                               void* stream) {
-  const int st = gieb_conv_validate(desc);
-  if (st != GIEB_OK) return st;
-  if (x == nullptr || w == nullptr || ref == nullptr || scale == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
-  if (desc->has_bias && bias == nullptr) return fail(GIEB_INVALID_ARGUMENT, "problem has a bias but no bias pointer was given");
-  if (desc->precision == GIEB_TF32) return fail(GIEB_UNSUPPORTED, "TF32 is not offered");
-  const Geometry g = geometry(*desc);
-  GIEB_CUDA(reference_conv_launch(desc->precision, x, w, desc->has_bias ? bias : nullptr, ref, scale, desc->batch, desc->in_channels,
-                                  desc->in_h, desc->in_w, desc->out_channels, desc->kernel_h, desc->kernel_w, desc->stride_h,
-                                  desc->stride_w, desc->pad_h, desc->pad_w, g.out_h, g.out_w, desc->relu, static_cast<cudaStream_t>(stream)));
-  return GIEB_OK;
-}
-
-int gieb_conv_check_output(const gieb_conv_desc* desc, const void* y, const float* ref, const float* scale, double* max_abs_err,
-                           double* frac_over_tol, int64_t* nonfinite, void* stream) {
-  const int st = gieb_conv_validate(desc);
-  if (st != GIEB_OK) return st;
-  if (y == nullptr || ref == nullptr || scale == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
-  if (desc->precision == GIEB_TF32) return fail(GIEB_UNSUPPORTED, "TF32 is not offered");
-  const Geometry g = geometry(*desc);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  unsigned long long* d_out = nullptr;
-  GIEB_CUDA(cudaMalloc(&d_out, 3 * sizeof(unsigned long long)));
-  unsigned long long h[3] = {0, 0, 0};
-  cudaError_t e = cudaMemsetAsync(d_out, 0, sizeof(h), s);
-  if (e == cudaSuccess) e = check_output_launch(desc->precision, y, ref, scale, g.y_elems, int64_t(desc->in_channels) * desc->kernel_h * desc->kernel_w, d_out, s);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(h, d_out, sizeof(h), cudaMemcpyDeviceToHost, s);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-  cudaFree(d_out);
-  if (e != cudaSuccess) return fail_cuda(e, "checking a convolution output");
-  float worst;
-  const unsigned int bits = static_cast<unsigned int>(h[2] & 0xffffffffu);
-  memcpy(&worst, &bits, sizeof(worst));
-  if (max_abs_err) *max_abs_err = double(worst);
-  if (frac_over_tol) *frac_over_tol = g.y_elems ? double(h[0]) / double(g.y_elems) : 0.0;
-  if (nonfinite) *nonfinite = int64_t(h[1]);
-  return GIEB_OK;
-}
-
-int gieb_fill_uniform(int precision, void* data, int64_t count, uint64_t seed, float lo, float hi, void* stream) {
-  if (data == nullptr || count < 0) return fail(GIEB_INVALID_ARGUMENT, "null pointer or negative count");
-  if (precision < 0 || precision > 2) return fail(GIEB_INVALID_ARGUMENT, "precision must be fp32, fp16 or bf16");
-  if (count == 0) return GIEB_OK;
-  GIEB_CUDA(fill_uniform_launch(precision, data, count, seed, lo, hi, static_cast<cudaStream_t>(stream)));
-  return GIEB_OK;
-}
-
 int gieb_add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, void* stream) {
   if (a == nullptr || b == nullptr || y == nullptr) return fail(GIEB_INVALID_ARGUMENT, "null device pointer");
   if (n <= 0) return fail(GIEB_INVALID_ARGUMENT, "element count must be positive");

@@ -200,12 +200,4 @@ cudaError_t maxpool2d_nhwc_launch(int precision, int batch, int channels, int h,
                                   void* y, cudaStream_t stream);
 cudaError_t add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, cudaStream_t stream);
 
-// Tuning support (not on the forward path): double-accumulating reference convolution, tolerance check, buffer fill.
-cudaError_t reference_conv_launch(int precision, const void* x, const void* w, const void* bias, float* ref, float* scale, int B, int C,
-                                  int H, int W, int O, int R, int S, int sh, int sw, int ph, int pw, int P, int Q, int relu,
-                                  cudaStream_t stream);
-cudaError_t check_output_launch(int precision, const void* y, const float* ref, const float* scale, int64_t n, int64_t k,
-                                unsigned long long* out3, cudaStream_t stream);
-cudaError_t fill_uniform_launch(int precision, void* p, int64_t n, uint64_t seed, float lo, float hi, cudaStream_t stream);
-
 }  // namespace gieb

@@ -258,27 +258,10 @@ GIEB_API int gieb_maxpool2d_nhwc_launch(int precision, int batch, int channels, 
                                         const void* x, void* y, void* stream);
 GIEB_API int gieb_add_relu_launch(int precision, int relu, const void* a, const void* b, void* y, int64_t n, void* stream);
 
-/* ---- support for validate-then-time tuning (src/autotuner/autotuner.cpp:60-117); not on the forward path -------- */
-
 /* estimate_kernel (src/runtime/perf_model.cpp:130-174) for this family: the library's own cycle model for the
- * configuration `cfg` (NULL = the one the heuristic picks), in microseconds.  Used to rank and prune candidates. */
+ * configuration `cfg` (NULL = the one the heuristic picks), in microseconds.  For ranking and pruning tuning candidates;
+ * validation and timing of candidates are the reference autotuner's own (src/autotuner/autotuner.cpp:60-117). */
 GIEB_API int gieb_conv_estimate_us(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, double* microseconds);
-
-/* gpu_conv2d_reference (src/runtime/reference.cu:83-93): direct convolution with double accumulation on the GPU.
- * x, w, bias in the problem's storage type (NCHW / OIHW); ref = act(conv + bias) rounded once to float, and
- * scale = sum |x*w| + |bias| per output, both float[B*O*P*Q] in NCHW order. */
-GIEB_API int gieb_conv_reference_launch(const gieb_conv_desc* desc, const void* x, const void* w, const void* bias, float* ref,
-                                        float* scale, void* stream);
-
-/* compare_outputs under TolerancePolicy::for_problem (src/runtime/reference.cu:139-205): y (storage type, NCHW) against
- * ref / scale from gieb_conv_reference_launch.  Synchronises `stream`.  A candidate passes when frac_over_tol == 0 and
- * nonfinite == 0. */
-GIEB_API int gieb_conv_check_output(const gieb_conv_desc* desc, const void* y, const float* ref, const float* scale,
-                                    double* max_abs_err, double* frac_over_tol, int64_t* nonfinite, void* stream);
-
-/* make_conv_data's role (src/runtime/testing.cu:83-86): reproducible uniform values in [lo, hi) from a counter-based
- * generator (element i depends on seed and i only), rounded to the storage type. */
-GIEB_API int gieb_fill_uniform(int precision, void* data, int64_t count, uint64_t seed, float lo, float hi, void* stream);
 
 #ifdef __cplusplus
 }
