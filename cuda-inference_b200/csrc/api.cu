@@ -239,8 +239,16 @@ double estimate_cycles_pair(const gieb_conv_desc& d, const Geometry& g, int64_t 
   return total;
 }
 
-// Whether the heuristic may choose CTA-pair tiles unasked (a configuration can always ask for them).
-constexpr bool kAutoPair = false;
+// When the heuristic chooses CTA-pair tiles unasked (a configuration can always ask for them).  Measured per layer of
+// the ResNet-50-shaped chain and on the benchmark shapes: pairs win on long reductions (sixteen 64-channel slabs or more)
+// when there is at least one full wave of pair tiles or the reduction is very long (3x3 over 256 channels and up); short
+// reductions are bound by memory or by fixed costs, where the pair's cluster launch and its two extra cluster barriers
+// cost more than the halved weight traffic returns; with few output pixels split-K inside clusters does better.
+bool auto_pair(const gieb_conv_desc& d, int64_t rows, int total_kb, int tile_k) {
+  const int kb64 = total_kb * tile_k / 64;  // reduction length in 64-channel slabs
+  if (rows < int64_t(2 * kTileM) * 16) return false;  // few pixels: split-K inside clusters fills the machine better
+  return d.out_channels >= 128 && kb64 >= 16 && (rows >= int64_t(2 * kTileM) * kNumSmPairs || kb64 >= 32);
+}
 
 }  // namespace
 
@@ -356,12 +364,14 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   int best_m = 0, best_n = 0, best_s = 0, best_mode = 0, best_pair = 0;
   const int n_opts[4] = {32, 64, 128, 256};
   // 256-pixel tiles of CTA pairs: only the workspace reduction for split-K
-  for (int ni = 1; ni < 4 && !tf32 && c.cta_pair != 1 && (c.cta_pair == 2 || kAutoPair) && (c.tile_m == 0 || c.tile_m == 256) && c.reduce != 2; ++ni) {
+  const bool pair_unasked = c.cta_pair == 0 && !tf32 && c.tile_m == 0 && c.split_k <= 1 && c.reduce == 0 && c.variant != 2 &&
+                            auto_pair(d, rows, r->total_kb, r->tile_k);
+  for (int ni = 1; ni < 4 && !tf32 && (c.cta_pair == 2 || pair_unasked) && (c.tile_m == 0 || c.tile_m == 256) && c.reduce != 2; ++ni) {
     const int tn = n_opts[ni];
     if (r->tile_n && tn != r->tile_n) continue;
     if (!r->tile_n && tn / 2 >= d.out_channels) continue;
     if (c.cta_pair != 2 && rows <= kTileM) continue;  // the peer CTA would own no pixel
-    for (int s = 1; s <= 16; ++s) {
+    for (int s = 1; s <= (pair_unasked ? 1 : 16); ++s) {
       if (c.split_k && s != c.split_k) continue;
       if (s > 1 && r->total_kb < 2 * s) break;
       if (s > 1 && size_t(s) * size_t(g.y_elems) * 4 > (size_t(1) << 31)) continue;
@@ -369,7 +379,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
       if (t < best) { best = t; best_m = 2 * kTileM; best_n = tn; best_s = s; best_mode = s > 1 ? 1 : 0; best_pair = 1; }
     }
   }
-  for (int tm = 128; tm <= 256 && c.cta_pair != 2; tm += 128) {
+  for (int tm = 128; tm <= 256 && c.cta_pair != 2 && !(pair_unasked && best_pair); tm += 128) {
     if (c.tile_m && tm != c.tile_m) continue;
     if (!c.tile_m && tm == 256 && int64_t(ceil_div(g.pixels, 256)) * ceil_div(d.out_channels, 128) < 4 * kNumSms) continue;  // big tiles only where wave quantisation is negligible
     for (int ni = 0; ni < 4; ++ni) {
