@@ -108,7 +108,7 @@ struct Resolved {
   int eff_in_w, eff_kernel_w, eff_stride_w, eff_pad_w;
   double est_cycles;  // the cost model's estimate for the chosen configuration (SM cycles; 0 on the FP32 path)
   int tma_epilogue;  // channel-contiguous output staged in shared memory and written by TMA stores
-  int nchw_stage;    // NCHW output transposed through 1 KiB of shared memory per epilogue warp and written as 4..16-byte vectors
+  int swap;          // transposed accumulator (lane = output channel): NCHW output staged per warp and written by TMA stores
   int reduce;  // 1 workspace partials + reduction launch, 2 cluster (distributed shared memory); 0 when split_k == 1
   int c_padded, kb_per_tap, total_kb, kb_per_split;
   int tiles_m, tiles_n;
@@ -181,7 +181,10 @@ bool cluster_reduce_ok(int tile_m, int tile_n, int tile_k, int stages, int split
 //  * ~4500 cycles from launch to the first MMA, ~500 + 16 per accumulator column for an epilogue, which is hidden
 //    behind the next tile's main loop when the accumulator is double-buffered or a second CTA shares the SM.
 // reduce: 0 none, 1 FP32 partials in the workspace + reduction launch, 2 cluster.
-double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, int tile_n, int tile_k, int split, int reduce, int total_kb) {
+// swap: the accumulator is transposed (the instruction's M is 128 channels, its N the tile's pixels), so the issue cost
+// follows tile_m instead of tile_n, and the epilogue is short (one TMA store per 32 x 32 box).
+double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, int tile_n, int tile_k, int split, int reduce, int total_kb,
+                       bool swap = false) {
   const int kb_per_split = ceil_div(total_kb, split);
   const int real_split = ceil_div(total_kb, kb_per_split);
   const int64_t ctas = int64_t(ceil_div(g.pixels, tile_m)) * ceil_div(d.out_channels, tile_n) * real_split;
@@ -192,12 +195,14 @@ double estimate_cycles(const gieb_conv_desc& d, const Geometry& g, int tile_m, i
   const int resident = resident_ctas(tile_m, tile_n, smem);
   const double tiles_per_sm = double((ctas + kNumSms - 1) / kNumSms);
   const double sharing = fmin(double(resident), tiles_per_sm);   // CTAs that really run side by side on an SM
-  const double mmas = double(mh) * (tile_k / 16);
-  const double pipe = mmas * (tile_n / 2.0);
-  const double issue = tile_n >= 256 ? pipe : mmas * 78.0 + 110.0;  // narrow tiles: two slabs per wait / vote / fence when they queue up
+  const int instr_n = swap ? tile_m : tile_n;                                                // N of one instruction
+  const double mmas = (swap ? double(tile_n / kTileM) : double(mh)) * (tile_k / 16);        // instructions per slab
+  const double pipe = mmas * (instr_n / 2.0);
+  const double issue = instr_n >= 256 ? pipe : mmas * 78.0 + 110.0;  // narrow instructions: two slabs per wait / vote / fence when they queue up
   const double feed = double(stage_bytes_of(tile_m, tile_n, tile_k)) / kFeedBytesPerClk;
   const double slab = fmax(fmax(pipe, feed), issue / sharing);
-  double epilogue = 500.0 + 16.0 * mh * tile_n;
+  // transposed: eight warps, ~900 cycles per 32 x 32 box (TMEM load, rounding, one TMA store issue), (tile_n / 128) * (tile_m / 32) / 2 boxes per warp
+  double epilogue = swap ? 300.0 + 900.0 * (tile_n / 128) * (tile_m / 64) : 500.0 + 16.0 * mh * tile_n;
   if (real_split > 1 && reduce == 1) epilogue *= 2.0;  // FP32 partials: twice the bytes
   const bool overlapped = sharing >= 2.0 || (mh * tile_n <= 256 && tiles_per_sm >= 2.0);
   double total = 4500.0 + tiles_per_sm * kb_per_split * slab + (overlapped ? epilogue : tiles_per_sm * epilogue);
@@ -359,9 +364,17 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
     if (c.tile_n != 0 && c.tile_n < 64) return no("CTA-pair tiles are 64, 128 or 256 output channels wide");
     if (c.reduce == 2) return no("a CTA pair is a cluster already: its split-K slices are summed through the workspace (reduce 0 or 1)");
   }
+  // NCHW output whose planes are 16-byte multiples, 16-bit types: 128- and 256-channel tiles that a CTA finishes alone
+  // keep the accumulator transposed (lane = output channel) and write their boxes with TMA stores.
+  bool swap_ok = !tf32 && !(d.flags & (GIEB_FLAG_OUTPUT_NHWC | GIEB_FLAG_RESIDUAL)) && g.pq % 8 == 0;
+  bool swap_forced = false;
+  if (const char* e = getenv("GIEB_TRANSPOSED_ACC")) {  // debugging aid: 0 = pixel-lane kernels only, 2 = transposed wherever it is possible
+    swap_ok = swap_ok && e[0] != '0';
+    swap_forced = e[0] == '2';
+  }
   // search (tile_m, tile_n, split_k, pair) unless fixed
   double best = 1e300;
-  int best_m = 0, best_n = 0, best_s = 0, best_mode = 0, best_pair = 0;
+  int best_m = 0, best_n = 0, best_s = 0, best_mode = 0, best_pair = 0, best_swap = 0;
   const int n_opts[4] = {32, 64, 128, 256};
   // 256-pixel tiles of CTA pairs: only the workspace reduction for split-K
   const bool pair_unasked = c.cta_pair == 0 && !tf32 && c.tile_m == 0 && c.split_k <= 1 && c.reduce == 0 && c.variant != 2 &&
@@ -401,8 +414,13 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
             // unasked, clusters are used only when the whole grid is one wave of one CTA per SM
             if (c.reduce == 0 && ctas > kNumSms) continue;
           }
-          const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s, mode, r->total_kb) + (r->variant == 2 && tn < d.out_channels && tn < 256 ? 1e6 : 0.0);
-          if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; best_mode = mode; best_pair = 0; }
+          // tiles of 128 or 256 channels that a CTA finishes alone may keep the accumulator transposed: both forms compete
+          const bool can_swap = swap_ok && s == 1 && tn >= 128;
+          for (int sw = (can_swap && swap_forced ? 1 : 0); sw <= (can_swap ? 1 : 0); ++sw) {
+            const double t = estimate_cycles(d, g, tm, tn, r->tile_k, s, mode, r->total_kb, sw != 0) +
+                             (r->variant == 2 && tn < d.out_channels && tn < 256 ? 1e6 : 0.0);
+            if (t < best) { best = t; best_m = tm; best_n = tn; best_s = s; best_mode = mode; best_pair = 0; best_swap = sw; }
+          }
         }
       }
     }
@@ -425,9 +443,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   // Channel-contiguous output goes through shared-memory boxes and TMA stores when the rows of the [pixels][O] matrix
   // are 16-byte multiples, rows are numbered by pixel (not the direct-NCHW route) and each CTA finishes its tiles alone.
   r->tma_epilogue = (d.flags & GIEB_FLAG_OUTPUT_NHWC) && d.out_channels % 8 == 0 && r->variant != 2 && r->split_k == 1;
-  // NCHW output of a 16-bit problem that each CTA finishes alone: the epilogue warps transpose their 32-pixel x 16-channel
-  // pieces through shared memory (1 KiB per warp) so that every store instruction writes whole runs of one channel.
-  bool nchw_stage = !tf32 && !(d.flags & (GIEB_FLAG_OUTPUT_NHWC | GIEB_FLAG_RESIDUAL)) && r->split_k == 1 && g.pq % 2 == 0;
+  bool swap = best_swap != 0 && !r->pair && r->split_k == 1;  // 2 KiB of staging per epilogue warp
   const int64_t total_tiles = int64_t(r->tiles_m) * r->tiles_n * r->split_k;
   auto stages_for = [&](size_t epi_smem) {
     int st = c.stages ? c.stages
@@ -446,27 +462,23 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   // (with several tiles per CTA the extra polling warps cost more than the last epilogue gains).
   auto epi_warps_for = [&](size_t smem) {
     if (r->pair) return conv_tc_pair_epi_warps(r->tile_n);
+    if (swap) return 8;  // the transposed epilogue is short: eight warps, 16 KiB of staging
     const bool alone = resident_ctas(r->tile_m, r->tile_n, smem) == 1;
     const bool single_tile = total_tiles <= kNumSms;
     return (alone && (r->tile_n >= 256 || (r->tile_n >= 128 && single_tile && best_mode != 2))) ? 16 : 8;
   };
-  size_t epi_smem = r->tma_epilogue ? conv_tc_epilogue_staging_bytes(r->tile_n) : (nchw_stage ? size_t(8) * 1024 : 0);
+  size_t epi_smem = r->tma_epilogue ? conv_tc_epilogue_staging_bytes(r->tile_n) : (swap ? size_t(8) * 2048 : 0);
   int stages = stages_for(epi_smem);
   if (stages < 2 || stages > kMaxStages) return no("stages must be in [2, 8]");
   r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, epi_smem, r->pair != 0);
   r->epi_warps = epi_warps_for(r->smem);
-  if (nchw_stage && r->epi_warps == 16) {  // sixteen warps stage 16 KiB
-    epi_smem = size_t(16) * 1024;
-    stages = stages_for(epi_smem);
-    r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, epi_smem, r->pair != 0);
-  }
-  if (nchw_stage && r->smem > kMaxDynamicSmem) {  // a ring depth that was asked for leaves no room: plain stores
-    nchw_stage = false;
+  if (swap && r->smem > kMaxDynamicSmem) {  // a ring depth that was asked for leaves no room: the pixel-lane kernel
+    swap = false;
     stages = stages_for(0);
     r->smem = conv_tc_smem_bytes(r->tile_m, r->tile_n, r->tile_k, stages, 0, r->pair != 0);
     r->epi_warps = epi_warps_for(r->smem);
   }
-  r->nchw_stage = nchw_stage;
+  r->swap = swap;
   r->stages = stages;
   if (r->smem > kMaxDynamicSmem) return no("configuration needs more shared memory than one CTA may have (227 KiB)");
   // A CTA of a pair keeps its SM to itself (the tensor-memory allocation of a pair spans two SMs): a short ring still
@@ -743,17 +755,13 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.bias_fp32 = (p.is_tf32 || (d.flags & GIEB_FLAG_BIAS_FP32)) ? 1 : 0;
   p.a_mode = mode;
   p.idesc = p.is_tf32 ? ptx::make_idesc_tf32(kTileM, r.tile_n, false, false)
+            : r.swap  ? ptx::make_idesc_f16(kTileM, r.tile_m, p.is_bf16, false, mode == 2)  // A = 128 weight rows, B = the tile's pixels
                       : ptx::make_idesc_f16(r.pair ? 2 * kTileM : kTileM, r.tile_n, p.is_bf16, mode == 2, false);  // a pair's instruction spans 256 rows
   p.bias = bias;
   p.residual = residual;
   p.out_nhwc = (d.flags & GIEB_FLAG_OUTPUT_NHWC) ? 1 : 0;
   p.y = y;
   p.partial = part;
-  if (r.nchw_stage && part == nullptr && residual == nullptr && !p.out_nhwc) {  // widest pixel run the plane size and y's alignment allow
-    const uintptr_t ya = reinterpret_cast<uintptr_t>(y);
-    const int pq = pl->g.pq;
-    p.out_vec = (pq % 8 == 0 && ya % 16 == 0) ? 8 : ((pq % 4 == 0 && ya % 8 == 0) ? 4 : ((pq % 2 == 0 && ya % 4 == 0) ? 2 : 0));
-  }
   p.status = pl->d_status;
   p.wait_limit = pl->wait_limit;
   p.debug_skip = pl->debug_skip;
@@ -789,8 +797,26 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
       p.res_tma = 1;
     }
   }
+  if (r.swap) {
+    const uintptr_t ya = reinterpret_cast<uintptr_t>(y);
+    p.out_vec = (pl->g.pq % 4 == 0 && ya % 8 == 0) ? 4 : ((pl->g.pq % 2 == 0 && ya % 4 == 0) ? 2 : 1);
+    if (ya % 16 == 0) {  // y as {P*Q, O, N}: boxes of 32 pixels x 32 channels, 64-byte swizzle
+      const CUtensorMapDataType dt = d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+      const cuuint64_t pq = cuuint64_t(pl->g.pq);
+      const cuuint64_t dims[3] = {pq, cuuint64_t(d.out_channels), cuuint64_t(d.batch)};
+      const cuuint64_t strides[2] = {pq * 2, pq * d.out_channels * 2};
+      const cuuint32_t box[3] = {32, 32, 1};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      const CUresult res = g_encode_tiled(&tm_out, dt, 3, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (NCHW output) failed with CUresult %d", int(res));
+      small_tensor_fixup(&tm_out, size_t(pl->g.y_elems) * 2);
+      p.swap_tma = 1;
+    }
+  }
   if (!(stage_mask & 2u)) {
-  } else if (r.pair) GIEB_CUDA(conv_tc_pair_launch(r.tile_n, r.tile_k, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
+  } else if (r.swap) GIEB_CUDA(conv_tc_swap_launch(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, tm_act, tm_wgt, tm_out, p, grid, r.smem, st));
+  else if (r.pair) GIEB_CUDA(conv_tc_pair_launch(r.tile_n, r.tile_k, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
   else GIEB_CUDA(conv_tc_launch(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, tm_act, tm_wgt, tm_out, tm_res, p, grid, r.smem, st));
   if (ev) GIEB_CUDA(cudaEventRecord(ev[2], st));
   if (r.reduce == 1 && (stage_mask & 4u))
@@ -868,7 +894,9 @@ int gieb_conv_plan_create(const gieb_conv_desc* desc, const gieb_conv_cfg* cfg, 
     }
   }
   if (e == cudaSuccess && r.variant != 3)
-    e = r.pair ? conv_tc_pair_prepare(r.tile_n, r.tile_k, kMaxDynamicSmem) : conv_tc_prepare(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, kMaxDynamicSmem);
+    e = r.swap ? conv_tc_swap_prepare(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, kMaxDynamicSmem)
+        : r.pair ? conv_tc_pair_prepare(r.tile_n, r.tile_k, kMaxDynamicSmem)
+                 : conv_tc_prepare(r.tile_m, r.tile_n, r.tile_k, r.epi_warps, kMaxDynamicSmem);
   if (e != cudaSuccess) {
     if (pl->d_status) cudaFree(pl->d_status);
     delete pl;
@@ -1015,8 +1043,9 @@ int gieb_conv_forward_static(const gieb_conv_desc* desc, const gieb_conv_cfg* cf
   pl.d_status = reinterpret_cast<uint32_t*>(base);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (pl.r.variant != 3)
-    GIEB_CUDA(pl.r.pair ? conv_tc_pair_prepare(pl.r.tile_n, pl.r.tile_k, kMaxDynamicSmem)
-                        : conv_tc_prepare(pl.r.tile_m, pl.r.tile_n, pl.r.tile_k, pl.r.epi_warps, kMaxDynamicSmem));
+    GIEB_CUDA(pl.r.swap ? conv_tc_swap_prepare(pl.r.tile_m, pl.r.tile_n, pl.r.tile_k, pl.r.epi_warps, kMaxDynamicSmem)
+              : pl.r.pair ? conv_tc_pair_prepare(pl.r.tile_n, pl.r.tile_k, kMaxDynamicSmem)
+                          : conv_tc_prepare(pl.r.tile_m, pl.r.tile_n, pl.r.tile_k, pl.r.epi_warps, kMaxDynamicSmem));
   // The array keeps whatever the previous call left: the status word must start at zero.  Everything else in the
   // scratch is fully rewritten by the repack kernels (padding channels included) and the split-K slices before use.
   GIEB_CUDA(cudaMemsetAsync(base, 0, kStaticScratchHeader, s));

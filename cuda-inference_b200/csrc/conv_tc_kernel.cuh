@@ -158,64 +158,29 @@ __device__ __forceinline__ void chunk_to_staging(const uint32_t (&v)[32], const 
   }
 }
 
-// NCHW output through a per-warp staging tile: the 32 lanes of the warp hold 32 consecutive pixels and, in v, 32 consecutive
-// channels of each.  Sixteen channels at a time are rounded and written to `stage` as [channel][pixel] (a lane writes two
-// bytes per channel: 64 contiguous bytes per warp instruction, no bank conflict), then read back as vectors of V pixels of
-// one channel and stored: one store instruction covers 32 / (32 / V) ... whole runs of 2 V bytes instead of 32 two-byte pieces.
-// `gdst` = address of (this lane's pixel group, first channel of the chunk); channels are `cstride` elements apart.
-// Lane l owns pixel group l % (32 / V) and the channel rows l / (32 / V) + k * V of each sixteen.
-template <typename T, int V, bool RELU>
-__device__ __forceinline__ void store_chunk_staged(const uint32_t (&v)[32], const float* __restrict__ bias, T* stage, int lane, T* gdst,
-                                                   int64_t cstride, bool group_ok, int nvalid) {
-  constexpr int GROUPS = 32 / V;      // pixel groups per staged row: 4, 8 or 16
-  constexpr int RSTEP = 32 / GROUPS;  // channel rows one pass of the warp covers: 8, 4 or 2
-  using Vec = typename std::conditional<V == 8, uint4, typename std::conditional<V == 4, uint2, uint32_t>::type>::type;
-  const int g = lane % GROUPS, r0 = lane / GROUPS;
+// Transposed accumulator: 32 consecutive pixels of ONE channel (this lane's) -> + bias, ReLU on the rounded pair (rounding is
+// monotonic and keeps zero), packed as 64 bytes and written as the lane's row of the warp's staging box (32 rows of 64
+// bytes, 64-byte swizzled: 16-byte cell q of row r sits at cell q ^ ((r >> 1) & 3); conflict-free).
+template <typename T, bool RELU>
+__device__ __forceinline__ void row_to_staging(const uint32_t (&v)[32], float bias, uint8_t* box, int lane) {
+  uint32_t w[16];
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    // two channels per conversion; the ReLU is applied to the rounded pair (rounding is monotonic and keeps zero)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float2 b = reinterpret_cast<const float2*>(bias)[half * 8 + j];
-      const float a0 = __uint_as_float(v[half * 16 + 2 * j]) + b.x;
-      const float a1 = __uint_as_float(v[half * 16 + 2 * j + 1]) + b.y;
-      if constexpr (std::is_same<T, __half>::value) {
-        __half2 o = __floats2half2_rn(a0, a1);
-        if (RELU) o = __hmax2(o, __half2half2(__ushort_as_half(0)));
-        stage[(2 * j) * 32 + lane] = __low2half(o);
-        stage[(2 * j + 1) * 32 + lane] = __high2half(o);
-      } else {
-        __nv_bfloat162 o = __floats2bfloat162_rn(a0, a1);
-        if (RELU) o = __hmax2(o, __bfloat162bfloat162(__ushort_as_bfloat16(0)));
-        stage[(2 * j) * 32 + lane] = __low2bfloat16(o);
-        stage[(2 * j + 1) * 32 + lane] = __high2bfloat16(o);
-      }
+  for (int j = 0; j < 16; ++j) {
+    const float a0 = __uint_as_float(v[2 * j]) + bias, a1 = __uint_as_float(v[2 * j + 1]) + bias;
+    if constexpr (std::is_same<T, __half>::value) {
+      __half2 o = __floats2half2_rn(a0, a1);
+      if (RELU) o = __hmax2(o, __half2half2(__ushort_as_half(0)));
+      w[j] = *reinterpret_cast<const uint32_t*>(&o);
+    } else {
+      __nv_bfloat162 o = __floats2bfloat162_rn(a0, a1);
+      if (RELU) o = __hmax2(o, __bfloat162bfloat162(__ushort_as_bfloat16(0)));
+      w[j] = *reinterpret_cast<const uint32_t*>(&o);
     }
-    __syncwarp();
+  }
+  const int sw = (lane >> 1) & 3;
 #pragma unroll
-    for (int i = 0; i < 16 / RSTEP; ++i) {
-      const int row = r0 + i * RSTEP;
-      const int c = half * 16 + row;
-      const Vec q = *reinterpret_cast<const Vec*>(stage + row * 32 + g * V);
-      if (group_ok && c < nvalid) *reinterpret_cast<Vec*>(gdst + int64_t(c) * cstride) = q;
-    }
-    __syncwarp();
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ void store_chunk_staged(const uint32_t (&v)[32], const float* bias, T* stage, int lane, T* gdst, int64_t cstride,
-                                                   bool group_ok, int nvalid, int vec, int relu) {
-  if (vec == 8) {
-    if (relu) store_chunk_staged<T, 8, true>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
-    else store_chunk_staged<T, 8, false>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
-  } else if (vec == 4) {
-    if (relu) store_chunk_staged<T, 4, true>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
-    else store_chunk_staged<T, 4, false>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
-  } else {
-    if (relu) store_chunk_staged<T, 2, true>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
-    else store_chunk_staged<T, 2, false>(v, bias, stage, lane, gdst, cstride, group_ok, nvalid);
-  }
+  for (int q = 0; q < 4; ++q)
+    *reinterpret_cast<uint4*>(box + lane * 64 + ((q ^ sw) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
 }
 
 // dst / res point at the first element of the chunk for this row; consecutive channels are `stride` elements apart
@@ -268,7 +233,14 @@ __device__ __forceinline__ void with_output_type(const ConvTcParams& p, F&& f) {
 // and each CTA's epilogue warps drain the 128 accumulator rows that sit in their own tensor memory.  Per slab and SM that is
 // (128 + BN / 2) rows of operands instead of (128 + BN): the weight traffic from L2 is halved.  MH = 1, no cluster split-K,
 // 16-bit types.
-template <int BN, int BK, int MH, int EW, bool PAIR>
+// SWAP: the accumulator is held TRANSPOSED -- tensor-memory lane = output channel, column = output pixel -- by handing the
+// weight slab to the instruction as its A operand (M = 128 channels per instruction, BN / 128 of them per slab) and the
+// activation slab as its B operand (N = 128 or 256 pixels).  Shared-memory layouts and producers are unchanged: both slabs
+// are K-major row blocks either way.  An epilogue thread then owns one channel and 32 consecutive pixels, i.e. 64
+// contiguous bytes of an NCHW tensor: the warp stages its 32 channels x 32 pixels as one box and a TMA store writes it
+// (tensor {P*Q, O, N}); for NCHW output whose planes are 16-byte multiples.  BN 128 or 256, 16-bit types, no split-K,
+// no pair.
+template <int BN, int BK, int MH, int EW, bool PAIR, bool SWAP = false>
 __global__ void __launch_bounds__(32 * (kProducerWarps + 1 + EW), (EW == 16 || PAIR) ? 1 : 2)  // EW = 8: at most 80 registers, two CTAs per SM
 conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_wgt,
                const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_res, const ConvTcParams p) {
@@ -276,6 +248,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   constexpr uint32_t A_HALF_BYTES = kTileM * ROW_BYTES;
   constexpr uint32_t A_BYTES = MH * A_HALF_BYTES;
   static_assert(!PAIR || (MH == 1 && BN >= 32), "a CTA pair computes one 256-pixel tile");
+  static_assert(!SWAP || (!PAIR && BN % 128 == 0), "the transposed accumulator takes 128 channels per instruction");
   constexpr int B_ROWS = PAIR ? BN / 2 : BN;                   // weight rows this CTA loads per slab
   constexpr uint32_t B_BYTES = B_ROWS * ROW_BYTES;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -504,6 +477,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         auto issue_slab = [&](int slot, bool first) {
           const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(slot) * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
+          if constexpr (SWAP) {
+            // A = 128 weight rows (output channels), B = all MH * 128 activation rows (pixels) of the slab
+#pragma unroll
+            for (int hc = 0; hc < BN / 128; ++hc) {
+#pragma unroll
+              for (int k = 0; k < MMAS_PER_SLAB; ++k) {
+                const uint64_t wdesc = ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + hc * (128 * ROW_BYTES) + k * 32);
+                const uint64_t xdesc = FORM == 1 ? ptx::smem_desc_mnmajor_sw128(a_addr + k * 2048, A_HALF_BYTES / 2, 1024)
+                                                 : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + k * 32);
+                ptx::mma_f16_ss(acc + hc * (MH * 128), wdesc, xdesc, p.idesc, !first || k != 0);
+              }
+            }
+          } else {
 #pragma unroll
           for (int h = 0; h < MH; ++h) {
             if (h < halves) {
@@ -519,6 +505,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
                 else ptx::mma_f16_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
               }
             }
+          }
           }
           // frees the slot (in both CTAs of a pair) once these MMAs have read it
           if constexpr (PAIR) ptx::mma_commit_pair(&empty_bar[slot], 3);
@@ -635,22 +622,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       if (p.out_tma) prefetch_residual(0);
 
       // Row decode and output addresses, done while the main loop still runs (the accumulator is not needed for them).
-      const bool staged = p.out_vec != 0 && p.partial == nullptr;  // warp-uniform: NCHW stores through the staging tile
       const int64_t cstride = p.out_nhwc ? 1 : p.pq;
-      bool m_ok_h[MH], g_ok_h[MH];
-      int64_t base_h[MH], gbase_h[MH];
+      bool m_ok_h[MH];
+      int64_t base_h[MH];
 #pragma unroll
       for (int h = 0; h < MH; ++h) {
         int img, pix;
         decode_row(m0 + h * kTileM + quad * 32 + lane, m_ok_h[h], img, pix);
         base_h[h] = p.out_nhwc ? (int64_t(img) * p.pq + pix) * p.out_channels + n0 : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
-        g_ok_h[h] = false;
-        gbase_h[h] = 0;
-        if (staged) {  // this lane's group of out_vec pixels within the warp's 32 (a group never straddles an image)
-          const int gsh = p.out_vec == 8 ? 2 : (p.out_vec == 4 ? 3 : 4);  // log2 of the groups per 32 pixels
-          decode_row(m0 + h * kTileM + quad * 32 + (lane & ((1 << gsh) - 1)) * p.out_vec, g_ok_h[h], img, pix);
-          gbase_h[h] = (int64_t(img) * p.out_channels + n0) * p.pq + pix;
-        }
       }
 
       const bool ok = ptx::mbar_wait(&acc_full[buf], acc_phase, p.status, kStatusEpilogueTimeout, p.wait_limit);
@@ -732,12 +711,77 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         }
         break;  // one tile per CTA in this mode
       }
+      if constexpr (SWAP) {
+        // Transposed accumulator: lane = output channel, 32 columns = 32 consecutive pixels.  Work units = (128-channel
+        // half, 32-pixel column chunk); the EG warps of a lane quarter take them in turn.  A unit is rounded and written
+        // into the warp's staging box as 32 rows (channels) of 64 bytes, 64-byte swizzled (16-byte cell q of row r at
+        // cell q ^ ((r >> 1) & 3): conflict-free), and leaves as ONE TMA store when its pixels lie in one image;
+        // otherwise (the unit crosses into the next image, or y is not 16-byte aligned) the lanes read the box back as
+        // runs of out_vec pixels and store them.
+        constexpr int PC = MH * 4;                 // 32-pixel chunks per channel half
+        constexpr int UNITS = (BN / 128) * PC;
+        uint8_t* box = epi_base + size_t(we) * 2048;
+        // fallback geometry: lane owns the pixel group g of rows r0, r0 + rstep, ...
+        const int vec = p.out_vec;                                   // 4, 2 or 1 pixels per store
+        const int gsh = vec == 4 ? 3 : (vec == 2 ? 4 : 5);           // log2(groups per row)
+        const int g = lane & ((1 << gsh) - 1), r0 = lane >> gsh, rstep = 32 >> gsh;
+#pragma unroll 1
+        for (int u = par; u < UNITS; u += EG) {
+          const int hc = u / PC, pc = u - hc * PC;
+          const int ch0 = n0 + hc * 128 + quad * 32;                 // channel of lane 0
+          const int mstart = m0 + pc * 32;                           // first pixel row of the unit
+          if (ch0 >= p.out_channels || mstart >= p.m_total) continue;  // warp-uniform
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(hc * (MH * 128) + pc * 32), v);
+          ptx::tmem_ld_wait();
+          const float bv = bias_t[hc * 128 + quad * 32 + lane];
+          if (lane == 0) ptx::bulk_wait_group_read0();  // the previous store of this warp has left the box
+          __syncwarp();
+          if (p.is_bf16) {
+            if (p.relu) row_to_staging<__nv_bfloat16, true>(v, bv, box, lane);
+            else row_to_staging<__nv_bfloat16, false>(v, bv, box, lane);
+          } else {
+            if (p.relu) row_to_staging<__half, true>(v, bv, box, lane);
+            else row_to_staging<__half, false>(v, bv, box, lane);
+          }
+          bool u_ok;
+          int img, pix0;
+          decode_row(mstart, u_ok, img, pix0);
+          // one image holds the whole unit (rows numbered in 64-pixel boxes never leave their image: the map clips the tail)
+          const bool whole = p.swap_tma && u_ok && (p.a_mode == 2 || pix0 + 32 <= p.pq);
+          if (whole) {
+            ptx::fence_proxy_async_smem();  // generic-proxy writes above -> visible to the TMA store below
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_3d(&tm_out, box, pix0, ch0, img);  // channels beyond O are clipped by the tensor map
+              ptx::bulk_commit_group();
+            }
+          } else {
+            __syncwarp();
+            bool g_ok;
+            int gimg, gpix;
+            decode_row(mstart + g * vec, g_ok, gimg, gpix);  // a group never straddles an image (P*Q % vec == 0)
+            const int64_t gb = (int64_t(gimg) * p.out_channels + ch0) * p.pq + gpix;
+            uint8_t* yb = static_cast<uint8_t*>(p.y);
+            for (int row = r0; row < 32; row += rstep) {
+              if (!g_ok || ch0 + row >= p.out_channels) continue;
+              const int byte = g * vec * 2;  // offset of the group inside the 64-byte row
+              const uint8_t* src = box + row * 64 + (((byte >> 4) ^ ((row >> 1) & 3)) << 4) + (byte & 15);
+              uint8_t* dst = yb + (gb + int64_t(row) * p.pq) * 2;
+              if (vec == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(src);
+              else if (vec == 2) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+              else *reinterpret_cast<uint16_t*>(dst) = *reinterpret_cast<const uint16_t*>(src);
+            }
+            __syncwarp();
+          }
+        }
+      } else {
       float* part = p.partial ? p.partial + int64_t(z) * ((p.y_elems + 3) & ~int64_t(3)) : nullptr;
 #pragma unroll
       for (int h = 0; h < MH; ++h) {
         if (h >= halves) break;
-        const bool m_ok = m_ok_h[h], g_ok = g_ok_h[h];
-        const int64_t base = base_h[h], gbase = gbase_h[h];
+        const bool m_ok = m_ok_h[h];
+        const int64_t base = base_h[h];
         if (p.out_tma && h > 0) prefetch_residual(h);
 #pragma unroll 1
         for (int chunk = par; chunk < BN / 32; chunk += EG) {
@@ -745,18 +789,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           uint32_t v[32];
           ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(h * BN + chunk * 32), v);
           ptx::tmem_ld_wait();
-          if (staged) {
-            const int nvalid = min(32, p.out_channels - (n0 + chunk * 32));
-            const int64_t goff = gbase + int64_t(chunk * 32) * p.pq;
-            if (p.is_bf16) {
-              store_chunk_staged(v, bias_t + chunk * 32, reinterpret_cast<__nv_bfloat16*>(epi_base + we * 1024), lane,
-                                 static_cast<__nv_bfloat16*>(p.y) + goff, int64_t(p.pq), g_ok, nvalid, p.out_vec, p.relu);
-            } else {
-              store_chunk_staged(v, bias_t + chunk * 32, reinterpret_cast<__half*>(epi_base + we * 1024), lane,
-                                 static_cast<__half*>(p.y) + goff, int64_t(p.pq), g_ok, nvalid, p.out_vec, p.relu);
-            }
-            continue;
-          }
           if (p.out_tma) {
             const int k = chunk / EG;
             uint8_t* box = stage_box(k);
@@ -799,6 +831,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           }
         }
       }
+      }  // !SWAP
       // all TMEM reads of this warp are complete (wait::ld above): hand the accumulator set back to the MMA issuer
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -809,7 +842,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     }
   }
 
-  if (p.out_tma && warp > kProducerWarps && lane == 0) ptx::bulk_wait_group0();  // this warp's TMA stores are complete
+  if ((p.out_tma || SWAP) && warp > kProducerWarps && lane == 0) ptx::bulk_wait_group0();  // this warp's TMA stores are complete
   join_setup();  // no-op for every warp that had a tile (all of them: the grid never exceeds the tile count)
   ptx::tc_fence_before_sync();
   if constexpr (PAIR) {

@@ -130,10 +130,10 @@ struct ConvTcParams {
   const void* residual;  // optional tensor of the output's shape, layout and type, added before the activation
   int out_nhwc;          // 0: y (and residual, partials) are NCHW; 1: channel-contiguous [B][P][Q][O]
   int out_tma, res_tma;  // channel-contiguous output leaves through TMA stores / the residual arrives through TMA loads
-  // NCHW output of 16-bit type: 0 = one 2-byte store per element; 8 / 4 / 2 = the epilogue warps transpose their pieces
-  // through shared memory and store runs of that many pixels (16 / 8 / 4 bytes) of one channel.  Needs P*Q % out_vec == 0,
-  // y aligned to 2 * out_vec bytes and 1 KiB of staging per epilogue warp behind the ring.
-  int out_vec;
+  // Transposed-accumulator kernels: swap_tma = y may be written by TMA stores over its {P*Q, O, N} view (16-byte aligned y,
+  // P*Q % 8 == 0); out_vec = pixels per store (4, 2 or 1) of the path that handles everything else (a unit that crosses
+  // into the next image, or an unaligned y): needs P*Q % out_vec == 0 and y aligned to 2 * out_vec bytes.
+  int swap_tma, out_vec;
   void* y;            // output in the storage type (split_k == 1 or cluster reduction)
   float* partial;     // [splits][B*O*P*Q] FP32 partial sums in the output's element order (workspace reduction), else null
   uint32_t* status;
@@ -160,6 +160,12 @@ int conv_tc_pair_epi_warps(int tile_n);
 cudaError_t conv_tc_pair_prepare(int tile_n, int tile_k, size_t smem_bytes);
 cudaError_t conv_tc_pair_launch(int tile_n, int tile_k, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt, const CUtensorMap& tm_out,
                                 const CUtensorMap& tm_res, const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream);
+
+// Transposed-accumulator points (lane = output channel): NCHW output through TMA stores; tile_n 128 or 256, 16-bit types.
+// tm_out: y as the 3-D tensor {P*Q, O, N} with a 32-pixel x 32-channel box and 64-byte swizzle (read when p.swap_tma).
+cudaError_t conv_tc_swap_prepare(int tile_m, int tile_n, int tile_k, int epi_warps, size_t smem_bytes);
+cudaError_t conv_tc_swap_launch(int tile_m, int tile_n, int tile_k, int epi_warps, const CUtensorMap& tm_act, const CUtensorMap& tm_wgt,
+                                const CUtensorMap& tm_out, const ConvTcParams& p, dim3 grid, size_t smem_bytes, cudaStream_t stream);
 
 // Sum of split-K partials + bias (+ residual) + ReLU + one rounding; `total` = B*O*P*Q elements in the output's order.
 cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total, int out_channels, int pq,

@@ -64,13 +64,19 @@ def test_epilogue_warp_count_follows_the_plan(pkg):
     """CTAs that own their SM run 16 epilogue warps (640 threads): every 256-column tile whose ring leaves no room for a
     second CTA, and 128-column tiles with one tile per CTA; everything else keeps 8 (384 threads)."""
     c2 = pkg.query(P(pkg, 32, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1, precision=pkg.FP16))
-    assert c2.supported and c2.threads_per_block == 640 and (c2.cfg.tile_m, c2.cfg.tile_n, c2.cfg.split_k) == (128, 128, 1)
+    # a long reduction with enough pixels: 256-pixel tiles of CTA pairs, each CTA alone on its SM
+    assert c2.supported and c2.threads_per_block == 640 and (c2.cfg.tile_m, c2.cfg.tile_n, c2.cfg.split_k, c2.cfg.cta_pair) == (256, 128, 1, 2)
+    single = pkg.query(P(pkg, 32, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1, precision=pkg.FP16), pkg.make_cfg(cta_pair=1))
+    assert single.supported and single.threads_per_block == 640 and (single.cfg.tile_m, single.cfg.tile_n, single.cfg.cta_pair) == (128, 128, 1)
     c3 = pkg.query(P(pkg, 64, 512, 28, 28, 128, 1, 1, precision=pkg.FP16))
     assert c3.supported and c3.variant == 2 and c3.threads_per_block == 384 and c3.launches == 1   # 416 tiles on 148 CTAs; weights in place
-    wide = pkg.query(P(pkg, 16, 128, 56, 56, 256, 3, 3, 2, 2, 1, 1, precision=pkg.FP16), pkg.make_cfg(tile_n=256, tile_k=64, stages=4))
-    assert wide.supported and wide.threads_per_block == 640
-    shallow = pkg.query(P(pkg, 16, 128, 56, 56, 256, 3, 3, 2, 2, 1, 1, precision=pkg.FP16), pkg.make_cfg(tile_n=128, tile_k=64, stages=2))
+    wide = pkg.query(P(pkg, 16, 128, 54, 54, 256, 3, 3, 2, 2, 1, 1, precision=pkg.FP16), pkg.make_cfg(tile_n=256, tile_k=64, stages=4))
+    assert wide.supported and wide.threads_per_block == 640                                         # 27 x 27 output planes: pixel-lane kernel
+    shallow = pkg.query(P(pkg, 16, 128, 54, 54, 256, 3, 3, 2, 2, 1, 1, precision=pkg.FP16), pkg.make_cfg(tile_n=128, tile_k=64, stages=2))
     assert shallow.supported and shallow.threads_per_block == 384                                   # two CTAs share an SM
+    # NCHW output planes of 28 x 28 (16-byte multiples): transposed accumulator, a short epilogue on eight warps
+    tr = pkg.query(P(pkg, 64, 512, 28, 28, 128, 1, 1, precision=pkg.FP16), pkg.make_cfg(tile_m=128, tile_n=128, tile_k=64, stages=6))
+    assert tr.supported and tr.threads_per_block == 384 and tr.dynamic_smem_bytes == 1024 + 3072 + 6 * 32768 + 8 * 2048
 
 
 def test_query_precision_routing_and_reasons(pkg):
@@ -146,7 +152,8 @@ def test_selection_is_deterministic_and_fills_the_machine(pkg):
         assert 1 <= c.split_k <= max(1, total_kb // 2)
         pixels = a[0] * p.out_h * p.out_w
         rows = a[0] * -(-(a[2] * a[3]) // 64) * 64 if i1.variant == 2 else pixels   # direct NCHW route counts 64-pixel boxes
-        assert i1.num_blocks == -(-rows // c.tile_m) * -(-a[4] // c.tile_n) * c.split_k
+        ctas_per_tile = 2 if c.cta_pair == 2 else 1   # a 256-pixel tile of a CTA pair is two CTAs
+        assert i1.num_blocks == -(-rows // c.tile_m) * -(-a[4] // c.tile_n) * c.split_k * ctas_per_tile
     # the small deep layer gets split-K, the big ones do not
     assert pkg.query(P(pkg, 1, 512, 7, 7, 512, 3, 3, 1, 1, 1, 1, precision=pkg.FP16)).cfg.split_k > 1
     assert pkg.query(P(pkg, 256, 64, 56, 56, 256, 1, 1, precision=pkg.FP16)).cfg.split_k == 1

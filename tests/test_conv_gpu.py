@@ -139,6 +139,41 @@ def test_cta_pair_tiles(pkg, orc, oracle, case, prec_name):
     _check(oracle, p, got, ref, scale, f"pair case {case} {kw} {prec_name}")
 
 
+SWAP_CASES = [
+    # NCHW output whose planes are 16-byte multiples, on 128- or 256-channel tiles: the accumulator is kept transposed
+    # (lane = output channel) and the epilogue writes 32-channel x 32-pixel boxes with TMA stores.  (shape, cfg, y offset in elements)
+    ((4, 64, 16, 16, 128, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=4), 0),               # 256 px per image: units never leave an image
+    ((3, 64, 12, 14, 130, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=32, stages=3), 0),               # 168 px per image: units cross images; channel tail of 2
+    ((3, 64, 12, 14, 200, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=16, stages=4), 0),               # two channel halves, the second one partial
+    ((5, 32, 12, 14, 256, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=256, tile_k=32, stages=3), 0),   # 256 x 256 tile, 840 px: last tile owns one half
+    ((2, 64, 28, 28, 128, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=128, tile_k=64, stages=2), 0),
+    ((40, 32, 8, 8, 128, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=32, stages=2), 0),                # 20 tiles; several per CTA with two CTAs per SM
+    ((64, 64, 24, 24, 256, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=64, stages=3), 0),              # 288 tiles on 148 persistent CTAs
+    ((3, 64, 12, 14, 130, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=3), 1),               # y off by 2 bytes: no TMA, single-element stores
+    ((3, 64, 12, 14, 130, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=3), 2),               # y 4-byte aligned: pairs of pixels
+    ((3, 64, 12, 14, 130, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=64, stages=3), 4),               # y 8-byte aligned: runs of four pixels
+    ((2, 96, 16, 24, 192, 1, 1, 1, 1, 0, 0), dict(variant=4, tile_n=128, tile_k=32, stages=4), 0),    # tiled activation loads
+    ((2, 512, 28, 28, 128, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=128, tile_k=64, stages=4), 0),   # direct NCHW in (pixel-major operand), NCHW out
+    ((3, 70, 10, 20, 255, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=256, tile_k=32, stages=3), 0),    # 200 px = 3 boxes of 64 + 8: the map clips the tail
+    ((5, 256, 28, 28, 96, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_m=256, tile_n=128, tile_k=64), 0),
+    ((2, 64, 56, 56, 128, 3, 3, 2, 2, 1, 1), dict(tile_n=128, tile_k=64, stages=4), 0),               # stride 2 -> 28 x 28
+]
+
+
+@pytest.mark.parametrize("case", range(len(SWAP_CASES)))
+@pytest.mark.parametrize("prec_name", ["fp16", "bf16"])
+def test_transposed_accumulator_nchw_stores(pkg, orc, oracle, case, prec_name, monkeypatch):
+    monkeypatch.setenv("GIEB_TRANSPOSED_ACC", "2")  # this form wherever the problem allows it, whatever the cost model prefers
+    args, kw, yoff = SWAP_CASES[case]
+    prec = orc.FP16 if prec_name == "fp16" else orc.BF16
+    p = orc.Problem.P(*args, precision=prec, bias=(case % 3 != 1), relu=(case % 2 == 0))
+    x, w, b = oracle.make_conv_data(p, 8000 + case, case % 4)
+    ref, scale = oracle.conv2d(p, x, w, b if p.has_bias else None)
+    got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b if p.has_bias else None, cfg=pkg.make_cfg(**kw), offsets=(0, 0, yoff), repeats=2)
+    assert plan.info.cfg.split_k == 1 and plan.info.cfg.tile_n == kw["tile_n"] and plan.info.threads_per_block == 384
+    _check(oracle, p, got, ref, scale, f"transposed-accumulator case {case} {kw} yoff={yoff} {prec_name}")
+
+
 DIRECT_CASES = [
     # 1x1 / stride 1 / pad 0 with H*W % 8 == 0: activations are read straight from NCHW (pixel-major operand)
     ((2, 64, 8, 8, 64, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=64, tile_k=64, stages=2), 0),
