@@ -311,7 +311,7 @@ def protocol_samples(torch, stream, run, units_per_run, samples=30, min_ms=1.0, 
             "units_per_sample": reps * units_per_run}
 
 
-def time_conv(torch, pkg, shape, steps, warmup, world, barrier, max_over_ranks, cfg=None, stage_times=True):
+def time_conv(torch, pkg, shape, steps, warmup, world, barrier, max_over_ranks, cfg=None, stage_times=True, protocol=True):
     """Times forward calls on rotating buffer sets (the rotation is larger than L2), always as replays of CUDA graphs so
     that the host never bounds the measurement.  Two measurements:
       * the K-step region: exactly `steps` steps between one event pair, bracketed by barriers and synchronisation;
@@ -362,6 +362,11 @@ def time_conv(torch, pkg, shape, steps, warmup, world, barrier, max_over_ranks, 
         torch.cuda.synchronize()
         barrier()
         ms = max_over_ranks(start.elapsed_time(end))
+    if not protocol:  # a short run for a profiler: the K-step region only
+        us = ms * 1e3 / steps
+        return dict(plan=plan, ms=ms, proto={"median_us": us, "p10_us": us, "p90_us": us, "samples": 0, "units_per_sample": steps},
+                    kernel={"median_us": us, "p10_us": us, "p90_us": us}, nsets=nsets, sets=sets, wss=wss,
+                    launches=steps * plan.info.launches, rotation_bytes=per_set * nsets)
     full = capture(nsets) if group != nsets else graph
     proto = protocol_samples(torch, stream, full.replay, nsets)
     for k in ("median_us", "p10_us", "p90_us"):
@@ -587,8 +592,17 @@ def run_ours(args):
     shape, bound = wl.CONV_WORKLOADS[args.workload]
     sampler = ClockSampler(local_rank)
     sampler.start()
-    res = time_conv(torch, pkg, shape, args.steps, args.warmup, world, barrier, max_over_ranks)
+    cfg = None
+    if args.cfg:  # an explicit point of the kernel family instead of the heuristic's choice, e.g. --cfg split_k=4,reduce=1
+        cfg = pkg.make_cfg(**{k: int(v) for k, v in (kv.split("=") for kv in args.cfg.split(","))})
+    res = time_conv(torch, pkg, shape, args.steps, args.warmup, world, barrier, max_over_ranks, cfg=cfg, protocol=not args.profile_run)
     clocks = sampler.stop()
+    if args.profile_run:  # for ncu: warm-up and the K-step region only (the numbers of such a run are not measurements)
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": args.workload, "us_per_step_k_region": res["ms"] * 1e3 / args.steps,
+                              "launches_per_step": res["plan"].info.launches}))
+        ranks.close()
+        return
     plan = res["plan"]
     proto = res["proto"]
     step_us = proto["median_us"]                      # the number of record: median of 30 samples of >= 1 ms
@@ -761,11 +775,13 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20000)
     ap.add_argument("--warmup", type=int, default=200)
-    ap.add_argument("--workload", default="c2", help="c1 | c2 | c3_fp16 | c3_bf16 | c4a | c4b | chain")
+    ap.add_argument("--workload", default="c2", help="c1 | c2 | c3_fp16 | c3_bf16 | c4a | c4b | stem | chain")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layout", default="nchw", choices=["nchw", "nhwc"], help="--workload chain: tensor layout between layers")
     ap.add_argument("--tune", action="store_true", help="--workload chain: measure candidate configurations per layer first")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cfg", default="", help="explicit configuration, comma-separated key=value of tile_m, tile_n, tile_k, stages, split_k, variant, reduce, cta_pair")
+    ap.add_argument("--profile-run", action="store_true", help="warm-up and the K-step region only, nothing else (for a run under a profiler)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (other shapes, RMSNorm, conv chain)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -3,9 +3,13 @@
 //
 // GEMM view: rows = output pixels (b, oh, ow), columns = output channels, k = (c, r, s) in OIHW order so a weight
 // row is contiguous in k.  Per CTA: a TP x TO output tile, 4x4 outputs per thread, BK = 16 reduction slab staged in
-// shared memory (pixels contiguous in the X slab, so the gather from NCHW is coalesced along ow), next slab
-// prefetched into registers while the current one is consumed.  Accumulation is fmaf in k order.
+// shared memory by asynchronous copies (pixels contiguous in the X slab, so the gather from NCHW is coalesced along ow;
+// 128-bit copies of W along k), a ring of slabs in flight while one is consumed.  Accumulation is fmaf in k order.
 #include <stdint.h>
+
+#include <mutex>
+#include <set>
+#include <utility>
 
 #include "internal.h"
 
@@ -26,22 +30,37 @@ struct Fp32Args {
   FastDiv fd_rs, fd_s, fd_pq, fd_out_w;  // multiply-high reciprocals of r*s, s, out_h*out_w, out_w
 };
 
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+// 4-byte asynchronous copy global -> shared; `valid` false writes zero (nothing is read: the source size is 0).
+__device__ __forceinline__ void cp_async4(void* dst, const float* src, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(valid ? 4 : 0) : "memory");
+}
+// 16-byte asynchronous copy (both addresses 16-byte aligned); `bytes` of the source are read, the rest is zero-filled.
+__device__ __forceinline__ void cp_async16(void* dst, const float* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kWPitch = kBK + 4;  // floats per weight row in shared memory: 16-byte aligned rows, conflict-free 128-bit reads
+
 // KG = number of thread groups that split the reduction inside one CTA (slab s goes to group s % KG); their partial
 // accumulators are summed in a fixed order at the end, so results are deterministic.  KG > 1 gives small problems
 // (few CTAs, long dependent slab chains) enough warps per SM to hide global-load latency.
+// Operands reach shared memory through asynchronous copies (cp.async) into a ring of NS slabs per group, so the loads of
+// the next NS - 1 slabs are in flight while one is consumed and no register or store instruction is spent on staging:
+//   X slab [kBK][TP]: one 4-byte copy per element, gathered from NCHW with zero-fill for padding (pixels contiguous);
+//   W slab [TO][kBK]: 128-bit copies along k (OIHW rows are contiguous in k) when W16, else 4-byte copies.
 // LUT: k -> (offset of (c, r, s) inside one image, r, s) comes from a table built once per CTA (the analogue of
-// build_conv_lut, src/kernels/conv_common.cu:25-37) instead of two divisions per gathered element: the gather is
-// instruction-bound, and the table cuts a load from ~30 to ~10 instructions.
-template <int TP, int TO, int KG, bool LUT>
+// build_conv_lut, src/kernels/conv_common.cu:25-37) instead of two divisions per gathered element.
+template <int TP, int TO, int KG, int NS, bool LUT, bool W16>
 __global__ void __launch_bounds__((TP / 4) * (TO / 4) * KG)
 conv_fp32_kernel(const Fp32Args a) {
   constexpr int NT = (TP / 4) * (TO / 4);  // threads per group
-  constexpr int XE = kBK * TP / NT;        // X-slab elements loaded per thread
-  constexpr int WE = kBK * TO / NT;        // W-slab elements loaded per thread
-  constexpr int XS_FLOATS = KG * kBK * TP, WS_FLOATS = KG * kBK * (TO + 4);
-  __shared__ __align__(16) float tiles[XS_FLOATS + WS_FLOATS];  // operand tiles; reused for the group reduction
-  float (*xs)[kBK][TP] = reinterpret_cast<float (*)[kBK][TP]>(tiles);
-  float (*ws)[kBK][TO + 4] = reinterpret_cast<float (*)[kBK][TO + 4]>(tiles + XS_FLOATS);
+  constexpr int XE = kBK * TP / NT;        // X-slab elements copied per thread
+  constexpr int XS = kBK * TP, WS = TO * kWPitch;  // floats per X / W slab
+  extern __shared__ __align__(16) float tiles[];    // [KG][NS] X slabs, then [KG][NS] W slabs; reused for the group reduction
   __shared__ int2 lut[LUT ? kLutMax : 1];
 
   const int grp = threadIdx.x / NT;
@@ -50,6 +69,8 @@ conv_fp32_kernel(const Fp32Args a) {
   const int pix0 = blockIdx.x * TP, oc0 = blockIdx.y * TO;
   const int rs = a.r * a.s;
   const int pq = a.out_h * a.out_w;
+  float* xs_base = tiles + size_t(grp) * NS * XS;
+  float* ws_base = tiles + size_t(KG) * NS * XS + size_t(grp) * NS * WS;
 
   // Loader roles. X: thread owns pixel (t % TP) and slab rows (t / TP) + i * (NT / TP).
   const int lp = t % TP;
@@ -78,40 +99,52 @@ conv_fp32_kernel(const Fp32Args a) {
     }
     __syncthreads();
   }
-  // W: thread owns k offset (t % kBK) and channels (t / kBK) + i * (NT / kBK)  -> coalesced along k.
-  const int wk = t % kBK;
 
-  float xr[XE], wr[WE];
-  auto fetch = [&](int k0) {
+  // issue the copies of the slab that starts at reduction index k0 into ring slot `slot`
+  auto fetch = [&](int k0, int slot) {
+    float* xs = xs_base + slot * XS;
+    float* ws = ws_base + slot * WS;
 #pragma unroll
     for (int i = 0; i < XE; ++i) {
       const int kk = t / TP + i * (NT / TP);
       const int k = k0 + kk;
-      float v = 0.f;
+      const float* src = a.x;
+      bool ok = false;
       if (LUT) {
         const int2 e = lut[k];
         const int ih = ih0 + (e.y >> 16), iw = iw0 + (e.y & 0xffff);
-        if (lp_ok && unsigned(ih) < unsigned(a.h) && unsigned(iw) < unsigned(a.wd)) v = __ldg(xb + (e.x + xoff0));
+        ok = lp_ok && unsigned(ih) < unsigned(a.h) && unsigned(iw) < unsigned(a.wd);
+        if (ok) src = xb + (e.x + xoff0);
       } else if (lp_ok && k < a.k) {
         const int c = a.fd_rs.div(k), q = k - c * rs;
-        const int r = a.fd_s.div(q), s = q - r * a.s;
-        const int ih = ih0 + r, iw = iw0 + s;
-        if (ih >= 0 && ih < a.h && iw >= 0 && iw < a.wd) v = __ldg(xb + (size_t(c) * a.h + ih) * a.wd + iw);
+        const int r = a.fd_s.div(q), sx = q - r * a.s;
+        const int ih = ih0 + r, iw = iw0 + sx;
+        ok = ih >= 0 && ih < a.h && iw >= 0 && iw < a.wd;
+        if (ok) src = xb + (size_t(c) * a.h + ih) * a.wd + iw;
       }
-      xr[i] = v;
+      cp_async4(xs + kk * TP + lp, src, ok);
     }
+    if (W16) {  // TO rows x 4 vectors of 4 k-values
 #pragma unroll
-    for (int i = 0; i < WE; ++i) {
-      const int oc = oc0 + t / kBK + i * (NT / kBK);
-      const int k = k0 + wk;
-      wr[i] = (oc < a.o && k < a.k) ? __ldg(a.w + size_t(oc) * a.k + k) : 0.f;
+      for (int i = 0; i < (TO * 4 + NT - 1) / NT; ++i) {
+        const int v = t + i * NT;
+        if (v < TO * 4) {
+          const int row = v >> 2, kq = (v & 3) * 4;
+          const int oc = oc0 + row, k = k0 + kq;
+          const int left = (oc < a.o && k < a.k) ? min(4, a.k - k) * 4 : 0;
+          cp_async16(ws + row * kWPitch + kq, left ? a.w + size_t(oc) * a.k + k : a.w, left);
+        }
+      }
+    } else {
+      const int wk = t % kBK;
+#pragma unroll
+      for (int i = 0; i < kBK * TO / NT; ++i) {
+        const int row = t / kBK + i * (NT / kBK);
+        const int oc = oc0 + row, k = k0 + wk;
+        const bool ok = oc < a.o && k < a.k;
+        cp_async4(ws + row * kWPitch + wk, ok ? a.w + size_t(oc) * a.k + k : a.w, ok);
+      }
     }
-  };
-  auto stash = [&]() {
-#pragma unroll
-    for (int i = 0; i < XE; ++i) xs[grp][t / TP + i * (NT / TP)][lp] = xr[i];
-#pragma unroll
-    for (int i = 0; i < WE; ++i) ws[grp][wk][t / kBK + i * (NT / kBK)] = wr[i];
   };
 
   float acc[4][4];
@@ -120,30 +153,45 @@ conv_fp32_kernel(const Fp32Args a) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-  // every group runs the same number of rounds (slabs beyond K load zeros), so the barriers stay uniform
+  // every group runs the same number of rounds (slabs beyond K copy zeros), so the barriers stay uniform
   const int rounds = (a.k + kBK * KG - 1) / (kBK * KG);
-  fetch(grp * kBK);
-  for (int rd = 0; rd < rounds; ++rd) {
-    stash();
-    __syncthreads();
-    if (rd + 1 < rounds) fetch(((rd + 1) * KG + grp) * kBK);
 #pragma unroll
-    for (int kk = 0; kk < kBK; ++kk) {
-      const float4 xv = *reinterpret_cast<const float4*>(&xs[grp][kk][tx * 4]);
-      const float4 wv = *reinterpret_cast<const float4*>(&ws[grp][kk][ty * 4]);
-      const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
-      const float wa[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wa[j], acc[i][j]);
-    }
-    __syncthreads();
+  for (int s = 0; s < NS - 1; ++s) {  // prologue: NS - 1 slabs in flight
+    if (s < rounds) fetch((s * KG + grp) * kBK, s);
+    cp_async_commit();
   }
+  for (int rd = 0; rd < rounds; ++rd) {
+    cp_async_wait<NS - 2>();  // this thread's copies of slab rd have landed
+    __syncthreads();          // everyone's have; and everyone has finished reading the slot refilled below
+    if (rd + NS - 1 < rounds) fetch(((rd + NS - 1) * KG + grp) * kBK, (rd + NS - 1) % NS);
+    cp_async_commit();
+    const float* xs = xs_base + (rd % NS) * XS;
+    const float* ws = ws_base + (rd % NS) * WS;
+#pragma unroll
+    for (int k4 = 0; k4 < kBK; k4 += 4) {
+      float wa[4][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 wv = *reinterpret_cast<const float4*>(ws + (ty * 4 + j) * kWPitch + k4);
+        wa[j][0] = wv.x; wa[j][1] = wv.y; wa[j][2] = wv.z; wa[j][3] = wv.w;
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {  // k order: the accumulation order of the strict-FP32 contract
+        const float4 xv = *reinterpret_cast<const float4*>(xs + (k4 + kk) * TP + tx * 4);
+        const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wa[j][kk], acc[i][j]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // all slabs consumed: the tiles may be reused
 
-  if (KG > 1) {  // fold groups 1..KG-1 into group 0, in group order (the operand tiles are free now)
+  if (KG > 1) {  // fold groups 1..KG-1 into group 0, in group order
     float* red = tiles;
-    static_assert(KG == 1 || (KG - 1) * NT * 16 <= XS_FLOATS + WS_FLOATS, "reduction scratch must fit the operand tiles");
+    static_assert(KG == 1 || (KG - 1) * NT * 16 <= KG * NS * (XS + WS), "reduction scratch must fit the operand tiles");
     if (grp > 0) {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -159,20 +207,33 @@ conv_fp32_kernel(const Fp32Args a) {
         for (int j = 0; j < 4; ++j) acc[i][j] += red[(g * 16 + i * 4 + j) * NT + t];
   }
 
-  // Epilogue (fused_epilogue.cuh:11-16 order): + bias, ReLU, store.  Pixels are the fast index of NCHW.
+  // Epilogue (fused_epilogue.cuh:11-16 order): + bias, ReLU, store.  Pixels are the fast index of NCHW: a thread's four
+  // pixels leave as one 128-bit store when they lie in one image and the address is 16-byte aligned.
+  const int pixq = pix0 + tx * 4;
+  const int bq = pixq < a.pixels ? a.fd_pq.div(pixq) : 0, remq = pixq - bq * pq;
+  const bool quad_ok = pixq + 3 < a.pixels && remq + 3 < pq;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int oc = oc0 + ty * 4 + j;
     if (oc >= a.o) continue;
     const float bv = a.bias ? __ldg(a.bias + oc) : 0.f;
+    float v[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int pix = pix0 + tx * 4 + i;
-      if (pix >= a.pixels) continue;
-      const int b = a.fd_pq.div(pix), rem = pix - b * pq;
-      float v = acc[i][j] + bv;
-      if (a.relu) v = fmaxf(v, 0.f);
-      a.y[(size_t(b) * a.o + oc) * pq + rem] = v;
+      v[i] = acc[i][j] + bv;
+      if (a.relu) v[i] = fmaxf(v[i], 0.f);
+    }
+    float* dst = a.y + (size_t(bq) * a.o + oc) * pq + remq;
+    if (quad_ok && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int pix = pixq + i;
+        if (pix >= a.pixels) continue;
+        const int b = a.fd_pq.div(pix), rem = pix - b * pq;
+        a.y[(size_t(b) * a.o + oc) * pq + rem] = v[i];
+      }
     }
   }
 }
@@ -207,17 +268,40 @@ cudaError_t conv_fp32_launch(const void* x, const void* w, const void* bias, voi
   a.fd_s = FastDiv::make(s);
   a.fd_pq = FastDiv::make(out_h * out_w);
   a.fd_out_w = FastDiv::make(out_w);
-  const bool lut = (a.k + 63) / 64 * 64 <= kLutMax && int64_t(c) * h * wd < (int64_t(1) << 31) && r < 0x7fff && s <= 0xffff;
+  const bool lut = (a.k + 63) / 64 * 64 <= kLutMax && int64_t(c) * h * wd < (int64_t(1) << 31) && r < 0x7fff && s <= 0xffff && h < 0x7fff;
+  const bool w16 = a.k % 4 == 0 && (reinterpret_cast<uintptr_t>(w) & 15u) == 0;  // 128-bit copies along k
+  auto go = [&](auto kernel, dim3 grid, int threads, size_t smem) -> cudaError_t {
+    // the opt-in to more than 48 KiB of dynamic shared memory is per function and device: done once each, under a mutex
+    // (set_max_dynamic_smem of the reference, src/kernels/conv_common.cu:9-21)
+    if (smem > 48 * 1024) {
+      static std::mutex mu;
+      static std::set<std::pair<const void*, int>> done;
+      int dev = 0;
+      cudaError_t e = cudaGetDevice(&dev);
+      if (e != cudaSuccess) return e;
+      std::lock_guard<std::mutex> lock(mu);
+      const auto key = std::make_pair(reinterpret_cast<const void*>(kernel), dev);
+      if (done.find(key) == done.end()) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        done.insert(key);
+      }
+    }
+    kernel<<<grid, threads, smem, stream>>>(a);
+    return cudaGetLastError();
+  };
   if (use_small_tile(a.pixels, o)) {
+    constexpr int TP = 32, TO = 32, KG = 4, NS = 4;
+    const size_t smem = size_t(KG) * NS * (kBK * TP + TO * kWPitch) * sizeof(float);
     dim3 grid(unsigned((a.pixels + 31) / 32), unsigned((o + 31) / 32));
-    if (lut) conv_fp32_kernel<32, 32, 4, true><<<grid, 256, 0, stream>>>(a);
-    else conv_fp32_kernel<32, 32, 4, false><<<grid, 256, 0, stream>>>(a);
-  } else {
-    dim3 grid(unsigned((a.pixels + 63) / 64), unsigned((o + 63) / 64));
-    if (lut) conv_fp32_kernel<64, 64, 1, true><<<grid, 256, 0, stream>>>(a);
-    else conv_fp32_kernel<64, 64, 1, false><<<grid, 256, 0, stream>>>(a);
+    if (lut) return w16 ? go(conv_fp32_kernel<TP, TO, KG, NS, true, true>, grid, (TP / 4) * (TO / 4) * KG, smem) : go(conv_fp32_kernel<TP, TO, KG, NS, true, false>, grid, (TP / 4) * (TO / 4) * KG, smem);
+    return w16 ? go(conv_fp32_kernel<TP, TO, KG, NS, false, true>, grid, (TP / 4) * (TO / 4) * KG, smem) : go(conv_fp32_kernel<TP, TO, KG, NS, false, false>, grid, (TP / 4) * (TO / 4) * KG, smem);
   }
-  return cudaGetLastError();
+  constexpr int TP = 64, TO = 64, KG = 1, NS = 4;
+  const size_t smem = size_t(KG) * NS * (kBK * TP + TO * kWPitch) * sizeof(float);
+  dim3 grid(unsigned((a.pixels + 63) / 64), unsigned((o + 63) / 64));
+  if (lut) return w16 ? go(conv_fp32_kernel<TP, TO, KG, NS, true, true>, grid, (TP / 4) * (TO / 4) * KG, smem) : go(conv_fp32_kernel<TP, TO, KG, NS, true, false>, grid, (TP / 4) * (TO / 4) * KG, smem);
+  return w16 ? go(conv_fp32_kernel<TP, TO, KG, NS, false, true>, grid, (TP / 4) * (TO / 4) * KG, smem) : go(conv_fp32_kernel<TP, TO, KG, NS, false, false>, grid, (TP / 4) * (TO / 4) * KG, smem);
 }
 
 }  // namespace gieb

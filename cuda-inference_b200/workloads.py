@@ -61,6 +61,8 @@ CONV_WORKLOADS = {
     "c3_bf16": (ConvShape(64, 512, 28, 28, 128, 1, 1, 0, BF16), "hbm"),
     "c4a": (ConvShape(8, 512, 7, 7, 512, 3, 1, 1, FP16), "tensor"),
     "c4b": (ConvShape(16, 128, 56, 56, 256, 3, 2, 1, FP16), "tensor"),
+    # the first layer of the chain at 32 images per replica: 3 input channels, the row-gather route
+    "stem": (ConvShape(32, 3, 224, 224, 64, 7, 2, 3, FP16), "tensor"),
 }
 
 RMSNORM_WORKLOAD = dict(rows=8192, hidden=4096, dtype=BF16, eps=1e-6)
