@@ -1,6 +1,6 @@
 """Builds the reference library's OWN host layer, unmodified, on top of libgie_b200.so (no GPU needed).
 
-Where the reference checkout exists (GIE_REFERENCE_DIR, default /root/reference), its host sources -- plan cache,
+Where the reference checkout exists (the directory GIE_REFERENCE_DIR names), its host sources -- plan cache,
 ExecutionPlan, dispatcher and cost model, CUDA-graph executor, autotuner and tune cache, timing, CPU oracle, test helpers --
 are compiled from where they lie, with plain nvcc (its CMake build is not used), together with ONE file of this
 repository, cpp/src/b200_family.cpp, which stands in for the reference's kernels/*.cu, transformer/rmsnorm.cu and

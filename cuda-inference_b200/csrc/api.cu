@@ -40,7 +40,6 @@ int fail_cuda(cudaError_t e, const char* what) {
   } while (0)
 
 // ---- hardware constants of the one supported target (B200, sm_100a) -------------------------------------------------
-constexpr int kNumSms = 148;
 constexpr size_t kMaxDynamicSmem = 232448;  // 227 KiB opt-in limit per CTA
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }

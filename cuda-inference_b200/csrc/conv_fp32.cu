@@ -240,7 +240,7 @@ conv_fp32_kernel(const Fp32Args a) {
 
 bool use_small_tile(int64_t pixels, int o) {
   const int64_t big = ((pixels + 63) / 64) * ((o + 63) / 64);
-  return big < 2 * 148;
+  return big < 2 * kNumSms;
 }
 
 }  // namespace

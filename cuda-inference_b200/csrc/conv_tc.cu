@@ -164,7 +164,7 @@ cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total
   const bool vec = out_type != 2 && (reinterpret_cast<uintptr_t>(y) & 7u) == 0;
   const int64_t work = vec ? (total + 3) / 4 : total;
   int64_t blocks = (work + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > kNumSms * 16) blocks = kNumSms * 16;
   if (blocks < 1) blocks = 1;
   const FastDiv fd_pq = FastDiv::make(pq), fd_oc = FastDiv::make(out_channels);
   cudaError_t e;

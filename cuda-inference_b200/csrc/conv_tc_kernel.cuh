@@ -12,11 +12,13 @@
 //     `stages` buffers guarded by full/empty mbarriers.
 //   * One thread issues tcgen05.mma (128 x BN x 16 per instruction); the FP32 accumulator tile lives in tensor
 //     memory: lane = pixel, column = output channel.  CTAs are persistent and the accumulator is double-buffered.
-//   * Four epilogue warps read the accumulators with tcgen05.ld, add bias, apply ReLU, round once to the storage
-//     type and store to NCHW: for a fixed channel the 32 lanes of a warp hold 32 consecutive pixels, so every store
-//     instruction writes one contiguous run.  With split-K the FP32 partial tile is stored instead.
-// With pixels on M, a thread owns one pixel and all channels of the tile, which is what a contiguous-per-channel
-// NCHW store needs, and any output pointer alignment is legal (tests/test_runtime_concurrency.cu:190-216).
+//   * Eight or sixteen epilogue warps read the accumulators with tcgen05.ld, add bias, apply ReLU, round once to the
+//     storage type and store.  NCHW: for a fixed channel the 32 lanes of a warp hold 32 consecutive pixels, so every store
+//     instruction writes one contiguous run, and any output pointer alignment is legal
+//     (tests/test_runtime_concurrency.cu:190-216).  Channel-contiguous output: 32 x 32 boxes staged in shared memory and
+//     written by TMA stores.  With split-K the FP32 partial tile is stored (or exchanged inside a cluster) instead.
+// Two more forms of the same kernel, chosen per plan: CTA pairs (PAIR: 256-pixel tiles on tcgen05.mma.cta_group::2) and
+// the transposed accumulator (SWAP: lane = output channel, NCHW output through TMA stores); see the template below.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -547,8 +549,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       ptx::cluster_sync_all();
     }
   } else {
-    // ---------------- epilogue: 8 warps.  Warp w may read TMEM lanes 32*(w%4)..+31; warps 4..7 take the even
-    // 32-column chunks of a tile, warps 8..11 the odd ones (two warps per scheduler hide each other's latencies).
+    // ---------------- epilogue: EW = 8 or 16 warps.  Warp w may read TMEM lanes 32*(w%4)..+31; the EW / 4 warps of a lane
+    // quarter take the 32-column chunks of a tile in turn (several warps per scheduler hide each other's latencies).
     const int quad = warp & 3;
     const int par = (warp - kProducerWarps - 1) >> 2;  // 0 .. EG-1: which chunks this warp owns
     const int et = threadIdx.x - 32 * (kProducerWarps + 1);  // index among the epilogue threads

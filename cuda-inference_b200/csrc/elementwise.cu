@@ -158,7 +158,7 @@ maxpool2d_nhwc_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, int64_
 
 unsigned grid_for(int64_t work) {
   int64_t b = (work + 255) / 256;
-  if (b > 148 * 32) b = 148 * 32;
+  if (b > kNumSms * 32) b = kNumSms * 32;
   return unsigned(b < 1 ? 1 : b);
 }
 

@@ -15,10 +15,11 @@ enum : uint32_t {
   kStatusEpilogueTimeout = 1u << 2,
 };
 
+constexpr int kNumSms = 148;       // streaming multiprocessors of the one supported target (B200): grids are sized in multiples of it
 constexpr int kTileM = 128;        // output pixels per CTA tile = TMEM lanes = UMMA M
 constexpr int kMaxStages = 8;
 constexpr int kProducerWarps = 3;  // warps 0..2 issue the TMA loads, slab by slab in turn
-constexpr int kTcThreads = 384;    // + warp 3: MMA issuer and TMEM owner, warps 4..11: epilogue (4..19 with 16 epilogue warps)
+// warp 3: MMA issuer and TMEM owner; warps 4..11 (4..19 with 16 epilogue warps): epilogue
 static_assert((kProducerWarps + 1) % 4 == 0, "epilogue warp w must sit on TMEM lane quarter w % 4");
 
 // Division by a run-time constant as multiply-high + shift (round-up reciprocal method): exact for 0 <= n < 2^31 and

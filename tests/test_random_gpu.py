@@ -83,26 +83,31 @@ def test_random_problem(pkg, orc, oracle, case):
 
 @pytest.mark.parametrize("case", range(N_CASES))
 def test_random_configuration(pkg, orc, oracle, case):
-    """The same idea over the configuration space: random tile shape, ring depth, split-K factor and reduction mode on
-    a random tensor-path problem; points the library refuses are skipped, every accepted point must be right."""
+    """The same idea over the configuration space: random tile shape, ring depth, split-K factor, reduction mode and
+    CTA pairing on a random tensor-path problem.  Points the library refuses (with kUnsupported) are redrawn until one is
+    accepted, so every case runs; every accepted point must be right."""
     rng = np.random.default_rng(95000 + case)
-    prec = [orc.FP16, orc.BF16, orc.TF32][int(rng.integers(0, 3))]
-    k = int(rng.choice([1, 3, 3, 5]))
-    stride = int(rng.choice([1, 1, 2]))
-    pad = int(rng.integers(0, min(k, 3)))
-    c = int(rng.choice([16, 32, 64, 96, 128, 192]))
-    o = int(rng.choice([32, 64, 96, 128, 256]))
-    h, w = int(rng.integers(6, 20)), int(rng.integers(6, 20))
-    args = (int(rng.integers(1, 6)), c, h, w, o, k, k, stride, stride, pad, pad)
-    tile_k = int(rng.choice([16, 32, 64])) if prec != orc.TF32 else int(rng.choice([8, 16, 32]))
-    kw = dict(tile_m=int(rng.choice([128, 256])), tile_n=int(rng.choice([32, 64, 128, 256])), tile_k=tile_k,
-              stages=int(rng.integers(2, 7)), split_k=int(rng.choice([1, 1, 2, 3, 4, 8])), reduce=int(rng.integers(0, 3)))
-    p = orc.Problem.P(*args, precision=prec, bias=bool(rng.random() < 0.7), relu=bool(rng.random() < 0.5))
-    try:
-        plan = pkg.ConvPlan(gu.pkg_problem(pkg, p, 0), pkg.make_cfg(**kw))
-    except pkg.GieError as e:
-        assert e.code == pkg.UNSUPPORTED, str(e)
-        pytest.skip("configuration refused: " + str(e))
+    plan = None
+    for _attempt in range(200):
+        prec = [orc.FP16, orc.BF16, orc.TF32][int(rng.integers(0, 3))]
+        k = int(rng.choice([1, 3, 3, 5]))
+        stride = int(rng.choice([1, 1, 2]))
+        pad = int(rng.integers(0, min(k, 3)))
+        c = int(rng.choice([16, 32, 64, 96, 128, 192]))
+        o = int(rng.choice([32, 64, 96, 128, 256]))
+        h, w = int(rng.integers(6, 20)), int(rng.integers(6, 20))
+        args = (int(rng.integers(1, 6)), c, h, w, o, k, k, stride, stride, pad, pad)
+        tile_k = int(rng.choice([16, 32, 64])) if prec != orc.TF32 else int(rng.choice([8, 16, 32]))
+        kw = dict(tile_m=int(rng.choice([128, 256])), tile_n=int(rng.choice([32, 64, 128, 256])), tile_k=tile_k,
+                  stages=int(rng.integers(2, 7)), split_k=int(rng.choice([1, 1, 2, 3, 4, 8])), reduce=int(rng.integers(0, 3)),
+                  cta_pair=int(rng.choice([0, 1, 2])))
+        p = orc.Problem.P(*args, precision=prec, bias=bool(rng.random() < 0.7), relu=bool(rng.random() < 0.5))
+        try:
+            plan = pkg.ConvPlan(gu.pkg_problem(pkg, p, 0), pkg.make_cfg(**kw))
+            break
+        except pkg.GieError as e:
+            assert e.code == pkg.UNSUPPORTED, str(e)
+    assert plan is not None, "no accepted configuration in 200 draws"
     x, wt, b = oracle.make_conv_data(p, 96000 + case, case % 4)
     ref, scale = oracle.conv2d(p, x, wt, b if p.has_bias else None)
     got, plan, _ = gu.run_conv(pkg, oracle, p, x, wt, b if p.has_bias else None, plan=plan)
