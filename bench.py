@@ -150,7 +150,8 @@ def share_tuned_configs(ranks):
 
 def time_chain(torch, pkg, ranks, steps, warmup, global_batch=256, layout="nchw", tune=False, world=None, keep=False, protocol=True):
     """ResNet-50-shaped FP16 chain, one CUDA graph per replica, batch sharded contiguously over the ranks.
-    layout "nchw": the reference API's contract layer by layer; "nhwc": channel-contiguous tensors, prepacked weights and
+    layout "nchw": the reference API's contract layer by layer; "nchw_fused": the same NCHW tensors with each block's residual
+    add + ReLU inside the epilogue of its last convolution; "nhwc": channel-contiguous tensors, prepacked weights and
     the residual adds fused into the convolution epilogues.  world = 1 makes every rank run the WHOLE batch (the one-GPU
     point of the scaling curve, measured in the same run).  Times exactly `steps` passes between one event pair (max
     over ranks) and, beside it, the 30-sample protocol."""
@@ -158,11 +159,13 @@ def time_chain(torch, pkg, ranks, steps, warmup, global_batch=256, layout="nchw"
     w = ranks.world if world is None else world
     r = ranks.rank if world is None else 0
     _, count = shard_batch(global_batch, w, r)
+    fuse = layout == "nchw_fused"   # NCHW tensors, residual add + ReLU inside the epilogue of each block's last convolution
+    tensor_layout = "nchw" if fuse else layout
     if tune:
         if ranks.rank == 0:
-            ConvChain(max(count, 1), 1, 224, seed=0, layout=layout, tune=True)  # measures; the table stays in the process
+            ConvChain(max(count, 1), 1, 224, seed=0, layout=tensor_layout, tune=True, fuse_residual=fuse)  # measures; the table stays in the process
         share_tuned_configs(ranks)
-    chain = ConvChain(max(count, 1), 1, 224, seed=0, layout=layout, tune=tune)
+    chain = ConvChain(max(count, 1), 1, 224, seed=0, layout=tensor_layout, tune=tune, fuse_residual=fuse)
     g = torch.Generator(device="cuda")
     g.manual_seed(100 + r)
     chain.input.copy_(torch.randn(chain.input.numel(), device="cuda", generator=g).to(torch.float16))
@@ -560,7 +563,7 @@ def chain_block(torch, pkg, ranks, peaks, steps, do_cpu):
     against it.  On one GPU, rank 0 also runs the CPU baseline of the chain on a sub-batch and checks the GPU output."""
     out = {}
     passes = max(50, min(steps, 200))
-    for key, layout, tune in (("nchw", "nchw", False), ("nhwc_fused_tuned", "nhwc", True)):
+    for key, layout, tune in (("nchw", "nchw", False), ("nchw_fused", "nchw_fused", False), ("nhwc_fused_tuned", "nhwc", True)):
         ch = time_chain(torch, pkg, ranks, steps=passes, warmup=3, layout=layout, tune=tune, keep=True)
         chain = ch.pop("_chain")
         ch["frac_of_tensor"] = ch["tflops"] / ranks.world / peaks["bf16_tflops"]
@@ -781,7 +784,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=200)
     ap.add_argument("--workload", default="c2", help="c1 | c2 | c3_fp16 | c3_bf16 | c4a | c4b | stem | chain")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layout", default="nchw", choices=["nchw", "nhwc"], help="--workload chain: tensor layout between layers")
+    ap.add_argument("--layout", default="nchw", choices=["nchw", "nchw_fused", "nhwc"], help="--workload chain: tensor layout between layers")
     ap.add_argument("--chain-batch", type=int, default=256, help="--workload chain: global batch (256 is the benchmark's; 32 is one replica's share on 8 GPUs)")
     ap.add_argument("--tune", action="store_true", help="--workload chain: measure candidate configurations per layer first")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

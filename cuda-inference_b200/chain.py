@@ -66,7 +66,7 @@ def set_tuned_configs(table: dict) -> None:
 
 class ConvChain:
     def __init__(self, batch: int, precision: int = FP16, image: int = 224, seed: int = 0, weights=None, device=None,
-                 layout: str = "nchw", tune: bool = False):
+                 layout: str = "nchw", tune: bool = False, fuse_residual: bool | None = None):
         """weights: optional list of (w, b) host numpy arrays in storage bit patterns per convolution, in the order of
         resnet50_chain (tests); when None, weights are generated on the device from `seed` + layer index with the
         benchmark distributions.
@@ -75,6 +75,9 @@ class ConvChain:
         layout "nhwc": the input image stays NCHW; every later tensor is channel-contiguous, weights are prepacked once
         at construction, and each block's residual add + ReLU runs inside the epilogue of its last convolution
         (no repack launches, no add launches).
+        fuse_residual: each block's residual add + ReLU inside the epilogue of its last convolution (always in the nhwc
+        layout; in the nchw layout an option, default off: the unfused chain is the reference API's operator set layer by
+        layer, the fused one needs the residual operand this library adds to it).
         tune: time candidate_cfgs() for every distinct layer on this GPU (a few launches each, on scratch buffers of the
         chain) and build each plan with the fastest; the choice is remembered per process."""
         torch = _torch()
@@ -90,7 +93,8 @@ class ConvChain:
         self.base_ops = base_ops  # the unfused layer list (convolutions, max-pool, residual adds)
         self.oihw_weights = []    # OIHW weights per entry of self.convs, as generated (the nhwc layout launches converted copies)
         base_relu = {op.layer: op.relu for op in base_ops if op.kind == "conv"}
-        self.ops = fuse_residuals(base_ops) if nhwc else base_ops
+        self.fused = True if nhwc else bool(fuse_residual)
+        self.ops = fuse_residuals(base_ops) if self.fused else base_ops
         self.flops = chain_flops(self.ops)
         self.slots = {i: torch.empty(batch * c * h * w, dtype=self.dtype, device=self.device) for i, (c, h, w) in self.slot_shapes.items()}
         self.convs = []  # (op, plan, w, b) in launch order; w is prepacked in the nhwc layout
@@ -101,7 +105,7 @@ class ConvChain:
             s = op.shape
             li = op.layer
             # the chain owns its weights: they are converted once, here, to the layout each plan's kernel reads
-            flags = FLAG_WEIGHTS_PREPACKED
+            flags = FLAG_WEIGHTS_PREPACKED | (FLAG_RESIDUAL if (self.fused and op.other >= 0) else 0)
             if nhwc:
                 flags = FLAG_OUTPUT_NHWC | FLAG_WEIGHTS_PREPACKED
                 if op.src != 0:
@@ -195,7 +199,7 @@ class ConvChain:
             if op.kind == "conv":
                 _, plan, w, b = self.convs[ci]
                 ci += 1
-                if op.other >= 0 and self.layout == "nhwc":
+                if op.other >= 0 and self.fused:
                     plan.launch_fused(self.slots[op.src].data_ptr(), w.data_ptr(), b.data_ptr(), self.slots[op.other].data_ptr(),
                                       self.slots[op.dst].data_ptr(), self.ws_ptr, self.ws_bytes, stream)
                 else:

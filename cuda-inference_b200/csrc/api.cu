@@ -264,6 +264,14 @@ bool pdl_enabled() {
   }();
   return on;
 }
+// GIEB_DISABLE_PREFETCH=1 switches the L2 prefetches that precede the dependency waits off (a debugging aid).
+bool prefetch_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("GIEB_DISABLE_PREFETCH");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
 }  // namespace gieb
 
 namespace {
@@ -365,7 +373,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   }
   // NCHW output whose planes are 16-byte multiples, 16-bit types: 128- and 256-channel tiles that a CTA finishes alone
   // keep the accumulator transposed (lane = output channel) and write their boxes with TMA stores.
-  bool swap_ok = !tf32 && !(d.flags & (GIEB_FLAG_OUTPUT_NHWC | GIEB_FLAG_RESIDUAL)) && g.pq % 8 == 0;
+  bool swap_ok = !tf32 && !(d.flags & GIEB_FLAG_OUTPUT_NHWC) && g.pq % 8 == 0;
   bool swap_forced = false;
   if (const char* e = getenv("GIEB_TRANSPOSED_ACC")) {  // debugging aid: 0 = pixel-lane kernels only, 2 = transposed wherever it is possible
     swap_ok = swap_ok && e[0] != '0';
@@ -799,6 +807,7 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   if (r.swap) {
     const uintptr_t ya = reinterpret_cast<uintptr_t>(y);
     p.out_vec = (pl->g.pq % 4 == 0 && ya % 8 == 0) ? 4 : ((pl->g.pq % 2 == 0 && ya % 4 == 0) ? 2 : 1);
+    p.res_vec = reinterpret_cast<uintptr_t>(residual) % 16 == 0 ? 1 : 0;
     if (ya % 16 == 0) {  // y as {P*Q, O, N}: boxes of 32 pixels x 32 channels, 64-byte swizzle
       const CUtensorMapDataType dt = d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
       const cuuint64_t pq = cuuint64_t(pl->g.pq);

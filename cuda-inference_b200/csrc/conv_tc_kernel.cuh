@@ -84,6 +84,26 @@ __device__ __forceinline__ void store_chunk_tail(const uint32_t (&v)[32], const 
   }
 }
 
+// A full chunk with a residual in the output's own layout.  Nothing proves to the compiler that the residual and the output
+// do not overlap, so written as one loop every load would wait for the store before it: the loads of eight channels are
+// issued as a group, then their eight stores.
+template <typename T, bool RELU>
+__device__ __forceinline__ void store_chunk_full_res(const uint32_t (&v)[32], const float* __restrict__ bias, T* dst, const T* res,
+                                                     int64_t stride) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float r[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = load_as_float(res + int64_t(g * 8 + j) * stride);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float a = __uint_as_float(v[g * 8 + j]) + bias[g * 8 + j] + r[j];
+      if (RELU) a = fmaxf(a, 0.f);
+      dst[int64_t(g * 8 + j) * stride] = round_to<T>(a);
+    }
+  }
+}
+
 // Eight consecutive channels of one accumulator row: + bias (+ residual) -> ReLU -> one rounding, packed as 16 bytes.
 template <typename T, bool RELU, bool RES>
 __device__ __forceinline__ uint4 finish8(const uint32_t (&v)[32], int q, const float* __restrict__ bias, uint4 r) {
@@ -160,23 +180,34 @@ __device__ __forceinline__ void chunk_to_staging(const uint32_t (&v)[32], const 
   }
 }
 
-// Transposed accumulator: 32 consecutive pixels of ONE channel (this lane's) -> + bias, ReLU on the rounded pair (rounding is
-// monotonic and keeps zero), packed as 64 bytes and written as the lane's row of the warp's staging box (32 rows of 64
+// Transposed accumulator: 32 consecutive pixels of ONE channel (this lane's) -> + bias (+ residual), ReLU on the rounded pair
+// (rounding is monotonic and keeps zero), packed as 64 bytes and written as the lane's row of the warp's staging box (32 rows of 64
 // bytes, 64-byte swizzled: 16-byte cell q of row r sits at cell q ^ ((r >> 1) & 3); conflict-free).
-template <typename T, bool RELU>
-__device__ __forceinline__ void row_to_staging(const uint32_t (&v)[32], float bias, uint8_t* box, int lane) {
+template <typename T, bool RES>
+__device__ __forceinline__ void row_to_staging(const uint32_t (&v)[32], float bias, const uint4 (&res)[4], bool relu, uint8_t* box, int lane) {
   uint32_t w[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    const float a0 = __uint_as_float(v[2 * j]) + bias, a1 = __uint_as_float(v[2 * j + 1]) + bias;
+    float a0 = __uint_as_float(v[2 * j]) + bias, a1 = __uint_as_float(v[2 * j + 1]) + bias;
+    if constexpr (RES) {  // the residual's 32 pixels of this lane's channel, in storage type
+      const uint4& r4 = res[j >> 2];
+      const uint32_t rw = (j & 3) == 0 ? r4.x : ((j & 3) == 1 ? r4.y : ((j & 3) == 2 ? r4.z : r4.w));
+      if constexpr (std::is_same<T, __half>::value) {
+        const float2 rf = __half22float2(*reinterpret_cast<const __half2*>(&rw));
+        a0 += rf.x; a1 += rf.y;
+      } else {
+        const float2 rf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw));
+        a0 += rf.x; a1 += rf.y;
+      }
+    }
     if constexpr (std::is_same<T, __half>::value) {
       __half2 o = __floats2half2_rn(a0, a1);
-      if (RELU) o = __hmax2(o, __half2half2(__ushort_as_half(0)));
-      w[j] = *reinterpret_cast<const uint32_t*>(&o);
+      const __half2 oz = __hmax2(o, __half2half2(__ushort_as_half(0)));
+      w[j] = relu ? *reinterpret_cast<const uint32_t*>(&oz) : *reinterpret_cast<const uint32_t*>(&o);
     } else {
       __nv_bfloat162 o = __floats2bfloat162_rn(a0, a1);
-      if (RELU) o = __hmax2(o, __bfloat162bfloat162(__ushort_as_bfloat16(0)));
-      w[j] = *reinterpret_cast<const uint32_t*>(&o);
+      const __nv_bfloat162 oz = __hmax2(o, __bfloat162bfloat162(__ushort_as_bfloat16(0)));
+      w[j] = relu ? *reinterpret_cast<const uint32_t*>(&oz) : *reinterpret_cast<const uint32_t*>(&o);
     }
   }
   const int sw = (lane >> 1) & 3;
@@ -205,6 +236,9 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const float
   if (nvalid == 32 && res == nullptr) {
     if (relu) store_chunk_full<T, true>(v, bias, dst, stride);
     else store_chunk_full<T, false>(v, bias, dst, stride);
+  } else if (nvalid == 32) {
+    if (relu) store_chunk_full_res<T, true>(v, bias, dst, res, stride);
+    else store_chunk_full_res<T, false>(v, bias, dst, res, stride);
   } else {
     if (relu) store_chunk_tail<T, true>(v, bias, dst, res, stride, nvalid);
     else store_chunk_tail<T, false>(v, bias, dst, res, stride, nvalid);
@@ -292,6 +326,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     ptx::prefetch_tensormap(&tm_wgt);
     if (p.out_tma) ptx::prefetch_tensormap(&tm_out);
     if (p.res_tma) ptx::prefetch_tensormap(&tm_res);
+  }
+  // The barriers are initialised by a thread of the last epilogue warp, which has nothing else to do before the set-up
+  // barrier: the producers decode their first tile meanwhile (~25 cycles per mbarrier.init, one after the other).
+  if (threadIdx.x == 32 * (kProducerWarps + EW)) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(&full_bar[s], 1);
       ptx::mbar_init(&empty_bar[s], 1);
@@ -300,7 +338,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       ptx::mbar_init(&acc_full[b], 1);
       ptx::mbar_init(&acc_empty[b], PAIR ? 2 * EW : EW);  // one arrival per epilogue warp (of both CTAs of a pair: the leader's barrier collects them)
     }
-    for (int b = 0; b < EW * kEpiBufs; ++b) ptx::mbar_init(&res_bar[b], 1);
+    if (p.res_tma)
+      for (int b = 0; b < EW * kEpiBufs; ++b) ptx::mbar_init(&res_bar[b], 1);
     ptx::fence_mbar_init();
   }
   if (warp == kProducerWarps) {
@@ -634,6 +673,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         base_h[h] = p.out_nhwc ? (int64_t(img) * p.pq + pix) * p.out_channels + n0 : (int64_t(img) * p.out_channels + n0) * p.pq + pix;
       }
 
+      // A residual in NCHW layout is read by plain loads, eight channels at a time: too few bytes in flight to pull a large
+      // tensor from HBM.  Its lines start their way into L2 now, while the main loop of this tile still runs: lane j asks
+      // for the run of channel j of every chunk this warp owns (from the warp's first and last pixel: the 32 pixels may
+      // lie in two images).
+      if (!SWAP && p.residual != nullptr && !p.out_nhwc && !p.out_tma) {
+        const int esz = p.is_tf32 ? 4 : 2;
+        const uint8_t* rb = static_cast<const uint8_t*>(p.residual);
+#pragma unroll
+        for (int h = 0; h < MH; ++h) {
+          if (h >= halves) break;
+          const int64_t b_first = __shfl_sync(0xffffffffu, base_h[h], 0), b_last = __shfl_sync(0xffffffffu, base_h[h], 31);
+          const bool ok_first = __shfl_sync(0xffffffffu, int(m_ok_h[h]), 0) != 0, ok_last = __shfl_sync(0xffffffffu, int(m_ok_h[h]), 31) != 0;
+          for (int chunk = par; chunk < BN / 32; chunk += EG) {
+            const int ch = chunk * 32 + lane;
+            if (n0 + ch >= p.out_channels) break;
+            if (ok_first) ptx::prefetch_l2(rb + (b_first + int64_t(ch) * cstride) * esz);
+            if (ok_last) ptx::prefetch_l2(rb + (b_last + int64_t(ch) * cstride) * esz);
+          }
+        }
+      }
+
       const bool ok = ptx::mbar_wait(&acc_full[buf], acc_phase, p.status, kStatusEpilogueTimeout, p.wait_limit);
       __syncwarp();
       ptx::tc_fence_after_sync();
@@ -735,16 +795,41 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           if (ch0 >= p.out_channels || mstart >= p.m_total) continue;  // warp-uniform
           uint32_t v[32];
           ptx::tmem_ld_32x32b_x32(acc + (uint32_t(quad * 32) << 16) + uint32_t(hc * (MH * 128) + pc * 32), v);
+          // Fused residual (same NCHW layout as the output): this lane's channel, four groups of 8 consecutive pixels.  A
+          // group never straddles an image (P*Q % 8 == 0); its address is decoded on its own because a unit may.  The
+          // loads are in flight while the tensor-memory load completes.
+          uint4 rr[4];
+          const bool with_res = p.residual != nullptr;
+          if (with_res) {
+            const uint8_t* rb = static_cast<const uint8_t*>(p.residual);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              bool q_ok;
+              int qimg, qpix;
+              decode_row(mstart + q * 8, q_ok, qimg, qpix);
+              rr[q] = make_uint4(0u, 0u, 0u, 0u);
+              if (q_ok && ch0 + lane < p.out_channels) {
+                const uint8_t* src = rb + ((int64_t(qimg) * p.out_channels + ch0 + lane) * p.pq + qpix) * 2;
+                if (p.res_vec) rr[q] = *reinterpret_cast<const uint4*>(src);
+                else {  // residual not 16-byte aligned: element by element
+                  const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
+                  rr[q] = make_uint4(uint32_t(s16[0]) | (uint32_t(s16[1]) << 16), uint32_t(s16[2]) | (uint32_t(s16[3]) << 16),
+                                     uint32_t(s16[4]) | (uint32_t(s16[5]) << 16), uint32_t(s16[6]) | (uint32_t(s16[7]) << 16));
+                }
+              }
+            }
+          }
           ptx::tmem_ld_wait();
           const float bv = bias_t[hc * 128 + quad * 32 + lane];
           if (lane == 0) ptx::bulk_wait_group_read0();  // the previous store of this warp has left the box
           __syncwarp();
+          const bool relu = p.relu != 0;
           if (p.is_bf16) {
-            if (p.relu) row_to_staging<__nv_bfloat16, true>(v, bv, box, lane);
-            else row_to_staging<__nv_bfloat16, false>(v, bv, box, lane);
+            if (with_res) row_to_staging<__nv_bfloat16, true>(v, bv, rr, relu, box, lane);
+            else row_to_staging<__nv_bfloat16, false>(v, bv, rr, relu, box, lane);
           } else {
-            if (p.relu) row_to_staging<__half, true>(v, bv, box, lane);
-            else row_to_staging<__half, false>(v, bv, box, lane);
+            if (with_res) row_to_staging<__half, true>(v, bv, rr, relu, box, lane);
+            else row_to_staging<__half, false>(v, bv, rr, relu, box, lane);
           }
           bool u_ok;
           int img, pix0;

@@ -60,6 +60,7 @@ struct FastDiv {
 // programmatic dependency of the graph).
 // GIEB_DISABLE_PDL=1 in the environment launches every kernel fully serialised (a debugging aid).
 bool pdl_enabled();
+bool prefetch_enabled();
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -139,6 +140,7 @@ struct ConvTcParams {
   float* partial;     // [splits][B*O*P*Q] FP32 partial sums in the output's element order (workspace reduction), else null
   uint32_t* status;
   long long wait_limit;  // SM cycles a device-side wait may last before its role gives up and reports to *status
+  int res_vec;           // transposed-accumulator epilogue: the residual may be read as 16-byte vectors (pointer 16-byte aligned)
   uint32_t debug_skip;   // test hook, 0 in production: bit 0 = the producers load nothing, bit 1 = the MMA warp issues nothing
 };
 

@@ -143,6 +143,9 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// One 128-byte line into L2: a cache fill at the device's coherence point, legal before grid_dep_wait() even if the earlier
+// kernel still writes the line, because those writes go through L2 as well.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory"); }
 // im2col-mode 4-D load over an NHWC tensor {C, W, H, N}: starting base pixel (w, h, n), channel c, filter-tap
 // offsets (off_w, off_h).  The unit walks `pixelsPerColumn` base pixels (w fastest, then h, then n) inside the
 // descriptor's bounding box and fetches `channelsPerPixel` channels at base + offset for each, zero-filling

@@ -129,15 +129,32 @@ struct RepackJob {
   int hw_tiles, c_tiles;
   int span;  // mode 2: channels per CTA
   unsigned blocks;  // hw_tiles * c_tiles * batch
+  int prefetch;     // (read from the first job) L2 prefetch of the source lines before the dependency wait
 };
+
+// The 128-byte lines one CTA is about to read, one prefetch per line, never outside the source tensor.
+__device__ __forceinline__ void prefetch_source(const RepackJob& j, int hw_tile, int c_tile, int bi) {
+  const int t = threadIdx.x;
+  if (j.mode == 2) {
+    const int c0 = c_tile * j.span;
+    const int nch = min(j.span, j.C - c0);
+    if (nch <= 0) return;
+    const uint8_t* s = reinterpret_cast<const uint8_t*>(j.src + (size_t(bi) * j.C + c0) * j.HW);
+    const int bytes = nch * j.HW * 2;
+    for (int o = t * 128; o < bytes + 127; o += 256 * 128) ptx::prefetch_l2(s + min(o, bytes - 1));
+  } else if (t < 2 * kTile) {
+    const int ch = c_tile * kTile + (t >> 1), px0 = hw_tile * kTile;
+    if (ch < j.C && px0 < j.HW) {
+      const uint8_t* row = reinterpret_cast<const uint8_t*>(j.src + (size_t(bi) * j.C + ch) * j.HW + px0);
+      const int bytes = min(kTile, j.HW - px0) * 2;
+      ptx::prefetch_l2(row + ((t & 1) ? bytes - 1 : 0));  // a 128-byte run touches at most two lines
+    }
+  }
+}
 
 // Up to two jobs in one launch (activations + weights): block indices [0, a.blocks) belong to job a, the rest to job b.
 __global__ void __launch_bounds__(256) repack_jobs_kernel(const RepackJob a, const RepackJob b) {
   __shared__ __align__(16) uint32_t smem[kTile * kLdWords];  // 8448 B >= kTile * kSmallHwMax * 2 = 8192 B
-  // Launched with programmatic stream serialization: wait for the previous kernel of the stream (it may still read
-  // the destination or write the source), then let the convolution kernel behind this one begin its set-up.
-  ptx::grid_dep_wait();
-  ptx::grid_dep_launch();
   const bool first = blockIdx.x < a.blocks;
   const RepackJob& j = first ? a : b;
   unsigned id = first ? blockIdx.x : blockIdx.x - a.blocks;
@@ -145,6 +162,14 @@ __global__ void __launch_bounds__(256) repack_jobs_kernel(const RepackJob a, con
   id /= unsigned(j.hw_tiles);
   const int c_tile = int(id % unsigned(j.c_tiles));
   const int bi = int(id / unsigned(j.c_tiles));
+  // Launched with programmatic stream serialization, so this CTA may be resident well before the previous kernel of the
+  // stream has finished.  Meanwhile it starts its source lines on their way from HBM into L2 (a cache fill at the
+  // coherence point: harmless even if that kernel still writes them), so that the loads below hit L2.
+  if (a.prefetch) prefetch_source(j, hw_tile, c_tile, bi);
+  // Wait for the previous kernel (it may still read the destination or write the source), then let the convolution
+  // kernel behind this one begin its set-up.
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
   if (j.mode == 2) repack_small_hw(reinterpret_cast<uint16_t*>(smem), j.src, j.dst, j.C, j.HW, j.Cp, j.span, c_tile, bi);
   else if (j.mode == 1) repack_tile<1>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
   else if (j.mode == 3) repack_tile<2>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
@@ -323,6 +348,7 @@ RepackJob make_job(const void* src, void* dst, int batch, int channels, int hw, 
     j.hw_tiles = (hw + kTile - 1) / kTile;
   }
   j.blocks = 0;
+  j.prefetch = prefetch_enabled() ? 1 : 0;
   return j;
 }
 

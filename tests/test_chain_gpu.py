@@ -25,14 +25,14 @@ def _host_weights(orc, oracle, ops, precision, seed):
     return out
 
 
-def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed, layout="nchw", tune=False):
+def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed, layout="nchw", tune=False, fuse_residual=None):
     import torch
     from cuda_inference_b200.chain import ConvChain
     from cuda_inference_b200 import workloads as wl
     ops, _ = wl.resnet50_chain(batch, precision, image)
     hw = _host_weights(orc, oracle, ops, precision, seed)
     chain = ConvChain(batch, precision, image, weights=[(oracle.to_bits16(precision, w), oracle.to_bits16(precision, b)) for w, b in hw],
-                      layout=layout, tune=tune)
+                      layout=layout, tune=tune, fuse_residual=fuse_residual)
     x = oracle.quantize(precision, oracle.rng(seed + 1000).draw(orc.DIST_NORMAL, batch * 3 * image * image))
     chain.input.view(torch.int16).copy_(torch.from_numpy(oracle.to_bits16(precision, x).view(np.int16)).cuda())
     for t in list(chain.slots.values())[1:]:
@@ -58,7 +58,7 @@ def _run_chain_case(pkg, orc, oracle, batch, image, precision, seed, layout="nch
         assert np.all(np.isfinite(got)), f"non-finite output at {op.kind} -> slot {op.dst}"
         if op.kind == "conv":
             s = op.shape
-            fused = layout == "nhwc" and op.other >= 0
+            fused = chain.fused and op.other >= 0
             p = orc.Problem.P(s.batch, s.in_channels, s.in_h, s.in_w, s.out_channels, s.kernel, s.kernel, s.stride, s.stride, s.pad, s.pad,
                               precision, True, op.relu and not fused)
             w, b = hw[op.layer]
@@ -102,6 +102,15 @@ def test_chain_channel_contiguous_fused_residual_fp16(pkg, orc, oracle):
     of each block's last convolution.  One launch per convolution except the stem (which repacks the NCHW image)."""
     worst, nodes = _run_chain_case(pkg, orc, oracle, batch=2, image=64, precision=orc.FP16, seed=0, layout="nhwc")
     assert 53 + 2 <= nodes <= 53 + 2 + 20  # convolutions + stem repack + max-pool (+ workspace reductions of tiny layers)
+
+
+def test_chain_nchw_fused_residual(pkg, orc, oracle):
+    """NCHW tensors throughout, residual add + ReLU inside the epilogue of each block's last convolution (no add launches).
+    At 224 x 224 the 56 x 56 and 28 x 28 layers take the transposed-accumulator kernels, which read the residual as the
+    lane's own 64-byte pixel runs; the small case runs BF16 through the pixel-lane kernels."""
+    worst, nodes = _run_chain_case(pkg, orc, oracle, batch=1, image=224, precision=orc.FP16, seed=4, fuse_residual=True)
+    assert nodes <= 53 + 1 + 53 + 20  # no add launches: convolutions, max-pool, at most one repack each (+ reductions)
+    _run_chain_case(pkg, orc, oracle, batch=3, image=32, precision=orc.BF16, seed=6, fuse_residual=True)
 
 
 def test_chain_with_measured_configurations(pkg, orc, oracle):

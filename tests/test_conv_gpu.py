@@ -174,6 +174,42 @@ def test_transposed_accumulator_nchw_stores(pkg, orc, oracle, case, prec_name, m
     _check(oracle, p, got, ref, scale, f"transposed-accumulator case {case} {kw} yoff={yoff} {prec_name}")
 
 
+@pytest.mark.parametrize("case", [0, 1, 2, 3, 9, 11, 12])
+@pytest.mark.parametrize("res_off", [0, 1])
+def test_transposed_accumulator_fused_residual(pkg, orc, oracle, case, res_off, monkeypatch):
+    """y = act(conv + bias + residual) with one rounding on the NCHW TMA-store kernels: every lane reads the residual's 32
+    pixels of its own channel (16-byte vectors, or element by element when the residual pointer is off by 2 bytes); units
+    that cross into the next image, channel tails and clipped pixel tails included."""
+    import torch
+    monkeypatch.setenv("GIEB_TRANSPOSED_ACC", "2")
+    args, kw, yoff = SWAP_CASES[case]
+    prec = orc.FP16 if case % 2 == 0 else orc.BF16
+    relu = case % 3 != 0
+    p_lin = orc.Problem.P(*args, precision=prec, bias=True, relu=False)
+    p = orc.Problem.P(*args, precision=prec, bias=True, relu=relu)
+    x, w, b = oracle.make_conv_data(p, 8100 + case, case % 4)
+    lin, scale = oracle.conv2d(p_lin, x, w, b)
+    res = oracle.quantize(prec, oracle.rng(8200 + case).uniform(-1, 1, lin.size)).reshape(lin.shape)
+    ref = lin.astype(np.float64) + res.astype(np.float64)
+    ref = (np.maximum(ref, 0.0) if relu else ref).astype(np.float32)
+    scale = (scale.astype(np.float64) + np.abs(res)).astype(np.float32)
+    plan = pkg.ConvPlan(gu.pkg_problem(pkg, p, pkg.FLAG_RESIDUAL), pkg.make_cfg(**kw))
+    assert plan.info.threads_per_block == 384 and plan.info.cfg.split_k == 1
+    stream = torch.cuda.current_stream().cuda_stream
+    tx, px = gu.to_device_storage(oracle, prec, x)
+    tw, pw = gu.to_device_storage(oracle, prec, w)
+    tb, pb = gu.to_device_storage(oracle, prec, b)
+    tr, pr = gu.to_device_storage(oracle, prec, res, res_off)
+    out = gu.OutBuf(prec, int(np.prod(p.y_shape)), yoff)
+    ws = gu.Workspace(plan.workspace_bytes)
+    for _ in range(2):
+        plan.launch_fused(px, pw, pb, pr, out.ptr, ws.ptr if plan.workspace_bytes else None, plan.workspace_bytes, stream)
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    ws.check_guard()
+    _check(oracle, p, out.read(oracle).reshape(p.y_shape), ref, scale, f"transposed accumulator + residual, case {case} res_off={res_off}")
+
+
 DIRECT_CASES = [
     # 1x1 / stride 1 / pad 0 with H*W % 8 == 0: activations are read straight from NCHW (pixel-major operand)
     ((2, 64, 8, 8, 64, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=64, tile_k=64, stages=2), 0),
