@@ -259,14 +259,19 @@ def make_conv_sets(torch, pkg, shape, nsets, seed):
     touch different memory (the rotation is larger than L2)."""
     g = torch.Generator(device="cuda")
     g.manual_seed(seed)
-    dt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[shape.precision]
+    fp8 = shape.precision == 4   # FP8 E4M3 x and w (bit patterns as bytes), float bias, FP16 y
+    dt = torch.float16 if fp8 else {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[shape.precision]
     fan_in = shape.in_channels * shape.kernel * shape.kernel
     bound = (6.0 / fan_in) ** 0.5
     sets = []
     for _ in range(nsets):
-        x = (torch.rand(shape.x_elems, device="cuda", generator=g) * 2 - 1).to(dt)
-        w = ((torch.rand(shape.w_elems, device="cuda", generator=g) * 2 - 1) * bound).to(dt)
-        b = ((torch.rand(shape.out_channels, device="cuda", generator=g) * 2 - 1) * 0.1).to(dt)
+        x = torch.rand(shape.x_elems, device="cuda", generator=g) * 2 - 1
+        w = (torch.rand(shape.w_elems, device="cuda", generator=g) * 2 - 1) * bound
+        b = (torch.rand(shape.out_channels, device="cuda", generator=g) * 2 - 1) * 0.1
+        if fp8:
+            x, w = x.to(torch.float8_e4m3fn).view(torch.uint8), w.to(torch.float8_e4m3fn).view(torch.uint8)
+        else:
+            x, w, b = x.to(dt), w.to(dt), b.to(dt)
         y = torch.empty(shape.y_elems, device="cuda", dtype=dt)
         sets.append((x, w, b, y))
     return sets
@@ -596,6 +601,8 @@ def run_ours(args):
     if args.workload == "chain":
         return run_chain_primary(args, torch, pkg, ranks, peaks, peak_kind, local_rank)
     shape, bound = wl.CONV_WORKLOADS[args.workload]
+    if shape.precision == wl.FP8_E4M3:
+        raise SystemExit("c2_fp8 (an extension without a CPU-reference arm) is measured in the secondary block of the default run")
     sampler = ClockSampler(local_rank)
     sampler.start()
     cfg = None
@@ -667,7 +674,7 @@ def run_ours(args):
         out["chain"] = chain_block(torch, pkg, ranks, peaks, args.steps, do_cpu)
         if world == 1:
             sec = {}
-            for name in ("c1", "c3_fp16", "c3_bf16", "c4a", "c4b"):
+            for name in ("c1", "c3_fp16", "c3_bf16", "c4a", "c4b", "c2_fp8"):
                 if name == args.workload:
                     continue
                 sh, bd = wl.CONV_WORKLOADS[name]

@@ -21,6 +21,7 @@ OK, INVALID_ARGUMENT, UNSUPPORTED, WORKSPACE_TOO_SMALL, CUDA_ERROR, INTERNAL = 0
 STATUS_NAMES = {0: "ok", 1: "invalid_argument", 2: "unsupported", 3: "workspace_too_small", 4: "cuda_error", 7: "internal"}
 # gie::Precision order
 FP32, FP16, BF16, TF32 = 0, 1, 2, 3
+FP8_E4M3 = 4  # an extension of this library: FP8 E4M3 x and w, float bias, FP16 y (see include/gie_b200.h)
 FLAG_BIAS_FP32, FLAG_WEIGHTS_PREPACKED = 1, 2
 FLAG_INPUT_NHWC, FLAG_OUTPUT_NHWC, FLAG_RESIDUAL = 4, 8, 16
 

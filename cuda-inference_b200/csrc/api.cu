@@ -76,7 +76,7 @@ int validate(const gieb_conv_desc* d) {
   if (d->pad_h < 0 || d->pad_w < 0) return fail(GIEB_INVALID_ARGUMENT, "padding must be non-negative");
   if (d->dilation_h != 1 || d->dilation_w != 1) return fail(GIEB_UNSUPPORTED, "dilation != 1 is not supported");
   if (d->groups != 1) return fail(GIEB_UNSUPPORTED, "grouped convolution is not supported");
-  if (d->precision < GIEB_FP32 || d->precision > GIEB_TF32) return fail(GIEB_INVALID_ARGUMENT, "unknown precision id %d", d->precision);
+  if (d->precision < GIEB_FP32 || d->precision > GIEB_FP8_E4M3) return fail(GIEB_INVALID_ARGUMENT, "unknown precision id %d", d->precision);
   if (int64_t(d->in_h) + 2 * d->pad_h < d->kernel_h || int64_t(d->in_w) + 2 * d->pad_w < d->kernel_w)
     return fail(GIEB_INVALID_ARGUMENT, "kernel larger than padded input");
   const Geometry g = geometry(*d);
@@ -284,7 +284,10 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   memset(&c, 0, sizeof(c));
   if (user) c = *user;
 
-  const bool tf32 = d.precision == GIEB_TF32;
+  // TF32 (4-byte storage) and FP8 (1-byte storage) share the restrictions of a storage type that is not 2 bytes wide: their
+  // tensors pass through their own repack kernels, on the im2col and tiled routes, without the extension flags.
+  const bool fp8 = d.precision == GIEB_FP8_E4M3;
+  const bool tf32 = d.precision == GIEB_TF32 || fp8;   // "not a 2-byte type" in every route decision below
   if (tf32 && (d.flags & (GIEB_FLAG_WEIGHTS_PREPACKED | GIEB_FLAG_INPUT_NHWC | GIEB_FLAG_OUTPUT_NHWC | GIEB_FLAG_RESIDUAL)))
     return no("prepacked weights, channel-contiguous tensors and the fused residual are offered for FP16 / BF16 only");
   if (d.precision == GIEB_FP32) {
@@ -330,7 +333,18 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   if (d.stride_h > 8 || d.stride_w > 8) return no("stride > 8 cannot be expressed by the TMA im2col traversal stride");
   if (d.pad_h > 127 || d.pad_w > 127 || d.kernel_h > 128 || d.kernel_w > 128) return no("padding/kernel extent exceeds the TMA im2col corner range");
 
-  if (tf32) {
+  if (fp8) {
+    // FP8 storage: a 128/64/32-byte slab row holds 128/64/32 values.  cfg.tile_k counts FP8 values; internally every tile
+    // and padding quantity is kept in 2-byte units (half the FP8 counts), as for TF32.
+    if (c.variant == 2 || c.variant == 5) return no("FP8 runs on the im2col (1) and tiled (4) routes");
+    int tk = c.tile_k;
+    if (tk == 0) {
+      const int base = round_up(d.in_channels, 32);
+      tk = double(round_up(d.in_channels, 128)) <= 1.15 * base ? 128 : (double(round_up(d.in_channels, 64)) <= 1.15 * base ? 64 : 32);
+    }
+    if (tk != 32 && tk != 64 && tk != 128) return no("tile_k must be 32, 64 or 128 for FP8 (values per slab row)");
+    r->tile_k = tk / 2;
+  } else if (tf32) {
     // FP32 storage: a 128/64/32-byte slab row holds 32/16/8 values.  cfg.tile_k counts FP32 values; internally every
     // tile and padding quantity is kept in 2-byte units (twice the FP32 counts) so that the byte layouts coincide.
     if (c.variant == 2 || c.variant == 5) return no("TF32 runs on the im2col (1) and tiled (4) routes");
@@ -350,6 +364,8 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
     if (!c.tile_k) r->tile_k = gather_c2 % 64 == 0 ? 64 : (gather_c2 % 32 == 0 ? 32 : 16);
     if (gather_c2 % r->tile_k != 0) return no("tile_k must divide the gathered row length (padded kernel_w * channels)");
     r->c_padded = gather_c2;
+  } else if (fp8) {
+    r->c_padded = round_up(d.in_channels, 2 * r->tile_k) / 2;
   } else if (tf32) {
     r->c_padded = 2 * round_up(d.in_channels, r->tile_k / 2);
   } else {
@@ -513,7 +529,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
   out->variant = r.variant;
   out->cfg.tile_m = r.tile_m;
   out->cfg.tile_n = r.tile_n;
-  out->cfg.tile_k = d.precision == GIEB_TF32 ? r.tile_k / 2 : r.tile_k;  // in elements of the storage type
+  out->cfg.tile_k = d.precision == GIEB_TF32 ? r.tile_k / 2 : (d.precision == GIEB_FP8_E4M3 ? r.tile_k * 2 : r.tile_k);  // in elements of the storage type
   out->cfg.stages = r.stages;
   out->cfg.split_k = r.split_k;
   out->cfg.variant = r.variant;
@@ -521,7 +537,7 @@ void fill_info(const gieb_conv_desc& d, const Resolved& r, gieb_conv_info* out) 
   out->cfg.cta_pair = r.variant == 3 ? 0 : (r.pair ? 2 : 1);
   out->workspace_bytes = r.ws_total;
   out->persistent_bytes = sizeof(uint32_t);
-  out->padded_channels = d.precision == GIEB_TF32 ? r.c_padded / 2 : r.c_padded;
+  out->padded_channels = d.precision == GIEB_TF32 ? r.c_padded / 2 : (d.precision == GIEB_FP8_E4M3 ? r.c_padded * 2 : r.c_padded);
   if (r.variant == 3) {
     out->dynamic_smem_bytes = 0;
     out->threads_per_block = r.tile_n == 64 ? 256 : 64;
@@ -593,11 +609,13 @@ namespace {
 int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* wk, CUtensorMap* tm_act, CUtensorMap* tm_wgt) {
   const gieb_conv_desc& d = pl->desc;
   const Resolved& r = pl->r;
-  const bool tf32 = d.precision == GIEB_TF32;
-  const CUtensorMapDataType dt = tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                      : (d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  const bool tf32 = d.precision == GIEB_TF32, fp8 = d.precision == GIEB_FP8_E4M3;
+  const CUtensorMapDataType dt = tf32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                       : (d.precision == GIEB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   const CUtensorMapSwizzle sw = swizzle_for(r.tile_k);
-  const int esh = tf32 ? 1 : 0;  // element counts along channels: 2-byte units >> esh
+  // element counts along channels from counts of 2-byte units: halved for 4-byte elements, doubled for 1-byte elements
+  auto el = [&](uint64_t units) { return tf32 ? units >> 1 : (fp8 ? units << 1 : units); };
   if (mode == 2) {  // NCHW seen as {HW, C, N}: one box = 64 pixels (128 bytes, the swizzle span) x tile_k channels
     const cuuint64_t hw = cuuint64_t(d.in_h) * d.in_w;
     const cuuint64_t dims[3] = {hw, cuuint64_t(d.in_channels), cuuint64_t(d.batch)};
@@ -609,22 +627,22 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (NCHW activations) failed with CUresult %d", int(res));
     small_tensor_fixup(tm_act, size_t(hw) * d.in_channels * d.batch * 2);
   } else if (mode == 1) {  // 1x1 / stride 1 / pad 0: the NHWC copy is the GEMM operand [pixels][Cp] itself
-    const cuuint64_t dims[2] = {cuuint64_t(r.c_padded >> esh), cuuint64_t(d.batch) * d.in_h * d.in_w};
+    const cuuint64_t dims[2] = {cuuint64_t(el(r.c_padded)), cuuint64_t(d.batch) * d.in_h * d.in_w};
     const cuuint64_t strides[1] = {cuuint64_t(r.c_padded) * 2};
-    const cuuint32_t box[2] = {cuuint32_t(r.tile_k >> esh), cuuint32_t(kTileM)};
+    const cuuint32_t box[2] = {cuuint32_t(el(r.tile_k)), cuuint32_t(kTileM)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult res = g_encode_tiled(tm_act, dt, 2, const_cast<void*>(xn), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (activations) failed with CUresult %d", int(res));
     small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * d.in_w * r.c_padded * 2);
   } else {
-    const cuuint64_t dims[4] = {cuuint64_t(r.c_padded >> esh), cuuint64_t(r.eff_in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
+    const cuuint64_t dims[4] = {cuuint64_t(el(r.c_padded)), cuuint64_t(r.eff_in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
     const cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(r.eff_in_w) * r.c_padded * 2,
                                    cuuint64_t(d.in_h) * r.eff_in_w * r.c_padded * 2};
     const int lower[2] = {-r.eff_pad_w, -d.pad_h};
     const int upper[2] = {r.eff_pad_w - (r.eff_kernel_w - 1), d.pad_h - (d.kernel_h - 1)};
     const cuuint32_t trav[4] = {1, cuuint32_t(r.eff_stride_w), cuuint32_t(d.stride_h), 1};
-    const CUresult res = g_encode_im2col(tm_act, dt, 4, const_cast<void*>(xn), dims, strides, lower, upper, cuuint32_t(r.tile_k >> esh),
+    const CUresult res = g_encode_im2col(tm_act, dt, 4, const_cast<void*>(xn), dims, strides, lower, upper, cuuint32_t(el(r.tile_k)),
                                          cuuint32_t(kTileM), trav, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeIm2col failed with CUresult %d", int(res));
@@ -632,9 +650,9 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
   }
   {
     const cuuint64_t kp = cuuint64_t(d.kernel_h) * r.eff_kernel_w * r.c_padded;  // in 2-byte units
-    const cuuint64_t dims[2] = {kp >> esh, cuuint64_t(d.out_channels)};
+    const cuuint64_t dims[2] = {el(kp), cuuint64_t(d.out_channels)};
     const cuuint64_t strides[1] = {kp * 2};
-    const cuuint32_t box[2] = {cuuint32_t(r.tile_k >> esh), cuuint32_t(r.pair ? r.tile_n / 2 : r.tile_n)};  // a CTA of a pair loads half of the rows
+    const cuuint32_t box[2] = {cuuint32_t(el(r.tile_k)), cuuint32_t(r.pair ? r.tile_n / 2 : r.tile_n)};  // a CTA of a pair loads half of the rows
     const cuuint32_t estr[2] = {1, 1};
     const CUresult res = g_encode_tiled(tm_wgt, dt, 2, const_cast<void*>(wk), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -725,6 +743,9 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   if (ev) GIEB_CUDA(cudaEventRecord(ev[0], st));
   if (!(stage_mask & 1u)) {
     // the workspace already holds the repacked tensors of an earlier full launch
+  } else if (d.precision == GIEB_FP8_E4M3) {  // 1-byte tensors: their own transposing repack (one launch); c_padded is in 2-byte units
+    GIEB_CUDA(repack_bytes_pair_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded * 2, w, const_cast<void*>(wk), d.out_channels,
+                                       d.in_channels, d.kernel_h * d.kernel_w, r.c_padded * 2, st));
   } else if (d.precision == GIEB_TF32) {  // FP32 tensors rounded to TF32 while they are repacked (two launches)
     GIEB_CUDA(repack_tf32_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded / 2, st));
     GIEB_CUDA(repack_tf32_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded / 2, st));
@@ -759,7 +780,8 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.relu = d.relu; p.has_bias = d.has_bias;
   p.is_bf16 = d.precision == GIEB_BF16;
   p.is_tf32 = d.precision == GIEB_TF32;
-  p.bias_fp32 = (p.is_tf32 || (d.flags & GIEB_FLAG_BIAS_FP32)) ? 1 : 0;
+  p.is_fp8 = d.precision == GIEB_FP8_E4M3;
+  p.bias_fp32 = (p.is_tf32 || p.is_fp8 || (d.flags & GIEB_FLAG_BIAS_FP32)) ? 1 : 0;
   p.a_mode = mode;
   p.idesc = p.is_tf32 ? ptx::make_idesc_tf32(kTileM, r.tile_n, false, false)
             : r.swap  ? ptx::make_idesc_f16(kTileM, r.tile_m, p.is_bf16, false, mode == 2)  // A = 128 weight rows, B = the tile's pixels

@@ -381,7 +381,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     // No more producers than ring slots: a warp must never be a full ring ahead of its own previous slab, or the
     // parity of the slot's barrier could not tell its phases apart.
     const int np = min(kProducerWarps, stages);
-    const int esh = p.is_tf32 ? 1 : 0;  // FP32 elements: channel coordinates are half the 2-byte-unit counts
+    const int esh = p.is_tf32 ? 1 : (p.is_fp8 ? -1 : 0);  // channel coordinates from 2-byte-unit counts: halved for FP32, doubled for FP8
+    auto ch = [esh](int units) { return esh > 0 ? units >> 1 : (esh < 0 ? units << 1 : units); };
     int s = warp;        // ring slot of this warp's next slab (the ring and its phases continue across tiles)
     uint32_t phase = 0;
     while (s >= stages) { s -= stages; phase ^= 1u; }
@@ -455,14 +456,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           if (lane < nbox) {
             if (p.a_mode == 2) {
               // 64 pixels x BK channels, [channel][pixel] in shared memory
-              ptx::tma_load_3d(a_dst + a_off, &tm_act, &full_bar[s], c1, (cb * BK) >> esh, c3);
+              ptx::tma_load_3d(a_dst + a_off, &tm_act, &full_bar[s], c1, ch(cb * BK), c3);
             } else if (p.a_mode == 1) {
-              ptx::tma_load_2d(a_dst + a_off, &tm_act, &full_bar[s], (cb * BK) >> esh, c1);
+              ptx::tma_load_2d(a_dst + a_off, &tm_act, &full_bar[s], ch(cb * BK), c1);
             } else {
-              ptx::tma_load_im2col_4d(a_dst + a_off, &tm_act, &full_bar[s], (cb * BK) >> esh, c1, c2, c3, uint16_t(sx), uint16_t(r));
+              ptx::tma_load_im2col_4d(a_dst + a_off, &tm_act, &full_bar[s], ch(cb * BK), c1, c2, c3, uint16_t(sx), uint16_t(r));
             }
           }
-          if (lane == 0) ptx::tma_load_2d(a_dst + A_BYTES, &tm_wgt, &full_bar[s], (k0 + cb * BK) >> esh, n0);
+          if (lane == 0) ptx::tma_load_2d(a_dst + A_BYTES, &tm_wgt, &full_bar[s], ch(k0 + cb * BK), n0);
         }
         cb += np;
         while (cb >= p.kb_per_tap) {
@@ -513,7 +514,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       // The slab loop exists three times (16-bit K-major A, 16-bit pixel-major A, TF32): the operand form and the MMA
       // kind are compile-time inside it, so the elected lane's issue sequence carries no branch per instruction.
       auto slab_loop = [&](auto form_tag) {
-        constexpr int FORM = decltype(form_tag)::value;  // 0: kind::f16, K-major A; 1: kind::f16, pixel-major A; 2: kind::tf32
+        constexpr int FORM = decltype(form_tag)::value;  // 0: kind::f16, K-major A; 1: kind::f16, pixel-major A; 2: kind::tf32; 3: kind::f8f6f4 (E4M3)
         // one slab's MMAs and the commit that frees its ring slot (elected lane only)
         auto issue_slab = [&](int slot, bool first) {
           const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(slot) * STAGE_BYTES);
@@ -543,6 +544,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
                 const uint64_t bdesc = ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32);
                 if constexpr (PAIR) ptx::mma_f16_ss_pair(acc, adesc, bdesc, p.idesc, !first || k != 0);
                 else if constexpr (FORM == 2) ptx::mma_tf32_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
+                else if constexpr (FORM == 3) ptx::mma_f8_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
                 else ptx::mma_f16_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
               }
             }
@@ -572,7 +574,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           if (s >= stages) { s -= stages; phase ^= 1u; }
         }
       };
-      if (!PAIR && p.is_tf32) slab_loop(std::integral_constant<int, 2>{});
+      if (!PAIR && !SWAP && p.is_tf32) slab_loop(std::integral_constant<int, 2>{});
+      else if (!PAIR && !SWAP && p.is_fp8) slab_loop(std::integral_constant<int, 3>{});
       else if (p.a_mode == 2) slab_loop(std::integral_constant<int, 1>{});
       else slab_loop(std::integral_constant<int, 0>{});
       // accumulator set complete (also reached after a time-out in the slab loop, so nobody hangs)

@@ -114,6 +114,7 @@ struct ConvTcParams {
   // 1: FP32 storage computed as TF32 (kind::tf32).  Tile and padding quantities (BK, c_padded, kb_per_tap) stay in
   // 2-byte units, i.e. twice the FP32 element counts; TMA coordinates along channels are halved; Y is float.
   int is_tf32;
+  int is_fp8;            // FP8 E4M3 operands (kind::f8f6f4), FP16 output: channel coordinates are twice the 2-byte-unit counts
   // How the activation operand reaches shared memory:
   //   0  im2col-mode TMA over the channel-padded NHWC copy (any kernel / stride / padding)
   //   1  tiled TMA over the same copy seen as the matrix [pixels][c_padded] (1x1, stride 1, pad 0)
@@ -179,6 +180,10 @@ cudaError_t splitk_reduce_launch(const float* partial, int splits, int64_t total
 cudaError_t repack_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream);
 // FP32 [B][C][HW] -> [B][HW][Cp] (Cp in FP32 elements) with every value rounded to TF32 (ties away).
 cudaError_t repack_tf32_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream);
+// 1-byte elements (FP8), two tensors in one launch: [batch][channels][hw] -> [batch][hw][c_padded], zero-padded channels;
+// c_padded counts elements (a multiple of 32); destinations 16-byte aligned.
+cudaError_t repack_bytes_pair_launch(const void* src_a, void* dst_a, int batch_a, int ch_a, int hw_a, int cp_a, const void* src_b,
+                                     void* dst_b, int batch_b, int ch_b, int hw_b, int cp_b, cudaStream_t stream);
 // Two repacks (activations + weights) in ONE launch; src_b == nullptr runs only the first.
 cudaError_t repack_pair_launch(const void* src_a, void* dst_a, int batch_a, int ch_a, int hw_a, int cp_a, const void* src_b,
                                void* dst_b, int batch_b, int ch_b, int hw_b, int cp_b, cudaStream_t stream);

@@ -439,7 +439,85 @@ __global__ void __launch_bounds__(256) repack_tf32_kernel(const float* __restric
   }
 }
 
+// 1-byte elements (FP8 bit patterns): [B][C][HW] -> [B][HW][Cp], channels zero-padded to Cp (a multiple of 32).  Pure data
+// movement, bit-exact.  One CTA transposes a 64-channel x 64-pixel tile: 4-byte loads along the pixels where the plane
+// size and the source address allow it, 16-byte stores of 16 consecutive channels (a warp writes 8 pixels x 64 bytes).
+// Up to two tensors per launch (activations and weights), like repack_jobs_kernel.
+struct ByteJob {
+  const uint8_t* src;
+  uint8_t* dst;
+  int C, HW, Cp, hw_tiles, c_tiles;
+  unsigned blocks;
+};
+constexpr int kBytePitch = 68;
+
+__global__ void __launch_bounds__(256) repack_bytes_kernel(const ByteJob a, const ByteJob b) {
+  __shared__ __align__(16) uint8_t tile[64 * kBytePitch];
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
+  const bool first = blockIdx.x < a.blocks;
+  const ByteJob& j = first ? a : b;
+  unsigned id = first ? blockIdx.x : blockIdx.x - a.blocks;
+  const int hw_tile = int(id % unsigned(j.hw_tiles));
+  id /= unsigned(j.hw_tiles);
+  const int c_tile = int(id % unsigned(j.c_tiles));
+  const int bi = int(id / unsigned(j.c_tiles));
+  const int c0 = c_tile * 64, px0 = hw_tile * 64, t = threadIdx.x;
+  const uint8_t* s = j.src + (size_t(bi) * j.C + c0) * j.HW + px0;
+  const bool words = (j.HW & 3) == 0 && (reinterpret_cast<uintptr_t>(j.src) & 3u) == 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = t + i * 256, ch = idx >> 4, q = (idx & 15) * 4;
+    uint32_t v = 0;
+    if (c0 + ch < j.C && px0 + q < j.HW) {
+      const uint8_t* p = s + size_t(ch) * j.HW + q;
+      if (words) v = *reinterpret_cast<const uint32_t*>(p);   // a group of four never straddles the plane (HW % 4 == 0)
+      else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (px0 + q + e < j.HW) v |= uint32_t(p[e]) << (8 * e);
+      }
+    }
+    *reinterpret_cast<uint32_t*>(tile + ch * kBytePitch + q) = v;
+  }
+  __syncthreads();
+  const int cg = t & 3, px = t >> 2;
+  if (px0 + px < j.HW && c0 + cg * 16 < j.Cp) {
+    uint32_t o[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      uint32_t v = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v |= uint32_t(tile[(cg * 16 + w * 4 + e) * kBytePitch + px]) << (8 * e);
+      o[w] = v;
+    }
+    *reinterpret_cast<uint4*>(j.dst + (size_t(bi) * j.HW + px0 + px) * j.Cp + c0 + cg * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+ByteJob make_byte_job(const void* src, void* dst, int batch, int channels, int hw, int c_padded) {
+  ByteJob j;
+  j.src = static_cast<const uint8_t*>(src);
+  j.dst = static_cast<uint8_t*>(dst);
+  j.C = channels; j.HW = hw; j.Cp = c_padded;
+  j.hw_tiles = (hw + 63) / 64;
+  j.c_tiles = (c_padded + 63) / 64;
+  j.blocks = unsigned(int64_t(j.hw_tiles) * j.c_tiles * batch);
+  return j;
+}
+
 }  // namespace
+
+cudaError_t repack_bytes_pair_launch(const void* src_a, void* dst_a, int batch_a, int ch_a, int hw_a, int cp_a, const void* src_b,
+                                     void* dst_b, int batch_b, int ch_b, int hw_b, int cp_b, cudaStream_t stream) {
+  if (int64_t((hw_a + 63) / 64) * ((cp_a + 63) / 64) * batch_a + int64_t((hw_b + 63) / 64) * ((cp_b + 63) / 64) * batch_b > 2147483647LL)
+    return cudaErrorInvalidValue;
+  const ByteJob a = make_byte_job(src_a, dst_a, batch_a, ch_a, hw_a, cp_a);
+  const ByteJob b = make_byte_job(src_b, dst_b, batch_b, ch_b, hw_b, cp_b);
+  const cudaError_t e = launch_pdl(repack_bytes_kernel, dim3(a.blocks + b.blocks), dim3(256), 0, stream, a, b);
+  if (e != cudaSuccess) return e;
+  return cudaGetLastError();
+}
 
 cudaError_t repack_tf32_launch(const void* src, void* dst, int batch, int channels, int hw, int c_padded, cudaStream_t stream) {
   const dim3 grid(unsigned((hw + 31) / 32), unsigned((c_padded + 31) / 32), unsigned(batch));

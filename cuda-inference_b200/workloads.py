@@ -5,6 +5,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 
 FP32, FP16, BF16 = 0, 1, 2
+FP8_E4M3 = 4  # x and w as FP8 E4M3 bytes, float bias, FP16 y (an extension of this library)
 
 
 @dataclass(frozen=True)
@@ -33,7 +34,8 @@ class ConvShape:
 
     @property
     def elem_size(self) -> int:
-        return 4 if self.precision == FP32 else 2
+        """Bytes per element of x and w (y is FP16 for FP8 inputs, else the same type)."""
+        return 4 if self.precision == FP32 else (1 if self.precision == FP8_E4M3 else 2)
 
     @property
     def x_elems(self) -> int:
@@ -50,6 +52,8 @@ class ConvShape:
     @property
     def algorithmic_bytes(self) -> int:
         """X + W + Y + bias, each moved once, in the storage type."""
+        if self.precision == FP8_E4M3:
+            return self.x_elems + self.w_elems + 2 * self.y_elems + 4 * self.out_channels
         return (self.x_elems + self.w_elems + self.y_elems + self.out_channels) * self.elem_size
 
 
@@ -59,6 +63,7 @@ CONV_WORKLOADS = {
     "c2": (ConvShape(32, 256, 14, 14, 256, 3, 1, 1, FP16), "tensor"),
     "c3_fp16": (ConvShape(64, 512, 28, 28, 128, 1, 1, 0, FP16), "hbm"),
     "c3_bf16": (ConvShape(64, 512, 28, 28, 128, 1, 1, 0, BF16), "hbm"),
+    "c2_fp8": (ConvShape(32, 256, 14, 14, 256, 3, 1, 1, FP8_E4M3), "tensor"),   # c2 with FP8 E4M3 inputs (an extension; FP16 output)
     "c4a": (ConvShape(8, 512, 7, 7, 512, 3, 1, 1, FP16), "tensor"),
     "c4b": (ConvShape(16, 128, 56, 56, 256, 3, 2, 1, FP16), "tensor"),
     # the first layer of the chain at 32 images per replica: 3 input channels, the row-gather route

@@ -46,8 +46,12 @@ typedef enum gieb_status {
 /* Order of gie::Precision (include/gpu_inference/conv2d.h:26).  GIEB_TF32: FP32 tensors (x, w, bias, y), inputs rounded
  * to TF32 (nearest, ties away) and multiplied on the tensor cores (kind::tf32), FP32 accumulation and output; the
  * reference reaches this precision only through cuBLAS (src/kernels/im2col.cu:108-112).  cfg.tile_k counts FP32 values
- * for it (8, 16 or 32 per slab row); routes 1 and 4; no extension flags. */
-typedef enum gieb_precision { GIEB_FP32 = 0, GIEB_FP16 = 1, GIEB_BF16 = 2, GIEB_TF32 = 3 } gieb_precision;
+ * for it (8, 16 or 32 per slab row); routes 1 and 4; no extension flags.
+ * GIEB_FP8_E4M3 (an extension: gie::Precision has no such member, so it is reachable through this C ABI only): x and w are
+ * FP8 E4M3 bit patterns (1 byte per element, NCHW / OIHW), bias is float[O], y is FP16 NCHW.  Products are exact in the
+ * tensor core (kind::f8f6f4), FP32 accumulation, bias + ReLU in FP32, one rounding to FP16.  cfg.tile_k counts FP8 values
+ * (32, 64 or 128 per slab row); routes 1 and 4; no extension flags. */
+typedef enum gieb_precision { GIEB_FP32 = 0, GIEB_FP16 = 1, GIEB_BF16 = 2, GIEB_TF32 = 3, GIEB_FP8_E4M3 = 4 } gieb_precision;
 
 /* Optional behaviour beyond the reference API (all off by default = exact drop-in behaviour). */
 enum {

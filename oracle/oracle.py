@@ -139,6 +139,33 @@ def _ptr(a: np.ndarray | None, ty=C.c_float):
     return None if a is None else a.ctypes.data_as(C.POINTER(ty))
 
 
+def e4m3_quantize(a) -> np.ndarray:
+    """Values rounded to FP8 E4M3 (the 8-bit format of the OCP 8-bit floating point specification: 1 sign, 4 exponent bits
+    with bias 7, 3 mantissa bits, no infinities, largest finite value 448): round to nearest even, saturating at +-448.  The
+    reference has no FP8 path; this grid is what the FP8 extension of the library under test stores, and every value
+    on it is also an FP16 value, so the FP16 oracle applies to tensors quantized with it."""
+    x = np.asarray(a, dtype=np.float32)
+    mag = np.abs(x).astype(np.float64)
+    _, e = np.frexp(mag)                       # mag = m * 2**e with m in [0.5, 1)
+    exp = np.clip(e - 1, -6, 8)                # exponent of the leading bit; subnormals share the step of 2**-6
+    step = np.ldexp(1.0, exp - 3)
+    q = np.minimum(np.rint(mag / step) * step, 448.0)
+    return np.copysign(q, x).astype(np.float32)
+
+
+def e4m3_bits(q) -> np.ndarray:
+    """Bit patterns (uint8) of values that already lie on the E4M3 grid."""
+    x = np.asarray(q, dtype=np.float32)
+    mag = np.abs(x).astype(np.float64)
+    _, e = np.frexp(mag)
+    exp = np.clip(e - 1, -6, 8)
+    normal = mag >= 2.0 ** -6
+    mant = np.where(normal, mag / np.ldexp(1.0, exp) * 8.0 - 8.0, mag / 2.0 ** -9)
+    biased = np.where(normal, exp + 7, 0)
+    bits = (np.signbit(x).astype(np.uint8) << 7) | (biased.astype(np.uint8) << 3) | np.rint(mant).astype(np.uint8)
+    return bits.astype(np.uint8)
+
+
 def build(ref: bool = True, quiet: bool = True) -> None:
     """Compile the C restatement and, where the reference checkout exists, the reference's own oracle."""
     out = subprocess.DEVNULL if quiet else None

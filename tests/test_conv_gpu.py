@@ -210,6 +210,65 @@ def test_transposed_accumulator_fused_residual(pkg, orc, oracle, case, res_off, 
     _check(oracle, p, out.read(oracle).reshape(p.y_shape), ref, scale, f"transposed accumulator + residual, case {case} res_off={res_off}")
 
 
+FP8_CASES = [
+    # FP8 E4M3 x and w (1 byte per element), float bias, FP16 y: kind::f8f6f4 MMAs over the same byte layouts as the 16-bit path
+    ((2, 64, 12, 12, 64, 3, 3, 1, 1, 1, 1), dict()),
+    ((1, 128, 10, 9, 96, 3, 3, 1, 1, 1, 1), dict(tile_k=128, tile_n=32, stages=2)),
+    ((3, 40, 9, 11, 50, 3, 3, 2, 2, 1, 1), dict(tile_k=32)),                           # channel tails on both sides (40 -> 64, 50)
+    ((2, 96, 8, 8, 128, 1, 1, 1, 1, 0, 0), dict(variant=4)),                           # tiled loads
+    ((2, 256, 7, 7, 64, 1, 1, 1, 1, 0, 0), dict(variant=1, tile_k=64)),
+    ((1, 192, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=128, stages=3)),
+    ((4, 64, 16, 16, 64, 5, 5, 1, 1, 2, 2), dict(tile_k=64, split_k=4, reduce=1)),       # workspace reduction
+    ((2, 512, 6, 6, 128, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=128, split_k=2, reduce=2, stages=4)),  # cluster reduction
+    ((8, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=128, tile_k=128)),  # 256-pixel tiles, several tiles per CTA
+    ((1, 3, 20, 20, 16, 7, 7, 2, 2, 3, 3), dict()),                                     # 3 channels padded to 32
+]
+
+
+@pytest.mark.parametrize("case", range(len(FP8_CASES)))
+def test_fp8_e4m3_extension(pkg, orc, oracle, case):
+    """Inputs on the E4M3 grid are exact FP16 values and their products are exact in FP32, so the FP16 oracle (double
+    accumulation, FP16 output tolerance) is the oracle of the FP8 path on the same values."""
+    import torch
+    from oracle import oracle as orc_mod
+    args, kw = FP8_CASES[case]
+    relu, bias = case % 2 == 0, case % 3 != 1
+    p = orc.Problem.P(*args, precision=orc.FP16, bias=bias, relu=relu)
+    x, w, b = oracle.make_conv_data(p, 8300 + case, case % 4)
+    x, w = orc_mod.e4m3_quantize(x), orc_mod.e4m3_quantize(w)
+    ref, scale = oracle.conv2d(p, x, w, b if bias else None)
+    prob = pkg.ConvProblem(p.batch, p.in_channels, p.in_h, p.in_w, p.out_channels, p.kernel_h, p.kernel_w, p.stride_h, p.stride_w, p.pad_h,
+                           p.pad_w, 1, 1, 1, pkg.FP8_E4M3, bias, relu, 0)
+    plan = pkg.ConvPlan(prob, pkg.make_cfg(**kw))
+    for k, v in kw.items():
+        if k in ("tile_k", "tile_n", "split_k"):
+            assert getattr(plan.info.cfg, k) == v
+    stream = torch.cuda.current_stream().cuda_stream
+    tx = torch.from_numpy(orc_mod.e4m3_bits(x).ravel()).cuda()
+    tw = torch.from_numpy(orc_mod.e4m3_bits(w).ravel()).cuda()
+    tb = torch.from_numpy(np.ascontiguousarray(b, dtype=np.float32)).cuda()
+    out = gu.OutBuf(orc.FP16, int(np.prod(p.y_shape)))
+    ws = gu.Workspace(plan.workspace_bytes)
+    for _ in range(2):
+        plan.launch(tx.data_ptr(), tw.data_ptr(), tb.data_ptr() if bias else None, out.ptr, ws.ptr if plan.workspace_bytes else None,
+                    plan.workspace_bytes, stream)
+    torch.cuda.synchronize()
+    assert plan.device_status() == 0
+    ws.check_guard()
+    _check(oracle, p, out.read(oracle).reshape(p.y_shape), ref, scale, f"FP8 case {case} {kw}")
+
+
+def test_fp8_refuses_what_it_does_not_offer(pkg):
+    for flags in (pkg.FLAG_INPUT_NHWC, pkg.FLAG_OUTPUT_NHWC, pkg.FLAG_RESIDUAL, pkg.FLAG_WEIGHTS_PREPACKED):
+        with pytest.raises(pkg.GieError) as e:
+            pkg.ConvPlan(pkg.ConvProblem(1, 64, 8, 8, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1, pkg.FP8_E4M3, True, True, flags))
+        assert e.value.code == pkg.UNSUPPORTED
+    for kw in (dict(variant=2), dict(tile_k=16), dict(cta_pair=2)):
+        with pytest.raises(pkg.GieError) as e:
+            pkg.ConvPlan(pkg.ConvProblem(1, 64, 8, 8, 64, 1, 1, 1, 1, 0, 0, 1, 1, 1, pkg.FP8_E4M3, True, True, 0), pkg.make_cfg(**kw))
+        assert e.value.code == pkg.UNSUPPORTED
+
+
 DIRECT_CASES = [
     # 1x1 / stride 1 / pad 0 with H*W % 8 == 0: activations are read straight from NCHW (pixel-major operand)
     ((2, 64, 8, 8, 64, 1, 1, 1, 1, 0, 0), dict(variant=2, tile_n=64, tile_k=64, stages=2), 0),

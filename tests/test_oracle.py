@@ -196,3 +196,19 @@ def test_chain_glue_oracles(orc, oracle):
     assert np.array_equal(y, exp.astype(np.float32))
     a, b = oracle.quantize(orc.FP16, x.ravel()), oracle.quantize(orc.FP16, x.ravel()[::-1].copy())
     assert np.array_equal(oracle.add_relu(orc.FP16, a, b, True), np.maximum(oracle.quantize(orc.FP16, a + b), 0))
+
+
+def test_e4m3_grid_matches_an_independent_conversion():
+    """The FP8 E4M3 rounding used to prepare inputs for the FP8 extension (round to nearest even, saturating) against
+    torch's float8_e4m3fn conversion, values and bit patterns, including subnormals, ties, signed zero and the largest
+    finite value; and every value of the grid is exactly an FP16 value (so the FP16 oracle applies)."""
+    import torch
+    from oracle import oracle as orc_mod
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.uniform(-1, 1, 50000), rng.normal(0, 100, 50000), rng.uniform(-0.02, 0.02, 50000),
+                        [0.0, -0.0, 448, 449, 500, -1000, 2 ** -9, 2 ** -10, 1.5 * 2 ** -9, 2.5 * 2 ** -9, 0.0625 * 1.0625]]).astype(np.float32)
+    q = orc_mod.e4m3_quantize(x)
+    t = torch.from_numpy(x).clamp(-448, 448).to(torch.float8_e4m3fn)
+    assert np.array_equal(q, t.float().numpy())
+    assert np.array_equal(orc_mod.e4m3_bits(q), t.view(torch.uint8).numpy())
+    assert np.array_equal(q, q.astype(np.float16).astype(np.float32))
