@@ -11,31 +11,42 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <cooperative_groups.h>
+#include <cooperative_groups/reduce.h>
+
 #include "internal.h"
+
+namespace cg = cooperative_groups;
 
 namespace gieb {
 namespace {
 
-__device__ __forceinline__ float cvt(float v) { return v; }
-__device__ __forceinline__ float cvt(__half v) { return __half2float(v); }
-__device__ __forceinline__ float cvt(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <typename T> __device__ __forceinline__ T rnd(float v);
-template <> __device__ __forceinline__ float rnd<float>(float v) { return v; }
-template <> __device__ __forceinline__ __half rnd<__half>(float v) { return __float2half_rn(v); }
-template <> __device__ __forceinline__ __nv_bfloat16 rnd<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+// Storage type <-> FP32 (one rounding on the way back).
+template <typename T> struct Num;
+template <> struct Num<float> {
+  static __device__ __forceinline__ float up(float v) { return v; }
+  static __device__ __forceinline__ float down(float v) { return v; }
+};
+template <> struct Num<__half> {
+  static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
+};
+template <> struct Num<__nv_bfloat16> {
+  static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); }
+};
 
-__device__ __forceinline__ float block_sum(float v, float* red) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nw = (blockDim.x + 31) >> 5;
-  if (nw == 1) return v;
-  if (lane == 0) red[warp] = v;
+// Sum over the CTA, the same bits in every thread: each warp reduces its own values, warp leaders publish one partial
+// each, and after ONE barrier every thread folds the (at most 32) partials itself in warp order.
+__device__ __forceinline__ float cta_sum(float v, float* partial) {
+  const cg::thread_block_tile<32> warp = cg::tiled_partition<32>(cg::this_thread_block());
+  v = cg::reduce(warp, v, cg::plus<float>());
+  if (warp.meta_group_size() == 1) return v;
+  if (warp.thread_rank() == 0) partial[warp.meta_group_rank()] = v;
   __syncthreads();
-  float r = lane < nw ? red[lane] : 0.f;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-  return r;
+  float total = 0.f;
+  for (unsigned w = 0; w < warp.meta_group_size(); ++w) total += partial[w];
+  return total;
 }
 
 template <typename T> struct Vec { static constexpr int N = 16 / sizeof(T); };
@@ -56,7 +67,7 @@ __device__ __forceinline__ void load_gamma(const void* gamma, int i, float (&g)[
     T tv[VEC];
     memcpy(tv, &raw, 16);
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) g[j] = cvt(tv[j]);
+    for (int j = 0; j < VEC; ++j) g[j] = Num<T>::up(tv[j]);
   }
 }
 
@@ -92,19 +103,19 @@ rmsnorm_row_kernel(const T* x, const void* __restrict__ gamma, T* __restrict__ y
         T b[VEC];
         memcpy(b, &rv[k], 16);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) a[j] = rnd<T>(cvt(a[j]) + cvt(b[j]));
+        for (int j = 0; j < VEC; ++j) a[j] = Num<T>::down(Num<T>::up(a[j]) + Num<T>::up(b[j]));
         uint4 o;
         memcpy(&o, a, 16);
         reinterpret_cast<uint4*>(res_out + row * hidden)[i] = o;
       }
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
-        s[k][j] = cvt(a[j]);
+        s[k][j] = Num<T>::up(a[j]);
         ss = fmaf(s[k][j], s[k][j], ss);
       }
     }
   }
-  ss = block_sum(ss, red);
+  ss = cta_sum(ss, red);
   const float inv = rsqrtf(ss / float(hidden) + eps);
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
@@ -114,7 +125,7 @@ rmsnorm_row_kernel(const T* x, const void* __restrict__ gamma, T* __restrict__ y
       load_gamma<T, GAMMA_F32>(gamma, i, g);
       T o[VEC];
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) o[j] = rnd<T>(s[k][j] * inv * g[j]);
+      for (int j = 0; j < VEC; ++j) o[j] = Num<T>::down(s[k][j] * inv * g[j]);
       uint4 ov;
       memcpy(&ov, o, 16);
       reinterpret_cast<uint4*>(y + row * hidden)[i] = ov;
@@ -122,30 +133,38 @@ rmsnorm_row_kernel(const T* x, const void* __restrict__ gamma, T* __restrict__ y
   }
 }
 
-// Scalar two-pass path for odd hidden sizes, misaligned pointers and very long rows.
+// Element-wise path for odd hidden sizes, misaligned pointers and very long rows.  The normalised stream (x, or the rounded
+// x + residual) is kept as FP32 in shared memory between the square sum and the scaling when the row fits (`staged` floats
+// of dynamic shared memory, 0 = it does not): global memory is then read once here as well; longer rows are read again.
 template <typename T, bool FUSED, bool GAMMA_F32>
 __global__ void __launch_bounds__(1024)
 rmsnorm_generic_kernel(const T* x, const void* __restrict__ gamma, T* __restrict__ y, const T* res_in,
-                       T* res_out, int hidden, float eps) {
+                       T* res_out, int hidden, float eps, int staged) {
+  extern __shared__ float row_f32[];
   __shared__ float red[32];
-  const size_t row = blockIdx.x;
-  const T* xr = x + row * hidden;
+  const size_t base = size_t(blockIdx.x) * hidden;
+  auto stream_value = [&](int i) {   // element i of the stream that is normalised (stores the residual stream when fused)
+    float f = Num<T>::up(x[base + i]);
+    if (FUSED) {
+      const T sv = Num<T>::down(f + Num<T>::up(res_in[base + i]));
+      res_out[base + i] = sv;
+      f = Num<T>::up(sv);
+    }
+    return f;
+  };
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float f = cvt(xr[i]);
-    if (FUSED) {
-      const T sv = rnd<T>(f + cvt(res_in[row * hidden + i]));
-      res_out[row * hidden + i] = sv;
-      f = cvt(sv);
-    }
+    const float f = stream_value(i);
+    if (i < staged) row_f32[i] = f;
     ss = fmaf(f, f, ss);
   }
-  ss = block_sum(ss, red);
+  ss = cta_sum(ss, red);
   const float inv = rsqrtf(ss / float(hidden) + eps);
-  const T* src = FUSED ? res_out + row * hidden : xr;  // each thread re-reads only what it wrote itself
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float g = GAMMA_F32 ? static_cast<const float*>(gamma)[i] : cvt(static_cast<const T*>(gamma)[i]);
-    y[row * hidden + i] = rnd<T>(cvt(src[i]) * inv * g);
+    // beyond the staged part a thread reads back what it stored itself (res_out) or the input again
+    const float f = i < staged ? row_f32[i] : Num<T>::up(FUSED ? res_out[base + i] : x[base + i]);
+    const float g = GAMMA_F32 ? static_cast<const float*>(gamma)[i] : Num<T>::up(static_cast<const T*>(gamma)[i]);
+    y[base + i] = Num<T>::down(f * inv * g);
   }
 }
 
@@ -177,7 +196,8 @@ cudaError_t run(int rows, int hidden, float eps, const void* x, const void* gamm
   } else {
     int threads = 32;
     while (threads < hidden && threads < 1024) threads <<= 1;
-    rmsnorm_generic_kernel<T, FUSED, GAMMA_F32><<<rows, threads, 0, st>>>(xp, gamma, yp, ri, ro, hidden, eps);
+    const int staged = hidden <= 12 * 1024 ? hidden : 0;  // <= 48 KiB of dynamic shared memory (no opt-in needed)
+    rmsnorm_generic_kernel<T, FUSED, GAMMA_F32><<<rows, threads, size_t(staged) * sizeof(float), st>>>(xp, gamma, yp, ri, ro, hidden, eps, staged);
   }
   return cudaGetLastError();
 }
