@@ -382,7 +382,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   if (c.tile_m != 0 && c.tile_m != 128 && c.tile_m != 256) return no("tile_m must be 128 or 256");
   if (c.cta_pair < 0 || c.cta_pair > 2) return no("cta_pair must be 0 (auto), 1 (single CTA) or 2 (CTA pair)");
   if (c.cta_pair == 2) {
-    if (tf32) return no("CTA-pair tiles are offered for FP16 / BF16");
+    if (d.precision == GIEB_TF32) return no("CTA-pair tiles are offered for FP16, BF16 and FP8");
     if (c.tile_m != 0 && c.tile_m != 256) return no("a CTA pair computes 256-pixel tiles (tile_m 0 or 256)");
     if (c.tile_n != 0 && c.tile_n < 64) return no("CTA-pair tiles are 64, 128 or 256 output channels wide");
     if (c.reduce == 2) return no("a CTA pair is a cluster already: its split-K slices are summed through the workspace (reduce 0 or 1)");
@@ -400,9 +400,9 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   int best_m = 0, best_n = 0, best_s = 0, best_mode = 0, best_pair = 0, best_swap = 0;
   const int n_opts[4] = {32, 64, 128, 256};
   // 256-pixel tiles of CTA pairs: only the workspace reduction for split-K
-  const bool pair_unasked = c.cta_pair == 0 && !tf32 && c.tile_m == 0 && c.split_k <= 1 && c.reduce == 0 && c.variant != 2 &&
+  const bool pair_unasked = c.cta_pair == 0 && d.precision != GIEB_TF32 && c.tile_m == 0 && c.split_k <= 1 && c.reduce == 0 && c.variant != 2 &&
                             auto_pair(d, rows, r->total_kb, r->tile_k);
-  for (int ni = 1; ni < 4 && !tf32 && (c.cta_pair == 2 || pair_unasked) && (c.tile_m == 0 || c.tile_m == 256) && c.reduce != 2; ++ni) {
+  for (int ni = 1; ni < 4 && d.precision != GIEB_TF32 && (c.cta_pair == 2 || pair_unasked) && (c.tile_m == 0 || c.tile_m == 256) && c.reduce != 2; ++ni) {
     const int tn = n_opts[ni];
     if (r->tile_n && tn != r->tile_n) continue;
     if (!r->tile_n && tn / 2 >= d.out_channels) continue;

@@ -447,11 +447,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         if constexpr (PAIR) {
           const uint32_t fb = full0 + uint32_t(s) * 8u;  // the leader's full barrier of this slot
           if (lane < nbox) {
-            if (p.a_mode == 2) ptx::tma_load_3d_pair(a_dst + a_off, &tm_act, fb, c1, cb * BK, c3);
-            else if (p.a_mode == 1) ptx::tma_load_2d_pair(a_dst + a_off, &tm_act, fb, cb * BK, c1);
-            else ptx::tma_load_im2col_4d_pair(a_dst + a_off, &tm_act, fb, cb * BK, c1, c2, c3, uint16_t(sx), uint16_t(r));
+            if (p.a_mode == 2) ptx::tma_load_3d_pair(a_dst + a_off, &tm_act, fb, c1, ch(cb * BK), c3);
+            else if (p.a_mode == 1) ptx::tma_load_2d_pair(a_dst + a_off, &tm_act, fb, ch(cb * BK), c1);
+            else ptx::tma_load_im2col_4d_pair(a_dst + a_off, &tm_act, fb, ch(cb * BK), c1, c2, c3, uint16_t(sx), uint16_t(r));
           }
-          if (lane == 0) ptx::tma_load_2d_pair(a_dst + A_BYTES, &tm_wgt, fb, k0 + cb * BK, wrow0);
+          if (lane == 0) ptx::tma_load_2d_pair(a_dst + A_BYTES, &tm_wgt, fb, ch(k0 + cb * BK), wrow0);
         } else {
           if (lane < nbox) {
             if (p.a_mode == 2) {
@@ -542,7 +542,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
                 const uint64_t adesc = FORM == 1 ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
                                                  : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
                 const uint64_t bdesc = ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32);
-                if constexpr (PAIR) ptx::mma_f16_ss_pair(acc, adesc, bdesc, p.idesc, !first || k != 0);
+                if constexpr (PAIR && FORM == 3) ptx::mma_f8_ss_pair(acc, adesc, bdesc, p.idesc, !first || k != 0);
+                else if constexpr (PAIR) ptx::mma_f16_ss_pair(acc, adesc, bdesc, p.idesc, !first || k != 0);
                 else if constexpr (FORM == 2) ptx::mma_tf32_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
                 else if constexpr (FORM == 3) ptx::mma_f8_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
                 else ptx::mma_f16_ss(acc + h * BN, adesc, bdesc, p.idesc, !first || k != 0);
@@ -575,7 +576,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         }
       };
       if (!PAIR && !SWAP && p.is_tf32) slab_loop(std::integral_constant<int, 2>{});
-      else if (!PAIR && !SWAP && p.is_fp8) slab_loop(std::integral_constant<int, 3>{});
+      else if (!SWAP && p.is_fp8) slab_loop(std::integral_constant<int, 3>{});
       else if (p.a_mode == 2) slab_loop(std::integral_constant<int, 1>{});
       else slab_loop(std::integral_constant<int, 0>{});
       // accumulator set complete (also reached after a time-out in the slab loop, so nobody hangs)

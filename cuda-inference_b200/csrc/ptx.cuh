@@ -307,6 +307,16 @@ __device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t adesc,
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate))
       : "memory");
 }
+__device__ __forceinline__ void mma_f8_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate))
+      : "memory");
+}
 // Arrival on the mbarrier at this shared-memory offset in every CTA of `cta_mask` (bit i = cluster rank i) once all
 // MMAs issued so far by this thread have finished.  (A multicast of the barrier SIGNAL, not of any load.)
 __device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask) {

@@ -222,6 +222,8 @@ FP8_CASES = [
     ((2, 512, 6, 6, 128, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=128, split_k=2, reduce=2, stages=4)),  # cluster reduction
     ((8, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict(tile_m=256, tile_n=128, tile_k=128)),  # 256-pixel tiles, several tiles per CTA
     ((1, 3, 20, 20, 16, 7, 7, 2, 2, 3, 3), dict()),                                     # 3 channels padded to 32
+    ((6, 128, 14, 14, 256, 3, 3, 1, 1, 1, 1), dict(tile_n=128, tile_k=128, cta_pair=2)),  # CTA pairs (cta_group::2 kind::f8f6f4), 1176 px: the last pair's peer is half empty
+    ((3, 64, 12, 14, 200, 3, 3, 1, 1, 1, 1), dict(tile_n=256, tile_k=64, cta_pair=2, stages=3)),
 ]
 
 
@@ -263,7 +265,7 @@ def test_fp8_refuses_what_it_does_not_offer(pkg):
         with pytest.raises(pkg.GieError) as e:
             pkg.ConvPlan(pkg.ConvProblem(1, 64, 8, 8, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1, pkg.FP8_E4M3, True, True, flags))
         assert e.value.code == pkg.UNSUPPORTED
-    for kw in (dict(variant=2), dict(tile_k=16), dict(cta_pair=2)):
+    for kw in (dict(variant=2), dict(tile_k=16), dict(split_k=2, reduce=2, cta_pair=2)):
         with pytest.raises(pkg.GieError) as e:
             pkg.ConvPlan(pkg.ConvProblem(1, 64, 8, 8, 64, 1, 1, 1, 1, 0, 0, 1, 1, 1, pkg.FP8_E4M3, True, True, 0), pkg.make_cfg(**kw))
         assert e.value.code == pkg.UNSUPPORTED
