@@ -167,22 +167,29 @@ conv_fp32_kernel(const Fp32Args a) {
     cp_async_commit();
     const float* xs = xs_base + (rd % NS) * XS;
     const float* ws = ws_base + (rd % NS) * WS;
+    // Operands of four k steps at a time (four 128-bit reads of W, four of X), the next four read from shared memory
+    // while the current ones are multiplied: with two or three warps per scheduler nothing else hides that latency.
+    float4 wv[2][4], xv[2][4];
+    auto read_operands = [&](int k4, int buf) {
 #pragma unroll
-    for (int k4 = 0; k4 < kBK; k4 += 4) {
-      float wa[4][4];
+      for (int j = 0; j < 4; ++j) wv[buf][j] = *reinterpret_cast<const float4*>(ws + (ty * 4 + j) * kWPitch + k4);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float4 wv = *reinterpret_cast<const float4*>(ws + (ty * 4 + j) * kWPitch + k4);
-        wa[j][0] = wv.x; wa[j][1] = wv.y; wa[j][2] = wv.z; wa[j][3] = wv.w;
-      }
+      for (int kk = 0; kk < 4; ++kk) xv[buf][kk] = *reinterpret_cast<const float4*>(xs + (k4 + kk) * TP + tx * 4);
+    };
+    read_operands(0, 0);
+#pragma unroll
+    for (int q = 0; q < kBK / 4; ++q) {
+      const int cur = q & 1;
+      if (q + 1 < kBK / 4) read_operands((q + 1) * 4, cur ^ 1);
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {  // k order: the accumulation order of the strict-FP32 contract
-        const float4 xv = *reinterpret_cast<const float4*>(xs + (k4 + kk) * TP + tx * 4);
-        const float xa[4] = {xv.x, xv.y, xv.z, xv.w};
+        const float xa[4] = {xv[cur][kk].x, xv[cur][kk].y, xv[cur][kk].z, xv[cur][kk].w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int j = 0; j < 4; ++j) {
+          const float wk = kk == 0 ? wv[cur][j].x : (kk == 1 ? wv[cur][j].y : (kk == 2 ? wv[cur][j].z : wv[cur][j].w));
 #pragma unroll
-          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], wa[j][kk], acc[i][j]);
+          for (int i = 0; i < 4; ++i) acc[i][j] = fmaf(xa[i], wk, acc[i][j]);
+        }
       }
     }
   }
