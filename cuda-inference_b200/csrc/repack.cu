@@ -440,21 +440,25 @@ __global__ void __launch_bounds__(256) repack_tf32_kernel(const float* __restric
 }
 
 // 1-byte elements (FP8 bit patterns): [B][C][HW] -> [B][HW][Cp], channels zero-padded to Cp (a multiple of 32).  Pure data
-// movement, bit-exact.  One CTA transposes a 64-channel x 64-pixel tile: 4-byte loads along the pixels where the plane
-// size and the source address allow it, 16-byte stores of 16 consecutive channels (a warp writes 8 pixels x 64 bytes).
-// Up to two tensors per launch (activations and weights), like repack_jobs_kernel.
+// movement, bit-exact.  Up to two tensors per launch (activations and weights), like repack_jobs_kernel, and the same
+// two shapes of work:
+//   tile mode: one CTA transposes a 64-channel x 64-pixel tile: 4-byte loads along the pixels where the plane size and the
+//     source address allow it, 16-byte stores of 16 consecutive channels (a warp writes 8 pixels x 64 bytes);
+//   slab mode (planes of at most 16 elements: filter taps): one CTA takes `span` channels of one batch entry; the source
+//     slab [span][HW] is contiguous and is read linearly, then written as [HW][span].
+// Both prefetch their source lines into L2 before the dependency wait (see repack_jobs_kernel).
 struct ByteJob {
   const uint8_t* src;
   uint8_t* dst;
-  int C, HW, Cp, hw_tiles, c_tiles;
+  int C, HW, Cp, hw_tiles, c_tiles, span;  // span > 0: slab mode
   unsigned blocks;
 };
 constexpr int kBytePitch = 68;
+constexpr int kByteSlab = 8192;  // bytes of shared memory a slab may take
 
-__global__ void __launch_bounds__(256) repack_bytes_kernel(const ByteJob a, const ByteJob b) {
-  __shared__ __align__(16) uint8_t tile[64 * kBytePitch];
-  ptx::grid_dep_wait();
-  ptx::grid_dep_launch();
+__global__ void __launch_bounds__(256) repack_bytes_kernel(const ByteJob a, const ByteJob b, int prefetch) {
+  __shared__ __align__(16) uint8_t tile[kByteSlab];
+  static_assert(64 * kBytePitch <= kByteSlab, "the tile mode's 64 x 64 tile must fit the slab buffer");
   const bool first = blockIdx.x < a.blocks;
   const ByteJob& j = first ? a : b;
   unsigned id = first ? blockIdx.x : blockIdx.x - a.blocks;
@@ -462,8 +466,40 @@ __global__ void __launch_bounds__(256) repack_bytes_kernel(const ByteJob a, cons
   id /= unsigned(j.hw_tiles);
   const int c_tile = int(id % unsigned(j.c_tiles));
   const int bi = int(id / unsigned(j.c_tiles));
-  const int c0 = c_tile * 64, px0 = hw_tile * 64, t = threadIdx.x;
+  const int t = threadIdx.x;
+  if (j.span > 0) {
+    const int c0 = c_tile * j.span;
+    const int nch = min(j.span, j.C - c0);           // may be <= 0 for pure padding tiles
+    const int n = nch > 0 ? nch * j.HW : 0;
+    const uint8_t* s = j.src + (size_t(bi) * j.C + c0) * j.HW;
+    if (prefetch)
+      for (int o = t * 128; o < n + 127 && n > 0; o += 256 * 128) ptx::prefetch_l2(s + min(o, n - 1));
+    ptx::grid_dep_wait();
+    ptx::grid_dep_launch();
+    if ((reinterpret_cast<uintptr_t>(s) & 15u) == 0 && (n & 15) == 0) {
+      for (int i = t; i < (n >> 4); i += 256) reinterpret_cast<uint4*>(tile)[i] = reinterpret_cast<const uint4*>(s)[i];
+    } else {
+      for (int i = t; i < n; i += 256) tile[i] = s[i];
+    }
+    __syncthreads();
+    const int groups = min(j.span, j.Cp - c0) >> 4;  // 16-channel vectors in this tile
+    for (int v = t; v < j.HW * groups; v += 256) {
+      const int px = v / groups, cg = v - px * groups;
+      uint32_t o[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int ch = cg * 16 + e;
+        if (ch < nch) o[e >> 2] |= uint32_t(tile[ch * j.HW + px]) << (8 * (e & 3));
+      }
+      *reinterpret_cast<uint4*>(j.dst + (size_t(bi) * j.HW + px) * j.Cp + c0 + cg * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    return;
+  }
+  const int c0 = c_tile * 64, px0 = hw_tile * 64;
   const uint8_t* s = j.src + (size_t(bi) * j.C + c0) * j.HW + px0;
+  if (prefetch && t < 64 && c0 + t < j.C && px0 < j.HW) ptx::prefetch_l2(s + size_t(t) * j.HW);  // 64 bytes: one line, or the first of two
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
   const bool words = (j.HW & 3) == 0 && (reinterpret_cast<uintptr_t>(j.src) & 3u) == 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -500,8 +536,16 @@ ByteJob make_byte_job(const void* src, void* dst, int batch, int channels, int h
   j.src = static_cast<const uint8_t*>(src);
   j.dst = static_cast<uint8_t*>(dst);
   j.C = channels; j.HW = hw; j.Cp = c_padded;
-  j.hw_tiles = (hw + 63) / 64;
-  j.c_tiles = (c_padded + 63) / 64;
+  if (hw <= 16) {   // filter taps: as many 64-channel groups per CTA as the slab holds
+    j.span = (kByteSlab / hw) / 64 * 64;
+    if (j.span > (c_padded + 63) / 64 * 64) j.span = (c_padded + 63) / 64 * 64;
+    j.hw_tiles = 1;
+    j.c_tiles = (c_padded + j.span - 1) / j.span;
+  } else {
+    j.span = 0;
+    j.hw_tiles = (hw + 63) / 64;
+    j.c_tiles = (c_padded + 63) / 64;
+  }
   j.blocks = unsigned(int64_t(j.hw_tiles) * j.c_tiles * batch);
   return j;
 }
@@ -514,7 +558,7 @@ cudaError_t repack_bytes_pair_launch(const void* src_a, void* dst_a, int batch_a
     return cudaErrorInvalidValue;
   const ByteJob a = make_byte_job(src_a, dst_a, batch_a, ch_a, hw_a, cp_a);
   const ByteJob b = make_byte_job(src_b, dst_b, batch_b, ch_b, hw_b, cp_b);
-  const cudaError_t e = launch_pdl(repack_bytes_kernel, dim3(a.blocks + b.blocks), dim3(256), 0, stream, a, b);
+  const cudaError_t e = launch_pdl(repack_bytes_kernel, dim3(a.blocks + b.blocks), dim3(256), 0, stream, a, b, prefetch_enabled() ? 1 : 0);
   if (e != cudaSuccess) return e;
   return cudaGetLastError();
 }
