@@ -120,6 +120,61 @@ maxpool_3x3s2p1_kernel(const uint32_t* __restrict__ x, uint16_t* __restrict__ y,
   }
 }
 
+// The same pool for widths that are multiples of 4 (8-byte aligned rows): one WARP walks down one plane (or one 128-column
+// strip of it).  A lane owns output columns 2l, 2l+1 = input columns 4l-1 .. 4l+3: one 8-byte load per input row plus the
+// left neighbour's last column by shuffle; the horizontal maxima of a row are computed once and serve the two output rows
+// that contain it, so every input element is read once.  Rows are fetched eight at a time (eight loads in flight per lane).
+template <typename T2>
+__global__ void __launch_bounds__(256)
+maxpool_3x3s2p1_rows_kernel(const uint2* __restrict__ x, uint32_t* __restrict__ y, int planes, int h, int w4, int oh, int ow2, int strips) {
+  const int lane = threadIdx.x & 31;
+  const int64_t job = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (plane, strip)
+  if (job >= int64_t(planes) * strips) return;  // whole warps leave together
+  const int plane = int(job / strips), strip = int(job - int64_t(plane) * strips);
+  const int c = strip * 32 + lane;               // this lane's 4-column group
+  const bool live = c < w4;
+  const int cc = live ? c : w4 - 1;              // dead lanes shadow the last group so that shuffles stay defined
+  const uint2* xp = x + size_t(plane) * h * w4 + cc;
+  uint32_t* yp = y + size_t(plane) * oh * ow2 + cc;
+  T2 carry = T2();     // horizontal maxima of input row 2*oy - 1 (the row above the window's middle); unused while have_carry is false
+  bool have_carry = false;
+  for (int oy0 = 0; oy0 < oh; oy0 += 4) {
+    // rows 2*oy0 .. 2*oy0 + 7 (eight rows = four output rows), all loads first
+    uint2 v[8];
+    uint32_t lf[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int iy = 2 * oy0 + r;
+      v[r] = iy < h ? xp[size_t(iy) * w4] : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      lf[r] = __shfl_up_sync(0xffffffffu, v[r].y, 1);
+      const int iy = 2 * oy0 + r;
+      if (lane == 0 && cc > 0 && iy < h) lf[r] = xp[size_t(iy) * w4 - 1].y;
+    }
+    T2 hm[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const T2 a = *reinterpret_cast<const T2*>(&v[r].x), b = *reinterpret_cast<const T2*>(&v[r].y);
+      const T2 l = *reinterpret_cast<const T2*>(&lf[r]);
+      T2 m = __hmax2(a, T2(a.y, b.x));
+      hm[r] = __hmax2(m, T2(cc > 0 ? l.y : a.x, b.y));
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int oy = oy0 + k;
+      if (oy >= oh) break;
+      T2 m = hm[2 * k];                                   // row 2*oy (always inside: oy < oh = h / 2)
+      if (2 * oy + 1 < h) m = __hmax2(m, hm[2 * k + 1]);  // row 2*oy + 1
+      if (have_carry) m = __hmax2(m, carry);              // row 2*oy - 1
+      carry = hm[2 * k + 1];
+      have_carry = true;
+      if (live) yp[size_t(oy) * ow2] = *reinterpret_cast<const uint32_t*>(&m);
+    }
+  }
+}
+
 // Channel-contiguous variant ([B][H][W][C], C % 8 == 0, 16-bit types): one thread per (output pixel, group of 8
 // channels); consecutive threads take consecutive groups, so every window tap is a coalesced 16-byte load.
 template <typename T2>
@@ -200,6 +255,17 @@ cudaError_t maxpool2d_launch(int precision, int batch, int channels, int h, int 
   const int64_t planes64 = int64_t(batch) * channels;
   if (planes64 > 2147483647LL || int64_t(oh) * ow > 2147483647LL) return cudaErrorInvalidValue;
   const int planes = int(planes64);
+  if ((precision == 1 || precision == 2) && k == 3 && stride == 2 && pad == 1 && (w & 3) == 0 && (h & 1) == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (reinterpret_cast<uintptr_t>(y) & 3u) == 0) {
+    const int w4 = w / 4, strips = (w4 + 31) / 32;
+    const int64_t jobs = int64_t(planes) * strips;
+    const unsigned blocks = unsigned((jobs + 7) / 8);
+    if (precision == 1)
+      maxpool_3x3s2p1_rows_kernel<__half2><<<blocks, 256, 0, st>>>(static_cast<const uint2*>(x), static_cast<uint32_t*>(y), planes, h, w4, oh, ow / 2, strips);
+    else
+      maxpool_3x3s2p1_rows_kernel<__nv_bfloat162><<<blocks, 256, 0, st>>>(static_cast<const uint2*>(x), static_cast<uint32_t*>(y), planes, h, w4, oh, ow / 2, strips);
+    return cudaGetLastError();
+  }
   if ((precision == 1 || precision == 2) && k == 3 && stride == 2 && pad == 1 && (w & 1) == 0 && (h & 1) == 0 &&
       (reinterpret_cast<uintptr_t>(x) & 3u) == 0 && oh <= 65535) {
     const dim3 g3(unsigned((ow + 255) / 256), unsigned(oh), unsigned(planes < 4096 ? planes : 4096));
