@@ -105,6 +105,9 @@ struct Resolved {
   // Width geometry the kernel and its tensor maps see: the problem's own, except on the row-gather route (variant 5),
   // where the S taps of a filter row have become channels of a tensor of width Q (kernel width 1, stride 1, no padding).
   int eff_in_w, eff_kernel_w, eff_stride_w, eff_pad_w;
+  // A 1x1 convolution with stride > 1 and no padding over an NCHW tensor (variant 4): the repack copies only the pixels
+  // it reads, and the kernel sees a stride-1 1x1 problem over that copy of out_h x out_w pixels per image.
+  int subsampled;
   double est_cycles;  // the cost model's estimate for the chosen configuration (SM cycles; 0 on the FP32 path)
   int tma_epilogue;  // channel-contiguous output staged in shared memory and written by TMA stores
   int swap;          // transposed accumulator (lane = output channel): NCHW output staged per warp and written by TMA stores
@@ -312,14 +315,18 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   const bool gather_ok = !tf32 && !(d.flags & GIEB_FLAG_INPUT_NHWC) && d.kernel_w > 1 && gather_c2 <= 64;
   const bool gather_pays = gather_ok && 2 * gather_c2 <= d.kernel_w * round_up(d.in_channels, 16);
   if (c.variant == 5 && !gather_ok) return no("variant 5 (row gather) needs an NCHW input, a kernel wider than 1 and kernel_w * channels <= 64");
-  if (c.variant == 4 && !pointwise) return no("variant 4 (tiled activation loads) needs a 1x1 kernel with stride 1 and no padding");
+  const bool strided_pw = !tf32 && !(d.flags & GIEB_FLAG_INPUT_NHWC) && d.kernel_h == 1 && d.kernel_w == 1 && d.pad_h == 0 && d.pad_w == 0 &&
+                          (d.stride_h > 1 || d.stride_w > 1);
+  if (c.variant == 4 && !pointwise && !strided_pw)
+    return no("variant 4 (tiled activation loads) needs a 1x1 kernel without padding (stride 1, or any stride over an NCHW 16-bit input)");
   if (c.variant == 2 && !direct_ok) return no("variant 2 (direct NCHW loads) needs a 1x1 kernel, stride 1, no padding and H*W % 8 == 0");
   const bool in_nhwc = (d.flags & GIEB_FLAG_INPUT_NHWC) != 0;
   if (in_nhwc) {
     if (d.in_channels % 16 != 0) return no("channel-contiguous input needs a channel count that is a multiple of 16");
     if (c.variant == 2) return no("variant 2 reads NCHW activations; a channel-contiguous input takes variant 1 or 4");
   }
-  r->variant = c.variant ? c.variant : (in_nhwc ? (pointwise ? 4 : 1) : (direct_ok ? 2 : (pointwise ? 4 : (gather_pays ? 5 : 1))));
+  r->variant = c.variant ? c.variant : (in_nhwc ? (pointwise ? 4 : 1) : (direct_ok ? 2 : ((pointwise || strided_pw) ? 4 : (gather_pays ? 5 : 1))));
+  r->subsampled = (r->variant == 4 && strided_pw) ? 1 : 0;
   const bool gather = r->variant == 5;
   r->eff_in_w = gather ? g.out_w : d.in_w;
   r->eff_kernel_w = gather ? 1 : d.kernel_w;
@@ -510,7 +517,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
 
   // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
   // src/kernels/tensor_core_mma.cu:265-278)
-  r->ws_x = in_nhwc ? 0 : align256(size_t(d.batch) * d.in_h * r->eff_in_w * r->c_padded * 2);
+  r->ws_x = in_nhwc ? 0 : align256(size_t(d.batch) * (r->subsampled ? size_t(g.out_h) * g.out_w : size_t(d.in_h) * r->eff_in_w) * r->c_padded * 2);
   r->ws_w = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : align256(size_t(d.out_channels) * d.kernel_h * r->eff_kernel_w * r->c_padded * 2);
   // how the split-K slices are summed
   if (c.reduce < 0 || c.reduce > 2) return no("reduce must be 0 (auto), 1 (workspace) or 2 (cluster)");
@@ -627,14 +634,15 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (NCHW activations) failed with CUresult %d", int(res));
     small_tensor_fixup(tm_act, size_t(hw) * d.in_channels * d.batch * 2);
   } else if (mode == 1) {  // 1x1 / stride 1 / pad 0: the NHWC copy is the GEMM operand [pixels][Cp] itself
-    const cuuint64_t dims[2] = {cuuint64_t(el(r.c_padded)), cuuint64_t(d.batch) * d.in_h * d.in_w};
+    const cuuint64_t plane = r.subsampled ? cuuint64_t(pl->g.out_h) * pl->g.out_w : cuuint64_t(d.in_h) * d.in_w;
+    const cuuint64_t dims[2] = {cuuint64_t(el(r.c_padded)), cuuint64_t(d.batch) * plane};
     const cuuint64_t strides[1] = {cuuint64_t(r.c_padded) * 2};
     const cuuint32_t box[2] = {cuuint32_t(el(r.tile_k)), cuuint32_t(kTileM)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult res = g_encode_tiled(tm_act, dt, 2, const_cast<void*>(xn), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (activations) failed with CUresult %d", int(res));
-    small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * d.in_w * r.c_padded * 2);
+    small_tensor_fixup(tm_act, size_t(d.batch) * plane * r.c_padded * 2);
   } else {
     const cuuint64_t dims[4] = {cuuint64_t(el(r.c_padded)), cuuint64_t(r.eff_in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
     const cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(r.eff_in_w) * r.c_padded * 2,
@@ -755,6 +763,10 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   } else if (mode == 2 || in_nhwc) {
     if (!(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) && !w_direct)
       GIEB_CUDA(repack_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded, st));
+  } else if (r.subsampled) {
+    const bool with_w = !(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED);
+    GIEB_CUDA(repack_subsampled_launch(x, xn, d.batch, d.in_channels, d.in_h, d.in_w, pl->g.out_h, pl->g.out_w, d.stride_h, d.stride_w, r.c_padded,
+                                       with_w ? w : nullptr, with_w ? const_cast<void*>(wk) : nullptr, d.out_channels, st));
   } else if (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED)
     GIEB_CUDA(repack_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded, st));
   else

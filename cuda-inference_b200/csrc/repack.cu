@@ -130,11 +130,15 @@ struct RepackJob {
   int span;  // mode 2: channels per CTA
   unsigned blocks;  // hw_tiles * c_tiles * batch
   int prefetch;     // (read from the first job) L2 prefetch of the source lines before the dependency wait
+  // mode 4 (pixel subsampling for strided 1x1 convolutions): HW = out_h * out_w pixels are taken from a source plane of
+  // src_hw = h * w elements, destination pixel (p, q) from source pixel (p * sub_sh, q * sub_sw)
+  int src_hw, src_w, sub_ow, sub_sh, sub_sw;
 };
 
 // The 128-byte lines one CTA is about to read, one prefetch per line, never outside the source tensor.
 __device__ __forceinline__ void prefetch_source(const RepackJob& j, int hw_tile, int c_tile, int bi) {
   const int t = threadIdx.x;
+  if (j.mode == 4) return;  // (a strided selection of the source: its lines are not one run per channel)
   if (j.mode == 2) {
     const int c0 = c_tile * j.span;
     const int nch = min(j.span, j.C - c0);
@@ -148,6 +152,43 @@ __device__ __forceinline__ void prefetch_source(const RepackJob& j, int hw_tile,
       const uint8_t* row = reinterpret_cast<const uint8_t*>(j.src + (size_t(bi) * j.C + ch) * j.HW + px0);
       const int bytes = min(kTile, j.HW - px0) * 2;
       ptx::prefetch_l2(row + ((t & 1) ? bytes - 1 : 0));  // a 128-byte run touches at most two lines
+    }
+  }
+}
+
+// The tiled transpose over a strided selection of the source pixels: what a 1x1 convolution with stride > 1 and no padding
+// reads.  Only those pixels are repacked ([B][out_h * out_w][Cp]); the convolution then runs as a stride-1 1x1 over the copy
+// and the copy is stride_h * stride_w times smaller than the tensor.  2-byte loads (the selected pixels are not adjacent).
+__device__ __forceinline__ void repack_tile_sub(uint32_t* tile, const RepackJob& j, int hw_tile, int c_tile, int b) {
+  const int px0 = hw_tile * kTile, c0 = c_tile * kTile, t = threadIdx.x;
+  uint16_t* tile16 = reinterpret_cast<uint16_t*>(tile);
+  const int px = t & 63;
+  const int dp = px0 + px;                       // destination pixel
+  const int p = dp / j.sub_ow, q = dp - p * j.sub_ow;
+  const uint16_t* s = j.src + (size_t(b) * j.C + c0) * j.src_hw + size_t(p * j.sub_sh) * j.src_w + q * j.sub_sw;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int ch = (t >> 6) + i * 4;
+    uint16_t v = 0;
+    if (c0 + ch < j.C && dp < j.HW) v = s[size_t(ch) * j.src_hw];
+    tile16[ch * (kLdWords * 2) + px] = v;
+  }
+  __syncthreads();
+  const int lane = t & 31, warp = t >> 5;
+  const int cg = (warp & 1) * 4 + (lane & 3);
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int opx = ((warp >> 1) + it * 4) * 8 + (lane >> 2);
+    if (px0 + opx < j.HW && c0 + cg * 8 < j.Cp) {
+      uint16_t o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = tile16[(cg * 8 + e) * (kLdWords * 2) + opx];
+      uint4 v;
+      v.x = uint32_t(o[0]) | (uint32_t(o[1]) << 16);
+      v.y = uint32_t(o[2]) | (uint32_t(o[3]) << 16);
+      v.z = uint32_t(o[4]) | (uint32_t(o[5]) << 16);
+      v.w = uint32_t(o[6]) | (uint32_t(o[7]) << 16);
+      *reinterpret_cast<uint4*>(j.dst + (size_t(b) * j.HW + px0 + opx) * j.Cp + c0 + cg * 8) = v;
     }
   }
 }
@@ -170,7 +211,8 @@ __global__ void __launch_bounds__(256) repack_jobs_kernel(const RepackJob a, con
   // kernel behind this one begin its set-up.
   ptx::grid_dep_wait();
   ptx::grid_dep_launch();
-  if (j.mode == 2) repack_small_hw(reinterpret_cast<uint16_t*>(smem), j.src, j.dst, j.C, j.HW, j.Cp, j.span, c_tile, bi);
+  if (j.mode == 4) repack_tile_sub(smem, j, hw_tile, c_tile, bi);
+  else if (j.mode == 2) repack_small_hw(reinterpret_cast<uint16_t*>(smem), j.src, j.dst, j.C, j.HW, j.Cp, j.span, c_tile, bi);
   else if (j.mode == 1) repack_tile<1>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
   else if (j.mode == 3) repack_tile<2>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
   else repack_tile<0>(smem, j.src, j.dst, j.C, j.HW, j.Cp, hw_tile, c_tile, bi);
@@ -349,6 +391,7 @@ RepackJob make_job(const void* src, void* dst, int batch, int channels, int hw, 
   }
   j.blocks = 0;
   j.prefetch = prefetch_enabled() ? 1 : 0;
+  j.src_hw = hw; j.src_w = 0; j.sub_ow = 1; j.sub_sh = j.sub_sw = 0;
   return j;
 }
 
@@ -363,6 +406,29 @@ cudaError_t repack_pair_launch(const void* src_a, void* dst_a, int batch_a, int 
   if (src_b != nullptr) {
     b = make_job(src_b, dst_b, batch_b, ch_b, hw_b, cp_b);
     nb = int64_t(b.hw_tiles) * b.c_tiles * batch_b;
+  }
+  if (na + nb > 2147483647LL) return cudaErrorInvalidValue;
+  a.blocks = unsigned(na);
+  b.blocks = unsigned(nb);
+  const cudaError_t e = launch_pdl(repack_jobs_kernel, dim3(unsigned(na + nb)), dim3(256), 0, stream, a, b);
+  if (e != cudaSuccess) return e;
+  return cudaGetLastError();
+}
+
+cudaError_t repack_subsampled_launch(const void* x, void* xn, int batch, int channels, int h, int w, int out_h, int out_w, int stride_h,
+                                     int stride_w, int c_padded, const void* wsrc, void* wdst, int out_channels, cudaStream_t stream) {
+  RepackJob a = make_job(x, xn, batch, channels, out_h * out_w, c_padded);
+  a.mode = 4;
+  a.hw_tiles = (out_h * out_w + kTile - 1) / kTile;
+  a.c_tiles = (c_padded + kTile - 1) / kTile;
+  a.span = kTile;
+  a.src_hw = h * w; a.src_w = w; a.sub_ow = out_w; a.sub_sh = stride_h; a.sub_sw = stride_w;
+  RepackJob b = a;
+  const int64_t na = int64_t(a.hw_tiles) * a.c_tiles * batch;
+  int64_t nb = 0;
+  if (wsrc != nullptr) {  // the 1x1 filters: [O][C] -> [O][Cp]
+    b = make_job(wsrc, wdst, out_channels, channels, 1, c_padded);
+    nb = int64_t(b.hw_tiles) * b.c_tiles * out_channels;
   }
   if (na + nb > 2147483647LL) return cudaErrorInvalidValue;
   a.blocks = unsigned(na);

@@ -86,7 +86,8 @@ typedef struct gieb_conv_cfg {
   int32_t stages;   /* shared-memory ring depth, 2..8; 0 = auto                                              */
   int32_t split_k;  /* number of reduction splits, >= 1; 0 = auto                                            */
   int32_t variant;  /* 0 = auto; 1 = tensor path, im2col-mode TMA over the channel-contiguous copy (any geometry);
-                       4 = tensor path, tiled TMA over that copy (1x1, stride 1, pad 0);
+                       4 = tensor path, tiled TMA over that copy (1x1, pad 0; stride 1, or any stride over an NCHW 16-bit
+                           input, in which case the copy holds only the pixels the convolution reads);
                        2 = tensor path reading the caller's NCHW activations directly, no activation repack
                            (1x1, stride 1, pad 0, H*W % 8 == 0; a call whose x is not 16-byte aligned takes route 4);
                        3 = FP32 SIMT;

@@ -210,6 +210,38 @@ def test_transposed_accumulator_fused_residual(pkg, orc, oracle, case, res_off, 
     _check(oracle, p, out.read(oracle).reshape(p.y_shape), ref, scale, f"transposed accumulator + residual, case {case} res_off={res_off}")
 
 
+STRIDED_1X1_CASES = [
+    # 1x1 kernels with stride > 1 and no padding over NCHW input: the repack copies only the pixels the convolution reads and
+    # the kernel runs a stride-1 1x1 over the copy (tiled loads); variant 1 keeps the im2col route over the whole tensor
+    ((2, 64, 9, 11, 32, 1, 1, 2, 3, 0, 0), dict()),                       # asymmetric strides, odd extents
+    ((3, 96, 14, 14, 160, 1, 1, 2, 2, 0, 0), dict()),
+    ((2, 40, 7, 7, 50, 1, 1, 3, 3, 0, 0), dict(tile_k=16)),                # channel tails, 3 x 3 output
+    ((4, 256, 28, 28, 512, 1, 1, 2, 2, 0, 0), dict()),                     # a projection shortcut
+    ((4, 256, 28, 28, 512, 1, 1, 2, 2, 0, 0), dict(variant=1)),            # the same through im2col loads
+    ((1, 128, 5, 5, 64, 1, 1, 4, 4, 0, 0), dict(tile_k=32, split_k=2, reduce=1)),
+]
+
+
+@pytest.mark.parametrize("case", range(len(STRIDED_1X1_CASES)))
+@pytest.mark.parametrize("prec_name", ["fp16", "bf16"])
+def test_strided_pointwise_reads_a_subsampled_copy(pkg, orc, oracle, case, prec_name):
+    args, kw = STRIDED_1X1_CASES[case]
+    prec = orc.FP16 if prec_name == "fp16" else orc.BF16
+    p = orc.Problem.P(*args, precision=prec, bias=(case % 2 == 0), relu=(case % 3 != 0))
+    x, w, b = oracle.make_conv_data(p, 8400 + case, case % 4)
+    ref, scale = oracle.conv2d(p, x, w, b if p.has_bias else None)
+    got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b if p.has_bias else None, cfg=pkg.make_cfg(**kw), repeats=2)
+    want_variant = kw.get("variant", 4)
+    assert plan.info.cfg.variant == want_variant
+    if want_variant == 4:  # the copy holds out_h * out_w pixels per image, not in_h * in_w
+        al = lambda n: (n + 255) // 256 * 256
+        cp, sk = plan.info.padded_channels, plan.info.cfg.split_k
+        y_elems = int(np.prod(p.y_shape))
+        expect = al(p.batch * p.out_h * p.out_w * cp * 2) + al(p.out_channels * cp * 2) + (al(sk * ((y_elems + 3) // 4 * 4) * 4) if sk > 1 else 0)
+        assert plan.workspace_bytes == expect
+    _check(oracle, p, got, ref, scale, f"strided 1x1 case {case} {kw} {prec_name}")
+
+
 FP8_CASES = [
     # FP8 E4M3 x and w (1 byte per element), float bias, FP16 y: kind::f8f6f4 MMAs over the same byte layouts as the 16-bit path
     ((2, 64, 12, 12, 64, 3, 3, 1, 1, 1, 1), dict()),
