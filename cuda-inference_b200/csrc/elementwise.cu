@@ -126,11 +126,16 @@ maxpool_3x3s2p1_kernel(const uint32_t* __restrict__ x, uint16_t* __restrict__ y,
 // that contain it, so every input element is read once.  Rows are fetched eight at a time (eight loads in flight per lane).
 template <typename T2>
 __global__ void __launch_bounds__(256)
-maxpool_3x3s2p1_rows_kernel(const uint2* __restrict__ x, uint32_t* __restrict__ y, int planes, int h, int w4, int oh, int ow2, int strips) {
+maxpool_3x3s2p1_rows_kernel(const uint2* __restrict__ x, uint32_t* __restrict__ y, int planes, int h, int w4, int oh, int ow2, int strips,
+                            int bands, int band_rows) {
   const int lane = threadIdx.x & 31;
   const int64_t job = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (plane, strip)
-  if (job >= int64_t(planes) * strips) return;  // whole warps leave together
-  const int plane = int(job / strips), strip = int(job - int64_t(plane) * strips);
+  if (job >= int64_t(planes) * strips * bands) return;  // whole warps leave together
+  // few planes: a plane is cut into `bands` bands of band_rows output rows (a multiple of 4), one warp each
+  const int band = int(job % bands);
+  const int64_t ps = job / bands;
+  const int plane = int(ps / strips), strip = int(ps - int64_t(plane) * strips);
+  const int oy_begin = band * band_rows, oy_end = min(oh, oy_begin + band_rows);
   const int c = strip * 32 + lane;               // this lane's 4-column group
   const bool live = c < w4;
   const int cc = live ? c : w4 - 1;              // dead lanes shadow the last group so that shuffles stay defined
@@ -138,7 +143,17 @@ maxpool_3x3s2p1_rows_kernel(const uint2* __restrict__ x, uint32_t* __restrict__ 
   uint32_t* yp = y + size_t(plane) * oh * ow2 + cc;
   T2 carry = T2();     // horizontal maxima of input row 2*oy - 1 (the row above the window's middle); unused while have_carry is false
   bool have_carry = false;
-  for (int oy0 = 0; oy0 < oh; oy0 += 4) {
+  if (oy_begin > 0) {  // the row above this band's first window row
+    const size_t ro = size_t(2 * oy_begin - 1) * w4;
+    const uint2 v0 = xp[ro];
+    uint32_t l0 = __shfl_up_sync(0xffffffffu, v0.y, 1);
+    if (lane == 0 && cc > 0) l0 = xp[ro - 1].y;
+    const T2 a = *reinterpret_cast<const T2*>(&v0.x), b = *reinterpret_cast<const T2*>(&v0.y);
+    const T2 l = *reinterpret_cast<const T2*>(&l0);
+    carry = __hmax2(__hmax2(a, T2(a.y, b.x)), T2(cc > 0 ? l.y : a.x, b.y));
+    have_carry = true;
+  }
+  for (int oy0 = oy_begin; oy0 < oy_end; oy0 += 4) {
     // rows 2*oy0 .. 2*oy0 + 7 (eight rows = four output rows), all loads first
     uint2 v[8];
     uint32_t lf[8];
@@ -164,7 +179,7 @@ maxpool_3x3s2p1_rows_kernel(const uint2* __restrict__ x, uint32_t* __restrict__ 
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int oy = oy0 + k;
-      if (oy >= oh) break;
+      if (oy >= oy_end) break;
       T2 m = hm[2 * k];                                   // row 2*oy (always inside: oy < oh = h / 2)
       if (2 * oy + 1 < h) m = __hmax2(m, hm[2 * k + 1]);  // row 2*oy + 1
       if (have_carry) m = __hmax2(m, carry);              // row 2*oy - 1
@@ -258,12 +273,19 @@ cudaError_t maxpool2d_launch(int precision, int batch, int channels, int h, int 
   if ((precision == 1 || precision == 2) && k == 3 && stride == 2 && pad == 1 && (w & 3) == 0 && (h & 1) == 0 &&
       (reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (reinterpret_cast<uintptr_t>(y) & 3u) == 0) {
     const int w4 = w / 4, strips = (w4 + 31) / 32;
-    const int64_t jobs = int64_t(planes) * strips;
+    // enough warps for every SM (about 32 each): planes x column strips, and bands of output rows when that is too few
+    int bands = int((int64_t(kNumSms) * 32 + int64_t(planes) * strips - 1) / (int64_t(planes) * strips));
+    const int max_bands = (oh + 3) / 4;
+    if (bands > max_bands) bands = max_bands;
+    if (bands < 1) bands = 1;
+    const int band_rows = ((oh + bands - 1) / bands + 3) / 4 * 4;
+    bands = (oh + band_rows - 1) / band_rows;
+    const int64_t jobs = int64_t(planes) * strips * bands;
     const unsigned blocks = unsigned((jobs + 7) / 8);
     if (precision == 1)
-      maxpool_3x3s2p1_rows_kernel<__half2><<<blocks, 256, 0, st>>>(static_cast<const uint2*>(x), static_cast<uint32_t*>(y), planes, h, w4, oh, ow / 2, strips);
+      maxpool_3x3s2p1_rows_kernel<__half2><<<blocks, 256, 0, st>>>(static_cast<const uint2*>(x), static_cast<uint32_t*>(y), planes, h, w4, oh, ow / 2, strips, bands, band_rows);
     else
-      maxpool_3x3s2p1_rows_kernel<__nv_bfloat162><<<blocks, 256, 0, st>>>(static_cast<const uint2*>(x), static_cast<uint32_t*>(y), planes, h, w4, oh, ow / 2, strips);
+      maxpool_3x3s2p1_rows_kernel<__nv_bfloat162><<<blocks, 256, 0, st>>>(static_cast<const uint2*>(x), static_cast<uint32_t*>(y), planes, h, w4, oh, ow / 2, strips, bands, band_rows);
     return cudaGetLastError();
   }
   if ((precision == 1 || precision == 2) && k == 3 && stride == 2 && pad == 1 && (w & 1) == 0 && (h & 1) == 0 &&
