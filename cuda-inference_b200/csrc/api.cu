@@ -108,6 +108,10 @@ struct Resolved {
   // A 1x1 convolution with stride > 1 and no padding over an NCHW tensor (variant 4): the repack copies only the pixels
   // it reads, and the kernel sees a stride-1 1x1 problem over that copy of out_h x out_w pixels per image.
   int subsampled;
+  // Row-gather route with stride_w = 2 and at most 4 channels: the gathered tensor holds column PAIRS once (16 bytes per
+  // position) and the im2col tensor map reads it with a pixel stride of one position, so that the windows of adjacent
+  // output columns overlap in memory instead of being stored twice.  gp_t positions (8 values each) per window.
+  int gather_pairs, gp_positions, gp_left, gp_t, gp_shift;
   double est_cycles;  // the cost model's estimate for the chosen configuration (SM cycles; 0 on the FP32 path)
   int tma_epilogue;  // channel-contiguous output staged in shared memory and written by TMA stores
   int swap;          // transposed accumulator (lane = output channel): NCHW output staged per warp and written by TMA stores
@@ -267,6 +271,14 @@ bool pdl_enabled() {
   }();
   return on;
 }
+// GIEB_GATHER_PAIRS=0 keeps the row-gather route on its one-window-per-pixel layout (a debugging aid).
+bool pairs_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("GIEB_GATHER_PAIRS");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 // GIEB_DISABLE_PREFETCH=1 switches the L2 prefetches that precede the dependency waits off (a debugging aid).
 bool prefetch_enabled() {
   static const bool on = [] {
@@ -367,10 +379,22 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   }
   if (r->tile_k != 16 && r->tile_k != 32 && r->tile_k != 64) return no("tile_k must be 16, 32 or 64");
   if (in_nhwc && d.in_channels % r->tile_k != 0) return no("tile_k must divide the channel count of a channel-contiguous input (it is read in place)");
+  if (gather && d.stride_w == 2 && d.in_w % 2 == 0 && d.in_channels <= 4 && d.kernel_w - 1 - d.pad_w >= 0 && pairs_enabled()) {
+    const int left = (d.pad_w + 1) / 2, after = (d.kernel_w - 1 - d.pad_w) / 2;
+    const int t = left + after + 1;
+    if (t == 2 || t == 4 || t == 8) {
+      int right = (g.out_w - 1) + after - (d.in_w / 2 - 1);
+      if (right < 0) right = 0;
+      r->gather_pairs = 1;
+      r->gp_left = left; r->gp_t = t; r->gp_shift = 2 * left - d.pad_w;
+      r->gp_positions = d.in_w / 2 + left + right;
+    }
+  }
   if (gather) {
-    if (!c.tile_k) r->tile_k = gather_c2 % 64 == 0 ? 64 : (gather_c2 % 32 == 0 ? 32 : 16);
-    if (gather_c2 % r->tile_k != 0) return no("tile_k must divide the gathered row length (padded kernel_w * channels)");
-    r->c_padded = gather_c2;
+    const int gc2 = r->gather_pairs ? r->gp_t * 8 : gather_c2;
+    if (!c.tile_k) r->tile_k = gc2 % 64 == 0 ? 64 : (gc2 % 32 == 0 ? 32 : 16);
+    if (gc2 % r->tile_k != 0) return no("tile_k must divide the gathered row length (padded kernel_w * channels)");
+    r->c_padded = gc2;
   } else if (fp8) {
     r->c_padded = round_up(d.in_channels, 2 * r->tile_k) / 2;
   } else if (tf32) {
@@ -518,6 +542,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   // workspace: channel-padded NHWC activations, prepacked weights, split-K partials (ws_layout analogue,
   // src/kernels/tensor_core_mma.cu:265-278)
   r->ws_x = in_nhwc ? 0 : align256(size_t(d.batch) * (r->subsampled ? size_t(g.out_h) * g.out_w : size_t(d.in_h) * r->eff_in_w) * r->c_padded * 2);
+  if (r->gather_pairs) r->ws_x = align256(size_t(d.batch) * d.in_h * r->gp_positions * 16);
   r->ws_w = (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? 0 : align256(size_t(d.out_channels) * d.kernel_h * r->eff_kernel_w * r->c_padded * 2);
   // how the split-K slices are summed
   if (c.reduce < 0 || c.reduce > 2) return no("reduce must be 0 (auto), 1 (workspace) or 2 (cluster)");
@@ -645,8 +670,13 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
     small_tensor_fixup(tm_act, size_t(d.batch) * plane * r.c_padded * 2);
   } else {
     const cuuint64_t dims[4] = {cuuint64_t(el(r.c_padded)), cuuint64_t(r.eff_in_w), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
-    const cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(r.eff_in_w) * r.c_padded * 2,
-                                   cuuint64_t(d.in_h) * r.eff_in_w * r.c_padded * 2};
+    cuuint64_t strides[3] = {cuuint64_t(r.c_padded) * 2, cuuint64_t(r.eff_in_w) * r.c_padded * 2,
+                             cuuint64_t(d.in_h) * r.eff_in_w * r.c_padded * 2};
+    if (r.gather_pairs) {  // overlapping pixels: one position (16 bytes) apart, each gp_t positions long
+      strides[0] = 16;
+      strides[1] = cuuint64_t(r.gp_positions) * 16;
+      strides[2] = cuuint64_t(d.in_h) * r.gp_positions * 16;
+    }
     const int lower[2] = {-r.eff_pad_w, -d.pad_h};
     const int upper[2] = {r.eff_pad_w - (r.eff_kernel_w - 1), d.pad_h - (d.kernel_h - 1)};
     const cuuint32_t trav[4] = {1, cuuint32_t(r.eff_stride_w), cuuint32_t(d.stride_h), 1};
@@ -654,7 +684,7 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
                                          cuuint32_t(kTileM), trav, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeIm2col failed with CUresult %d", int(res));
-    small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * r.eff_in_w * r.c_padded * 2);
+    small_tensor_fixup(tm_act, r.gather_pairs ? size_t(d.batch) * d.in_h * r.gp_positions * 16 : size_t(d.batch) * d.in_h * r.eff_in_w * r.c_padded * 2);
   }
   {
     const cuuint64_t kp = cuuint64_t(d.kernel_h) * r.eff_kernel_w * r.c_padded;  // in 2-byte units
@@ -757,6 +787,10 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   } else if (d.precision == GIEB_TF32) {  // FP32 tensors rounded to TF32 while they are repacked (two launches)
     GIEB_CUDA(repack_tf32_launch(x, xn, d.batch, d.in_channels, d.in_h * d.in_w, r.c_padded / 2, st));
     GIEB_CUDA(repack_tf32_launch(w, const_cast<void*>(wk), d.out_channels, d.in_channels, d.kernel_h * d.kernel_w, r.c_padded / 2, st));
+  } else if (r.variant == 5 && r.gather_pairs) {
+    const bool with_w = !(d.flags & GIEB_FLAG_WEIGHTS_PREPACKED);
+    GIEB_CUDA(gather_pairs_launch(x, xn, d.batch, d.in_channels, d.in_h, d.in_w, r.gp_positions, r.gp_left, r.gp_t, r.gp_shift,
+                                  with_w ? w : nullptr, with_w ? const_cast<void*>(wk) : nullptr, d.out_channels, d.kernel_h, d.kernel_w, st));
   } else if (r.variant == 5) {  // row gather of the activations (and of the weights unless they come gathered)
     GIEB_CUDA(gather_rows_launch(x, xn, d.batch, d.in_channels, d.in_h, d.in_w, pl->g.out_w, d.kernel_w, d.stride_w, d.pad_w, r.c_padded,
                                  (d.flags & GIEB_FLAG_WEIGHTS_PREPACKED) ? nullptr : w, const_cast<void*>(wk), d.out_channels, d.kernel_h, st));
@@ -980,7 +1014,10 @@ int gieb_conv_plan_prepack_weights(const gieb_conv_plan* plan, const void* w, vo
   if (r.variant == 3) return fail(GIEB_UNSUPPORTED, "the FP32 path reads OIHW weights directly");
   if (reinterpret_cast<uintptr_t>(dst) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "prepacked weights must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (r.variant == 5)
+  if (r.variant == 5 && r.gather_pairs)
+    GIEB_CUDA(gather_pairs_launch(nullptr, nullptr, d.batch, d.in_channels, d.in_h, d.in_w, r.gp_positions, r.gp_left, r.gp_t, r.gp_shift, w, dst,
+                                  d.out_channels, d.kernel_h, d.kernel_w, st));
+  else if (r.variant == 5)
     GIEB_CUDA(gather_rows_launch(nullptr, nullptr, d.batch, d.in_channels, d.in_h, d.in_w, plan->g.out_w, d.kernel_w, d.stride_w, d.pad_w,
                                  r.c_padded, w, dst, d.out_channels, d.kernel_h, st));
   else

@@ -185,6 +185,9 @@ cudaError_t repack_tf32_launch(const void* src, void* dst, int batch, int channe
 cudaError_t repack_bytes_pair_launch(const void* src_a, void* dst_a, int batch_a, int ch_a, int hw_a, int cp_a, const void* src_b,
                                      void* dst_b, int batch_b, int ch_b, int hw_b, int cp_b, cudaStream_t stream);
 // Two repacks (activations + weights) in ONE launch; src_b == nullptr runs only the first.
+// Column-pair gather (row gather for stride_w = 2 and <= 4 channels): X3[n][h][positions][8], W3[o][r][t_positions * 8].
+cudaError_t gather_pairs_launch(const void* x, void* x3, int batch, int channels, int h, int w, int positions, int left, int t_positions,
+                                int shift, const void* wsrc, void* w3, int out_channels, int kernel_h, int kernel_w, cudaStream_t stream);
 // Activations of a strided 1x1 convolution: only the pixels it reads, [batch][out_h * out_w][c_padded]; optionally the
 // 1x1 filters in the same launch.
 cudaError_t repack_subsampled_launch(const void* x, void* xn, int batch, int channels, int h, int w, int out_h, int out_w, int stride_h,

@@ -438,6 +438,97 @@ cudaError_t repack_subsampled_launch(const void* x, void* xn, int batch, int cha
   return cudaGetLastError();
 }
 
+// ---- column-pair gather: the row gather for stride_w = 2 and at most 4 channels, four times smaller --------------------
+// X3[n][h][i][j * C + c] = x[n][c][h][2 * (i - left) + j], j = 0, 1 (8 values = 16 bytes per position i, zero where the
+// column lies outside the image or C * 2 < 8).  The window of output column q (input columns 2q - pad .. 2q - pad + S - 1)
+// is the T adjacent positions q .. q + T - 1, i.e. the T * 16 contiguous bytes at position q: the convolution's tensor
+// map reads X3 with a pixel stride of ONE position (16 bytes) and T * 8 "channels" per pixel, so consecutive pixels overlap
+// and nothing is stored twice.  W3[o][r][t * 8 + j * C + c] = w[o][c][r][2t + j - shift] (zero outside the kernel).
+struct PairGatherJob {
+  const uint16_t* x;   // null: weights only
+  uint16_t* x3;
+  const uint16_t* w;   // null: activations only
+  uint16_t* w3;
+  int B, C, H, W, R, S, O, positions, left, T, shift, words;  // words: x may be read as aligned 32-bit column pairs
+  unsigned x_blocks;
+};
+
+namespace {
+__global__ void __launch_bounds__(256) gather_pairs_kernel(const PairGatherJob j) {
+  ptx::grid_dep_wait();
+  ptx::grid_dep_launch();
+  if (blockIdx.x >= j.x_blocks) {  // weights: one thread per (o, r, e)
+    const int c2 = j.T * 8;
+    const int64_t total = int64_t(j.O) * j.R * c2;
+    for (int64_t i = int64_t(blockIdx.x - j.x_blocks) * 256 + threadIdx.x; i < total; i += int64_t(gridDim.x - j.x_blocks) * 256) {
+      const int e = int(i % c2);
+      const int64_t orr = i / c2;
+      const int r = int(orr % j.R), o = int(orr / j.R);
+      const int t = e >> 3, k = e & 7;
+      uint16_t v = 0;
+      if (k < 2 * j.C) {
+        const int jj = k / j.C, c = k - jj * j.C;
+        const int s = 2 * t + jj - j.shift;
+        if (s >= 0 && s < j.S) v = j.w[((int64_t(o) * j.C + c) * j.R + r) * j.S + s];
+      }
+      j.w3[i] = v;
+    }
+    return;
+  }
+  const int64_t total = int64_t(j.B) * j.H * j.positions;
+  const int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= total) return;
+  const int pos = int(i % j.positions);
+  const int64_t nh = i / j.positions;
+  const int h = int(nh % j.H), n = int(nh / j.H);
+  const int pp = pos - j.left;
+  uint16_t v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (pp >= 0 && 2 * pp < j.W) {
+    const uint16_t* src = j.x + ((int64_t(n) * j.C) * j.H + h) * j.W + 2 * pp;
+    for (int c = 0; c < j.C; ++c) {
+      const uint16_t* p = src + int64_t(c) * j.H * j.W;
+      if (j.words) {
+        const uint32_t two = *reinterpret_cast<const uint32_t*>(p);
+        v[c] = uint16_t(two & 0xffffu);
+        v[j.C + c] = uint16_t(two >> 16);
+      } else {
+        v[c] = p[0];
+        v[j.C + c] = p[1];
+      }
+    }
+  }
+  uint4 o;
+  o.x = uint32_t(v[0]) | (uint32_t(v[1]) << 16);
+  o.y = uint32_t(v[2]) | (uint32_t(v[3]) << 16);
+  o.z = uint32_t(v[4]) | (uint32_t(v[5]) << 16);
+  o.w = uint32_t(v[6]) | (uint32_t(v[7]) << 16);
+  reinterpret_cast<uint4*>(j.x3)[i] = o;
+}
+}  // namespace
+
+cudaError_t gather_pairs_launch(const void* x, void* x3, int batch, int channels, int h, int w, int positions, int left, int t_positions,
+                                int shift, const void* wsrc, void* w3, int out_channels, int kernel_h, int kernel_w, cudaStream_t stream) {
+  PairGatherJob j;
+  j.x = static_cast<const uint16_t*>(x);
+  j.x3 = static_cast<uint16_t*>(x3);
+  j.w = static_cast<const uint16_t*>(wsrc);
+  j.w3 = static_cast<uint16_t*>(w3);
+  j.B = batch; j.C = channels; j.H = h; j.W = w; j.R = kernel_h; j.S = kernel_w; j.O = out_channels;
+  j.positions = positions; j.left = left; j.T = t_positions; j.shift = shift;
+  j.words = (reinterpret_cast<uintptr_t>(x) & 3u) == 0 ? 1 : 0;   // (w is even on this route)
+  const int64_t xb = x != nullptr ? (int64_t(batch) * h * positions + 255) / 256 : 0;
+  int64_t wb = 0;
+  if (wsrc != nullptr) {
+    wb = (int64_t(out_channels) * kernel_h * t_positions * 8 + 255) / 256;
+    if (wb > 1024) wb = 1024;
+  }
+  if (xb + wb > 2147483647LL || xb + wb == 0) return cudaErrorInvalidValue;
+  j.x_blocks = unsigned(xb);
+  const cudaError_t e = launch_pdl(gather_pairs_kernel, dim3(unsigned(xb + wb)), dim3(256), 0, stream, j);
+  if (e != cudaSuccess) return e;
+  return cudaGetLastError();
+}
+
 cudaError_t gather_rows_launch(const void* x, void* x2, int batch, int channels, int h, int w, int q, int kernel_w, int stride_w,
                                int pad_w, int c2, const void* wsrc, void* w2, int out_channels, int kernel_h, cudaStream_t stream) {
   GatherJob j;

@@ -358,6 +358,11 @@ GATHER_CASES = [
     ((1, 3, 64, 64, 32, 7, 7, 2, 2, 3, 3), dict(variant=5, tile_m=256, tile_n=32)),
     ((2, 3, 30, 40, 64, 7, 7, 2, 2, 3, 3), dict(variant=5)),             # whole-row gather, rows not a multiple of four
     ((3, 4, 9, 16, 32, 5, 5, 1, 1, 2, 2), dict(variant=5)),              # whole-row gather, stride 1, 20 -> 32 channels
+    # stride_w = 2 with at most 4 channels: column pairs stored once, overlapping windows (the layout the stem takes)
+    ((2, 4, 20, 22, 16, 3, 3, 2, 2, 1, 1), dict(variant=5)),             # two positions per window (16 values)
+    ((2, 1, 18, 26, 32, 7, 7, 2, 2, 3, 3), dict(variant=5)),             # one channel
+    ((1, 3, 33, 48, 64, 7, 7, 1, 2, 3, 2), dict(variant=5)),             # pad_w = 2: the window starts on a pair, stride_h = 1
+    ((3, 2, 12, 8, 24, 7, 7, 2, 2, 3, 3), dict(variant=5, tile_k=16)),   # four output columns, windows mostly padding
 ]
 
 
@@ -372,6 +377,9 @@ def test_row_gather_route(pkg, orc, oracle, case, prec_name):
     got, plan, _ = gu.run_conv(pkg, oracle, p, x, w, b, cfg=pkg.make_cfg(**kw))
     assert plan.info.variant == 5
     _check(oracle, p, got, ref, scale, f"gather case {case} {kw} {prec_name}")
+    if p.stride_w == 2 and p.in_channels <= 4:  # x off by one element: the gather reads columns one by one
+        got, _, _ = gu.run_conv(pkg, oracle, p, x, w, b, cfg=pkg.make_cfg(**kw), offsets=(1, 0, 0))
+        _check(oracle, p, got, ref, scale, f"gather case {case} {kw} {prec_name}, x misaligned")
 
 
 @pytest.mark.parametrize("case", range(len(DIRECT_CASES)))
