@@ -112,6 +112,7 @@ struct Resolved {
   // position) and the im2col tensor map reads it with a pixel stride of one position, so that the windows of adjacent
   // output columns overlap in memory instead of being stored twice.  gp_t positions (8 values each) per window.
   int gather_pairs, gp_positions, gp_left, gp_t, gp_shift;
+  int strip;  // the pair layout read as one position strip per (output row, filter row): see resolve()
   double est_cycles;  // the cost model's estimate for the chosen configuration (SM cycles; 0 on the FP32 path)
   int tma_epilogue;  // channel-contiguous output staged in shared memory and written by TMA stores
   int swap;          // transposed accumulator (lane = output channel): NCHW output staged per warp and written by TMA stores
@@ -271,6 +272,14 @@ bool pdl_enabled() {
   }();
   return on;
 }
+// GIEB_GATHER_STRIPS=0 reads the pair layout through im2col-mode loads of whole windows (a debugging aid).
+bool strips_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("GIEB_GATHER_STRIPS");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 // GIEB_GATHER_PAIRS=0 keeps the row-gather route on its one-window-per-pixel layout (a debugging aid).
 bool pairs_enabled() {
   static const bool on = [] {
@@ -346,7 +355,23 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   r->eff_pad_w = gather ? 0 : d.pad_w;
   r->boxes_per_image = ceil_div(int64_t(d.in_h) * d.in_w, 64);
   // GEMM rows: output pixels, or (variant 2) 64-pixel boxes that never straddle an image
-  const int64_t rows = r->variant == 2 ? int64_t(d.batch) * r->boxes_per_image * 64 : g.pixels;
+  if (gather && d.stride_w == 2 && d.in_w % 2 == 0 && d.in_channels <= 4 && d.kernel_w - 1 - d.pad_w >= 0 && pairs_enabled()) {
+    const int left = (d.pad_w + 1) / 2, after = (d.kernel_w - 1 - d.pad_w) / 2;
+    const int t = left + after + 1;
+    if (t == 2 || t == 4 || t == 8) {
+      int right = (g.out_w - 1) + after - (d.in_w / 2 - 1);
+      if (right < 0) right = 0;
+      r->gather_pairs = 1;
+      r->gp_left = left; r->gp_t = t; r->gp_shift = 2 * left - d.pad_w;
+      r->gp_positions = d.in_w / 2 + left + right;
+    }
+  }
+  // The pair layout read as STRIPS: one 128-row tile per output row, whose operand for filter row r is the strip of positions
+  // of ONE input row (a single 2 KiB box instead of 128 pixels x 64 bytes), multiplied as overlapping windows through an
+  // unswizzled descriptor.  Needs out_w <= 128 and a CTA that finishes its tiles alone.
+  r->strip = (r->gather_pairs && g.out_w <= 128 && c.split_k <= 1 && c.reduce == 0 && c.cta_pair != 2 && (c.tile_k == 0 || c.tile_k == r->gp_t * 8) &&
+              strips_enabled()) ? 1 : 0;   // (one slab per filter row: the strip is loaded once per slab)
+  const int64_t rows = r->strip ? int64_t(d.batch) * g.out_h * 128 : (r->variant == 2 ? int64_t(d.batch) * r->boxes_per_image * 64 : g.pixels);
 
   // hardware limits of the im2col-mode tensor map (rank 4): traversal strides 1..8, corners and offsets 8-bit
   if (d.stride_h > 8 || d.stride_w > 8) return no("stride > 8 cannot be expressed by the TMA im2col traversal stride");
@@ -379,17 +404,6 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   }
   if (r->tile_k != 16 && r->tile_k != 32 && r->tile_k != 64) return no("tile_k must be 16, 32 or 64");
   if (in_nhwc && d.in_channels % r->tile_k != 0) return no("tile_k must divide the channel count of a channel-contiguous input (it is read in place)");
-  if (gather && d.stride_w == 2 && d.in_w % 2 == 0 && d.in_channels <= 4 && d.kernel_w - 1 - d.pad_w >= 0 && pairs_enabled()) {
-    const int left = (d.pad_w + 1) / 2, after = (d.kernel_w - 1 - d.pad_w) / 2;
-    const int t = left + after + 1;
-    if (t == 2 || t == 4 || t == 8) {
-      int right = (g.out_w - 1) + after - (d.in_w / 2 - 1);
-      if (right < 0) right = 0;
-      r->gather_pairs = 1;
-      r->gp_left = left; r->gp_t = t; r->gp_shift = 2 * left - d.pad_w;
-      r->gp_positions = d.in_w / 2 + left + right;
-    }
-  }
   if (gather) {
     const int gc2 = r->gather_pairs ? r->gp_t * 8 : gather_c2;
     if (!c.tile_k) r->tile_k = gc2 % 64 == 0 ? 64 : (gc2 % 32 == 0 ? 32 : 16);
@@ -431,7 +445,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
   int best_m = 0, best_n = 0, best_s = 0, best_mode = 0, best_pair = 0, best_swap = 0;
   const int n_opts[4] = {32, 64, 128, 256};
   // 256-pixel tiles of CTA pairs: only the workspace reduction for split-K
-  const bool pair_unasked = c.cta_pair == 0 && d.precision != GIEB_TF32 && c.tile_m == 0 && c.split_k <= 1 && c.reduce == 0 && c.variant != 2 &&
+  const bool pair_unasked = c.cta_pair == 0 && !r->strip && d.precision != GIEB_TF32 && c.tile_m == 0 && c.split_k <= 1 && c.reduce == 0 && c.variant != 2 &&
                             auto_pair(d, rows, r->total_kb, r->tile_k);
   for (int ni = 1; ni < 4 && d.precision != GIEB_TF32 && (c.cta_pair == 2 || pair_unasked) && (c.tile_m == 0 || c.tile_m == 256) && c.reduce != 2; ++ni) {
     const int tn = n_opts[ni];
@@ -453,7 +467,7 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
       const int tn = n_opts[ni];
       if (r->tile_n && tn != r->tile_n) continue;
       if (!r->tile_n && tn > 32 && tn / 2 >= d.out_channels) continue;  // never pad channels by 2x or more
-      for (int s = 1; s <= 16; ++s) {
+      for (int s = 1; s <= (r->strip ? 1 : 16); ++s) {   // (position strips: a CTA finishes its tiles alone)
         if (c.split_k && s != c.split_k) continue;
         if (s > 1 && r->total_kb < 2 * s) break;  // reduction too short (src/kernels/tensor_core_mma.cu:292 rule)
         const int kbs = ceil_div(r->total_kb, s);
@@ -496,8 +510,8 @@ int resolve(const gieb_conv_desc& d, const gieb_conv_cfg* user, Resolved* r, cha
 
   // Channel-contiguous output goes through shared-memory boxes and TMA stores when the rows of the [pixels][O] matrix
   // are 16-byte multiples, rows are numbered by pixel (not the direct-NCHW route) and each CTA finishes its tiles alone.
-  r->tma_epilogue = (d.flags & GIEB_FLAG_OUTPUT_NHWC) && d.out_channels % 8 == 0 && r->variant != 2 && r->split_k == 1;
-  bool swap = best_swap != 0 && !r->pair && r->split_k == 1;  // 2 KiB of staging per epilogue warp
+  r->tma_epilogue = (d.flags & GIEB_FLAG_OUTPUT_NHWC) && d.out_channels % 8 == 0 && r->variant != 2 && !r->strip && r->split_k == 1;
+  bool swap = best_swap != 0 && !r->pair && !r->strip && r->split_k == 1;  // 2 KiB of staging per epilogue warp
   const int64_t total_tiles = int64_t(r->tiles_m) * r->tiles_n * r->split_k;
   auto stages_for = [&](size_t epi_smem) {
     int st = c.stages ? c.stages
@@ -658,6 +672,15 @@ int encode_maps(const gieb_conv_plan* pl, int mode, const void* xn, const void* 
                                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (NCHW activations) failed with CUresult %d", int(res));
     small_tensor_fixup(tm_act, size_t(hw) * d.in_channels * d.batch * 2);
+  } else if (mode == 3) {  // the pair layout {8 values, positions, H, N}: one box = the strip of 128 + T - 1 positions of one input row
+    const cuuint64_t dims[4] = {8, cuuint64_t(r.gp_positions), cuuint64_t(d.in_h), cuuint64_t(d.batch)};
+    const cuuint64_t strides[3] = {16, cuuint64_t(r.gp_positions) * 16, cuuint64_t(d.in_h) * r.gp_positions * 16};
+    const cuuint32_t box[4] = {8, cuuint32_t(128 + r.gp_t - 1), 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult res = g_encode_tiled(tm_act, dt, 4, const_cast<void*>(xn), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (res != CUDA_SUCCESS) return fail(GIEB_CUDA_ERROR, "cuTensorMapEncodeTiled (position strips) failed with CUresult %d", int(res));
+    small_tensor_fixup(tm_act, size_t(d.batch) * d.in_h * r.gp_positions * 16);
   } else if (mode == 1) {  // 1x1 / stride 1 / pad 0: the NHWC copy is the GEMM operand [pixels][Cp] itself
     const cuuint64_t plane = r.subsampled ? cuuint64_t(pl->g.out_h) * pl->g.out_w : cuuint64_t(d.in_h) * d.in_w;
     const cuuint64_t dims[2] = {cuuint64_t(el(r.c_padded)), cuuint64_t(d.batch) * plane};
@@ -759,14 +782,14 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   float* part = r.reduce == 1 ? reinterpret_cast<float*>(wsb + r.ws_x + r.ws_w) : nullptr;
 
   // A direct-NCHW plan needs a 16-byte aligned x (TMA base address rule); otherwise this call takes the repack route.
-  int mode = (r.variant == 1 || r.variant == 5) ? 0 : (r.variant == 4 ? 1 : 2);
+  int mode = r.strip ? 3 : ((r.variant == 1 || r.variant == 5) ? 0 : (r.variant == 4 ? 1 : 2));
   if (mode == 2 && reinterpret_cast<uintptr_t>(x) % 16 != 0) mode = 1;
   const bool in_nhwc = (d.flags & GIEB_FLAG_INPUT_NHWC) != 0;
   if (in_nhwc) {  // read in place
     if (reinterpret_cast<uintptr_t>(x) % 16 != 0) return fail(GIEB_INVALID_ARGUMENT, "a channel-contiguous input must be 16-byte aligned");
     xn = const_cast<void*>(x);
   }
-  const int64_t rows = mode == 2 ? int64_t(d.batch) * r.boxes_per_image * 64 : pl->g.pixels;
+  const int64_t rows = mode == 3 ? int64_t(d.batch) * pl->g.out_h * 128 : (mode == 2 ? int64_t(d.batch) * r.boxes_per_image * 64 : pl->g.pixels);
   // 1x1 filters over unpadded channels: OIHW *is* the [O][RS][C] layout, so when no activation repack would share the
   // launch the weights are read where they lie and the step is the convolution kernel alone (measured on 512 -> 128
   // channels at 28x28: 16.4 instead of 17.5 us per step).
@@ -852,6 +875,8 @@ int launch_impl(const gieb_conv_plan* pl, const void* x, const void* w, const vo
   p.fd_kb_per_tap = FastDiv::make(p.kb_per_tap);
   p.fd_kernel_w = FastDiv::make(p.kernel_w);
   p.fd_boxes = FastDiv::make(p.boxes_per_image > 0 ? p.boxes_per_image : 1);
+  p.fd_out_h = FastDiv::make(p.out_h > 0 ? p.out_h : 1);
+  p.strip_bytes = r.strip ? (128 + r.gp_t - 1) * 16 : 0;
   // persistent CTAs: as many as can be resident at once, each walking the tile list
   const int64_t resident = r.pair ? kNumSmPairs : int64_t(kNumSms) * resident_ctas(r.tile_m, r.tile_n, r.smem);
   // cluster mode: one tile per CTA, blockIdx.x = tile * split + slice (the grid is a multiple of the cluster size);

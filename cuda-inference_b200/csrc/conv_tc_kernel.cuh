@@ -412,7 +412,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const int nbox = p.a_mode == 2 ? 2 * halves : halves;
       uint32_t a_off;
       int c1, c2, c3;  // box coordinates besides the channel coordinate
-      if (p.a_mode == 2) {
+      if (p.a_mode == 3) {
+        // one 128-row box per output row of an image; its operand is the strip of positions of ONE input row per slab
+        const int box = (m0 >> 7) + lane;
+        c3 = p.fd_out_h.div(box);                                    // image
+        c2 = (box - c3 * p.out_h) * p.stride_h - p.pad_h;           // topmost input row of that output row
+        c1 = 0;
+        a_off = uint32_t(lane) * A_HALF_BYTES;
+      } else if (p.a_mode == 2) {
         const int box = (m0 >> 6) + lane;
         c3 = p.fd_boxes.div(box);                        // image
         c1 = (box - c3 * p.boxes_per_image) << 6;       // first pixel
@@ -434,7 +441,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       int r = p.fd_kernel_w.div(tap);
       int sx = tap - r * p.kernel_w;
       int k0 = tap * p.c_padded;
-      const uint32_t tx_bytes = PAIR ? 2u * (A_HALF_BYTES + B_BYTES) : uint32_t(halves) * A_HALF_BYTES + B_BYTES;
+      const uint32_t tx_bytes = PAIR ? 2u * (A_HALF_BYTES + B_BYTES)
+                                     : uint32_t(halves) * (p.a_mode == 3 ? uint32_t(p.strip_bytes) : A_HALF_BYTES) + B_BYTES;
       const int wrow0 = n0 + int(pair_rank) * B_ROWS;  // first weight row (output channel) this CTA loads
       int i = skip;
       join_setup();
@@ -454,7 +462,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           if (lane == 0) ptx::tma_load_2d_pair(a_dst + A_BYTES, &tm_wgt, fb, ch(k0 + cb * BK), wrow0);
         } else {
           if (lane < nbox) {
-            if (p.a_mode == 2) {
+            if (p.a_mode == 3) {
+              ptx::tma_load_4d(a_dst + a_off, &tm_act, &full_bar[s], 0, 0, c2 + r, c3);   // positions 0.. of input row c2 + r
+            } else if (p.a_mode == 2) {
               // 64 pixels x BK channels, [channel][pixel] in shared memory
               ptx::tma_load_3d(a_dst + a_off, &tm_act, &full_bar[s], c1, ch(cb * BK), c3);
             } else if (p.a_mode == 1) {
@@ -514,7 +524,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       // The slab loop exists three times (16-bit K-major A, 16-bit pixel-major A, TF32): the operand form and the MMA
       // kind are compile-time inside it, so the elected lane's issue sequence carries no branch per instruction.
       auto slab_loop = [&](auto form_tag) {
-        constexpr int FORM = decltype(form_tag)::value;  // 0: kind::f16, K-major A; 1: kind::f16, pixel-major A; 2: kind::tf32; 3: kind::f8f6f4 (E4M3)
+        constexpr int FORM = decltype(form_tag)::value;  // 0: kind::f16, K-major A; 1: kind::f16, pixel-major A; 2: kind::tf32; 3: kind::f8f6f4 (E4M3); 4: kind::f16, A = overlapping windows of an unswizzled strip
         // one slab's MMAs and the commit that frees its ring slot (elected lane only)
         auto issue_slab = [&](int slot, bool first) {
           const uint32_t a_addr = ptx::smem_u32(stage_base + size_t(slot) * STAGE_BYTES);
@@ -539,8 +549,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
               for (int k = 0; k < MMAS_PER_SLAB; ++k) {
                 // K-major A: one MMA's K extent (16 two-byte or 8 four-byte values) = 32 bytes along a row.
                 // Pixel-major A (form 1): 16 channels = 16 rows of 128 B.
-                const uint64_t adesc = FORM == 1 ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
-                                                 : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
+                const uint64_t adesc = FORM == 1   ? ptx::smem_desc_mnmajor_sw128(a_addr + h * A_HALF_BYTES + k * 2048, A_HALF_BYTES / 2, 1024)
+                                       : FORM == 4 ? ptx::smem_desc_kmajor_plain(a_addr + h * A_HALF_BYTES + k * 32, 16, 128)
+                                                   : ptx::smem_desc_kmajor<ROW_BYTES>(a_addr + h * A_HALF_BYTES + k * 32);
                 const uint64_t bdesc = ptx::smem_desc_kmajor<ROW_BYTES>(b_addr + k * 32);
                 if constexpr (PAIR && FORM == 3) ptx::mma_f8_ss_pair(acc, adesc, bdesc, p.idesc, !first || k != 0);
                 else if constexpr (PAIR) ptx::mma_f16_ss_pair(acc, adesc, bdesc, p.idesc, !first || k != 0);
@@ -578,6 +589,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       if (!PAIR && !SWAP && p.is_tf32) slab_loop(std::integral_constant<int, 2>{});
       else if (!SWAP && p.is_fp8) slab_loop(std::integral_constant<int, 3>{});
       else if (p.a_mode == 2) slab_loop(std::integral_constant<int, 1>{});
+      else if (!PAIR && !SWAP && p.a_mode == 3) slab_loop(std::integral_constant<int, 4>{});
       else slab_loop(std::integral_constant<int, 0>{});
       // accumulator set complete (also reached after a time-out in the slab loop, so nobody hangs)
       if (ptx::elect_one()) {
@@ -603,7 +615,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     auto decode_row = [&](int m, bool& m_ok, int& img, int& pix) {
       m_ok = m < p.m_total;
       img = pix = 0;
-      if (p.a_mode == 2) {  // rows are numbered in 64-pixel boxes per image
+      if (p.a_mode == 3) {  // rows are numbered in 128-row boxes per output row
+        const int box = m >> 7, q = m & 127;
+        img = p.fd_out_h.div(box);
+        pix = (box - img * p.out_h) * p.out_w + q;
+        m_ok = m_ok && q < p.out_w;
+        if (!m_ok) img = pix = 0;
+      } else if (p.a_mode == 2) {  // rows are numbered in 64-pixel boxes per image
         const int box = m >> 6;
         img = p.fd_boxes.div(box);
         pix = ((box - img * p.boxes_per_image) << 6) + (m & 63);

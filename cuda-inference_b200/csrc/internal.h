@@ -123,6 +123,8 @@ struct ConvTcParams {
   //      numbered in 64-pixel boxes that never straddle an image: m_total = batch * boxes_per_image * 64.
   int a_mode;
   int boxes_per_image;  // mode 2: ceil(H*W / 64)
+  int strip_bytes;      // mode 3: bytes of one position strip (one TMA box); rows are numbered in 128-row boxes per output row
+  FastDiv fd_out_h;     // mode 3: reciprocal of out_h
   uint32_t idesc;
   // > 1: split-K slices of one tile form a thread-block cluster (cluster rank = slice) and are summed through
   // distributed shared memory; blockIdx.x = tile * cluster_split + slice, one tile per CTA, `partial` unused.

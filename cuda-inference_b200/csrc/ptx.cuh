@@ -146,6 +146,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
 // One 128-byte line into L2: a cache fill at the device's coherence point, legal before grid_dep_wait() even if the earlier
 // kernel still writes the line, because those writes go through L2 as well.
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory"); }
+// Tiled 4-D load.
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int32_t x, int32_t y, int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 // im2col-mode 4-D load over an NHWC tensor {C, W, H, N}: starting base pixel (w, h, n), channel c, filter-tap
 // offsets (off_w, off_h).  The unit walks `pixelsPerColumn` base pixels (w fastest, then h, then n) inside the
 // descriptor's bounding box and fetches `channelsPerPixel` channels at base + offset for each, zero-filling
@@ -227,6 +234,15 @@ __device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t saddr) {
   constexpr uint64_t mode = ROW_BYTES == 128 ? 2 : (ROW_BYTES == 64 ? 4 : 6);
   constexpr uint64_t sbo = (8u * ROW_BYTES) >> 4;
   return uint64_t((saddr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (sbo << 32) | (uint64_t(1) << 46) | (mode << 61);
+}
+
+// Unswizzled K-major operand given as its core matrices (8 rows x 16 bytes, rows 16 bytes apart): `lbo_bytes` = distance
+// between core matrices that are neighbours along K, `sbo_bytes` = between neighbours along M / N.  With lbo = 16 and
+// sbo = 128 row m, 16-byte chunk t sits at (m + t) * 16: the operand's rows are OVERLAPPING windows of one dense strip
+// of 16-byte positions (row m = positions m, m + 1, ...), which is how the column-pair gather is read without being
+// expanded.
+__device__ __forceinline__ uint64_t smem_desc_kmajor_plain(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return uint64_t((saddr & 0x3ffffu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(sbo_bytes >> 4) << 32) | (uint64_t(1) << 46);
 }
 
 // MN-major operand (the contiguous direction in shared memory is M or N, 64 elements = 128 bytes per row, 128-byte

@@ -154,6 +154,8 @@ def test_selection_is_deterministic_and_fills_the_machine(pkg):
         assert 1 <= c.split_k <= max(1, total_kb // 2)
         pixels = a[0] * p.out_h * p.out_w
         rows = a[0] * -(-(a[2] * a[3]) // 64) * 64 if i1.variant == 2 else pixels   # direct NCHW route counts 64-pixel boxes
+        if i1.variant == 5 and a[8] == 2 and a[1] <= 4 and p.out_w <= 128:
+            rows = a[0] * p.out_h * 128   # position strips: one 128-row box per output row
         ctas_per_tile = 2 if c.cta_pair == 2 else 1   # a 256-pixel tile of a CTA pair is two CTAs
         assert i1.num_blocks == -(-rows // c.tile_m) * -(-a[4] // c.tile_n) * c.split_k * ctas_per_tile
     # the small deep layer gets split-K, the big ones do not
